@@ -1,0 +1,133 @@
+/*
+ * axconv - table-driven approximate convolution for NVIDIA B200 (sm_100a).
+ *
+ * C ABI of the forward pass of TFApprox's `ApproxConv2DWithMinMaxVars` op and of a
+ * depthwise variant.  Every 8-bit x 8-bit product of the convolution is a lookup in a
+ * 256x256 uint16 truth table, index (activation << 8) | weight.
+ *
+ * The reference (ehw-fit/tf-approximate, tf2 generation) has no C ABI: its boundary is
+ * the TensorFlow op kernel `ApproxConv2DOp::Compute` (tf2/src/approx_nn_conv_ops.cpp:420-460).
+ * Each entry point below names the part of that op it stands in for, so that an op-kernel
+ * shim can keep the op registration (tf2/src/approx_nn_ops.cpp:38-54) byte for byte and
+ * forward to this library.
+ *
+ * Conventions: plain pointers and sizes only; every function returns an axc_status
+ * (0 = OK) and never aborts; tensor pointers are DEVICE pointers on `device` unless a
+ * parameter says otherwise; launches are asynchronous on `stream` (a cudaStream_t passed
+ * as void*, NULL = the legacy default stream).  Calls on different streams or devices may
+ * run concurrently from different host threads.
+ */
+#ifndef AXCONV_H
+#define AXCONV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes.  The numeric values of the first three are TensorFlow's error codes for
+ * the conditions the reference reports through OP_REQUIRES
+ * (tf2/src/approx_nn_conv_ops.cpp:120-121,160-163,224-232,274-303,315-341,521;
+ *  tf2/src/approx_ops_types.h:213). */
+typedef enum {
+    AXC_OK = 0,
+    AXC_INVALID_ARGUMENT = 3,  /* bad shapes/strides/dilations/num_bits, unreadable table  */
+    AXC_UNIMPLEMENTED = 12,    /* EXPLICIT padding, NCHW, grouped (non-depthwise) shapes   */
+    AXC_INTERNAL = 13,         /* e.g. workspace missing or too small                      */
+    AXC_CUDA_ERROR = 100       /* a CUDA call failed; see axc_last_cuda_error()            */
+} axc_status;
+
+enum { AXC_PADDING_SAME = 0, AXC_PADDING_VALID = 1, AXC_PADDING_EXPLICIT = 2 };
+enum { AXC_FORMAT_NHWC = 0, AXC_FORMAT_NCHW = 1 };
+
+/* Geometry of one call: what ApproxConv2DParameters + ApproxConv2DDimensions carry
+ * (tf2/src/approx_nn_conv_ops.h:36-98, filled at tf2/src/approx_nn_conv_ops.cpp:254-404).
+ * input  [n,h,w,c] fp32 NHWC; filter [kh,kw,filter_c,cout] fp32 (HWIO).
+ * For axc_conv2d_forward filter_c must equal c.  For the depthwise entry point filter_c
+ * must equal c and `cout` is the channel multiplier. */
+typedef struct {
+    int32_t n, h, w, c;
+    int32_t kh, kw, filter_c, cout;
+    int32_t stride_h, stride_w;
+    int32_t dil_h, dil_w;
+    int32_t padding;      /* AXC_PADDING_*  */
+    int32_t data_format;  /* AXC_FORMAT_*   */
+} axc_conv_desc;
+
+/* Optional taps into the integer pipeline, for parity checks (device pointers, any may be
+ * NULL).  No counterpart in the reference, whose integer operands live only in its
+ * temporary im2col buffer (tf2/src/approx_nn_conv_ops.cpp:126-153). */
+typedef struct {
+    uint8_t *qinput;  /* [n,h,w,c]            element-wise quantised input               */
+    uint8_t *qfilter; /* [kh*kw*filter_c,cout] element-wise quantised filter             */
+    int32_t *acc;     /* output shape          exact integer sum of the looked-up entries */
+} axc_debug_out;
+
+typedef struct axc_table axc_table;
+
+/* ---- truth table: BaseTableApproxOpType_t (tf2/src/approx_ops_types.h:99-122,205-216)
+ *      and its device copy (tf2/src/cuda/approx_ops_types.cu:20-49) -------------------- */
+
+/* `path` = attr mul_map_file: raw little-endian uint16[65536], no header; NULL or "" gives
+ * the exact product table.  `num_bits` = attr num_bits, must be 8.  Short or missing file:
+ * AXC_INVALID_ARGUMENT ("ApproxTF: Couldn't read the lookup table!"). */
+int axc_table_create_from_file(const char *path, int num_bits, axc_table **out);
+int axc_table_create_from_memory(const uint16_t *lut65536, axc_table **out);
+int axc_table_create_exact(axc_table **out);
+void axc_table_destroy(axc_table *table);
+/* Host copy of the 65536 entries (owned by the table). */
+int axc_table_host_data(const axc_table *table, const uint16_t **out);
+/* Uploads the 128 KiB replica for `device` if it is not there yet (blocking, once per
+ * device).  axc_*_forward does this lazily; call it first to keep the upload out of a
+ * timed or captured region. */
+int axc_table_ensure_device(axc_table *table, int device);
+
+/* ---- geometry: ComputeApproxConv2DDimensions (tf2/src/approx_nn_conv_ops.cpp:311-404) */
+/* out4 = {n, out_h, out_w, out_c}; for the depthwise form out_c = c * cout. */
+int axc_conv2d_output_dims(const axc_conv_desc *desc, int64_t out4[4]);
+int axc_depthwise_conv2d_output_dims(const axc_conv_desc *desc, int64_t out4[4]);
+
+/* Device scratch a forward call needs (the quantised filter in kernel layout and the
+ * per-channel filter sums; stands in for the reference's allocate_temp buffers,
+ * tf2/src/approx_nn_conv_ops.cpp:590-617).  The caller allocates it, 256-byte aligned. */
+int axc_conv2d_workspace_bytes(const axc_conv_desc *desc, size_t *bytes);
+int axc_depthwise_conv2d_workspace_bytes(const axc_conv_desc *desc, size_t *bytes);
+
+/* ---- forward: ApproxConv2DOp::Compute + LaunchApproxConv2DOp<GPUDevice>
+ *      (tf2/src/approx_nn_conv_ops.cpp:420-460, 510-664) with the quantisation state of
+ *      Update() (tf2/src/approx_ops_types.h:158-197) passed by value --------------------
+ * in_min/in_max/f_min/f_max are the op's host-memory scalar inputs 2..5.
+ * An output with zero elements returns AXC_OK without launching anything (:449-450). */
+int axc_conv2d_forward(axc_table *table, const axc_conv_desc *desc,
+                       const float *input, const float *filter,
+                       float in_min, float in_max, float f_min, float f_max,
+                       float *output, void *workspace, size_t workspace_bytes,
+                       const axc_debug_out *debug, int device, void *stream);
+
+/* Depthwise variant (new: the reference rejects grouped shapes,
+ * tf2/src/approx_nn_conv_ops.cpp:229-232).  filter [kh,kw,c,mult] in TensorFlow's
+ * DepthwiseConv2dNative layout, output channel c*mult + m, same quantiser, table
+ * indexing and dequantisation with K = kh*kw. */
+int axc_depthwise_conv2d_forward(axc_table *table, const axc_conv_desc *desc,
+                                 const float *input, const float *filter,
+                                 float in_min, float in_max, float f_min, float f_max,
+                                 float *output, void *workspace, size_t workspace_bytes,
+                                 const axc_debug_out *debug, int device, void *stream);
+
+/* ---- quantisation parameters: Nudge + UpdateVarQuantProps
+ *      (tf2/src/approx_ops_types.h:29-49, 135-152).  out3 = {scale, 1/scale, nudged_min}. */
+int axc_quant_props(float min_value, float max_value, float out3[3]);
+
+/* ---- diagnostics ------------------------------------------------------------------- */
+const char *axc_status_string(int status);
+/* cudaError_t of the most recent AXC_CUDA_ERROR on the calling thread (0 if none). */
+int axc_last_cuda_error(void);
+/* Number of kernels this library has launched in the calling process (monotonic). */
+uint64_t axc_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AXCONV_H */

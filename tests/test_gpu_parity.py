@@ -1,0 +1,272 @@
+"""GPU: the CUDA path, called through the C ABI (ctypes -> libaxconv.so), against the CPU checker.
+
+Bars: quantised uint8 operands and int32 accumulators bit for bit; fp32 output within 1e-6 of the
+checker's epilogue on the exact integer sum, and within 1e-5 of the reference-order fp32 result
+wherever the reference's fp32 running total is itself exact (K <= 256) - both measured with the
+reference's own metric max|out - ref| / max|ref| (tf2/test/test_table_approx_conv_2d.py:62)."""
+import numpy as np
+import pytest
+
+import cases
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL_EXACT = 1e-6   # vs. the epilogue applied to the exact integer sum
+TOL_REF = 1e-5     # vs. the reference-order fp32 arithmetic (north-star tolerance)
+
+
+@pytest.fixture(scope="module")
+def ax(built):
+    import torch
+    assert torch.cuda.is_available()
+    import tf_approximate_b200 as ax
+    from tf_approximate_b200 import _lib
+    _lib.load()  # raises when the CUDA library is missing: there is no fallback
+    return ax
+
+
+def linf(a, ref):
+    m = np.abs(ref).max()
+    return float(np.abs(a - ref).max() / (m if m > 0 else 1.0))
+
+
+def run_dense(ax, lut, x, f, mm, stride, dil, pad):
+    import torch
+    t = ax.Table(array=lut)
+    y, dbg = ax.approx_conv2d_with_min_max_vars(torch.from_numpy(x).cuda(), torch.from_numpy(f).cuda(), *mm,
+                                                strides=[1, stride[0], stride[1], 1], num_bits=8, mul_map_file=t,
+                                                padding=pad, dilations=[1, dil[0], dil[1], 1], debug=True)
+    torch.cuda.synchronize()
+    return y.cpu().numpy(), {k: v.cpu().numpy() for k, v in dbg.items()}
+
+
+def check_dense(ax, lut, x, f, mm, stride=(1, 1), dil=(1, 1), pad="SAME"):
+    n, h, w, c = x.shape
+    kh, kw, _, co = f.shape
+    d = O.desc(n, h, w, c, kh, kw, co, stride, dil, pad)
+    ref = O.conv2d(d, lut, x, f, *mm, want=("out_ref", "out_exact", "acc", "qinput", "qfilter"))
+    y, dbg = run_dense(ax, lut, x, f, mm, stride, dil, pad)
+    assert y.shape == ref["out_exact"].shape
+    assert np.array_equal(dbg["qinput"], ref["qinput"])
+    assert np.array_equal(dbg["qfilter"], ref["qfilter"])
+    assert np.array_equal(dbg["acc"], ref["acc"])
+    assert linf(y, ref["out_exact"]) < TOL_EXACT
+    if kh * kw * c <= 256:
+        assert linf(y, ref["out_ref"]) < TOL_REF
+    return y, ref
+
+
+@pytest.mark.parametrize("case", cases.DENSE_CASES, ids=[c[0] for c in cases.DENSE_CASES])
+def test_golden_dense(ax, golden, case):
+    name, ishape, (kh, kw, cout), stride, dil, pad, tspec, in_range, seed = case
+    lut = cases.make_table(tspec)
+    x, f = cases.make_inputs(ishape, (kh, kw, ishape[3], cout), in_range, seed)
+    mm = (in_range[0], in_range[1], float(f.min()), float(f.max()))
+    y, dbg = run_dense(ax, lut, x, f, mm, stride, dil, pad)
+    assert np.array_equal(dbg["acc"], golden["aux"][name + "_acc"])
+    assert np.array_equal(dbg["qinput"], golden["aux"][name + "_qinput"])
+    assert np.array_equal(dbg["qfilter"], golden["aux"][name + "_qfilter"])
+    assert linf(y, golden["aux"][name + "_out_exact"]) < TOL_EXACT
+    want = golden["ref"][name]   # output of the reference's own CPU kernels
+    if kh * kw * ishape[3] <= 256:
+        assert linf(y, want) < TOL_REF
+    else:
+        # K > 256: the reference's fp32 running total rounds; the residual is its rounding, not ours
+        exact = golden["aux"][name + "_out_exact"]
+        assert linf(y, want) <= linf(exact, want) + TOL_EXACT
+
+
+def test_reference_recipe(ax, golden):
+    """tf2/test/test_table_approx_conv_2d.py: exact table, fake-quantised [0,1] operands, SAME, 8x8 window."""
+    xq, fq = cases.recipe_inputs()
+    y, _ = run_dense(ax, ax.exact_table(), xq, fq, (0.0, 1.0, 0.0, 1.0), (1, 1), (1, 1), "SAME")
+    assert linf(y, golden["ref"]["recipe"]) < TOL_REF
+
+
+def test_config1_full(ax):
+    """N=8, 32x32x16 -> 32, 3x3 SAME, exact table, input [-1,1], filter range from the data."""
+    rng = np.random.Generator(np.random.PCG64(1001))
+    x = rng.uniform(-1, 1, (8, 32, 32, 16)).astype(np.float32)
+    f = np.random.Generator(np.random.PCG64(2100)).normal(0, 0.1, (3, 3, 16, 32)).astype(np.float32)
+    check_dense(ax, ax.exact_table(), x, f, (-1.0, 1.0, float(f.min()), float(f.max())))
+
+
+SHAPES = [
+    # n, h, w, c, kh, kw, cout, stride, dil, pad
+    (2, 9, 11, 5, 3, 3, 7, (1, 1), (1, 1), "SAME"),       # C % 4 != 0, Cout < 32
+    (1, 17, 13, 8, 3, 3, 40, (1, 1), (1, 1), "SAME"),     # Cout tail in the second warp column
+    (1, 10, 10, 12, 3, 3, 70, (2, 2), (1, 1), "SAME"),    # two channel tiles, tail in the second
+    (2, 12, 10, 4, 3, 2, 6, (2, 1), (2, 1), "VALID"),     # dilation + anisotropic stride
+    (3, 8, 8, 16, 1, 1, 32, (1, 1), (1, 1), "SAME"),      # 1x1 fused form
+    (2, 8, 8, 64, 1, 1, 256, (1, 1), (1, 1), "VALID"),    # bottleneck expand
+    (2, 9, 9, 256, 1, 1, 64, (2, 2), (1, 1), "SAME"),     # strided projection
+    (3, 6, 5, 4, 6, 5, 9, (1, 1), (1, 1), "VALID"),       # filter == image
+    (1, 21, 19, 3, 7, 7, 64, (2, 2), (1, 1), "SAME"),     # stem: K = 147, scalar loader
+    (1, 5, 5, 1, 3, 3, 1, (1, 1), (1, 1), "SAME"),        # smallest
+    (1, 4, 4, 512, 3, 3, 33, (1, 1), (1, 1), "SAME"),     # K = 4608, many chunks
+    (5, 7, 7, 20, 3, 3, 64, (1, 1), (1, 1), "SAME"),      # K = 180: chunk tail, pixel tail
+    (1, 30, 30, 2, 5, 5, 3, (3, 3), (1, 1), "VALID"),
+    (1, 9, 9, 6, 2, 2, 5, (1, 1), (3, 3), "SAME"),
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=["-".join(str(v) for v in s[:7]) for s in SHAPES])
+def test_dense_shapes(ax, shape):
+    n, h, w, c, kh, kw, co, stride, dil, pad = shape
+    rng = np.random.Generator(np.random.PCG64(hash(shape[:7]) % (1 << 30)))
+    x = rng.uniform(-1, 1, (n, h, w, c)).astype(np.float32)
+    f = rng.normal(0, 0.1, (kh, kw, c, co)).astype(np.float32)
+    check_dense(ax, cases.make_table(("noisy", 31)), x, f, (-1.0, 1.0, float(f.min()), float(f.max())), stride, dil, pad)
+
+
+def test_out_of_range_inputs_saturate(ax):
+    """Values outside [min,max] clamp to levels 0/255 (the reference's cast is undefined there)."""
+    rng = np.random.Generator(np.random.PCG64(12))
+    x = rng.uniform(-3, 3, (1, 8, 8, 8)).astype(np.float32)
+    f = rng.normal(0, 0.3, (3, 3, 8, 16)).astype(np.float32)
+    check_dense(ax, cases.make_table(("noisy", 32)), x, f, (-1.0, 1.0, -0.2, 0.2))
+
+
+def test_zero_ranges(ax):
+    """min == max == 0 gives scale = 1/scale = offset = 0 (tf2/src/approx_ops_types.h:135-152)."""
+    rng = np.random.Generator(np.random.PCG64(13))
+    x = rng.uniform(-1, 1, (1, 6, 6, 4)).astype(np.float32)
+    f = rng.normal(0, 0.1, (3, 3, 4, 8)).astype(np.float32)
+    check_dense(ax, cases.make_table(("noisy", 33)), x, f, (0.0, 0.0, float(f.min()), float(f.max())))
+    check_dense(ax, cases.make_table(("noisy", 33)), x, f, (-1.0, 1.0, 0.0, 0.0))
+
+
+def test_empty_batch(ax):
+    import torch
+    y = ax.approx_conv2d_with_min_max_vars(torch.zeros(0, 8, 8, 4).cuda(), torch.zeros(3, 3, 4, 8).cuda(),
+                                           -1., 1., -1., 1., [1, 1, 1, 1], 8, "", "SAME")
+    assert tuple(y.shape) == (0, 8, 8, 8)
+
+
+def test_non_symmetric_table_pins_operand_order(ax):
+    """LUT[activation][weight], not the transpose."""
+    lut = np.zeros((256, 256), np.uint16)
+    lut[:, :] = np.arange(256, dtype=np.uint16)[:, None]          # value = activation level
+    x = np.full((1, 3, 3, 4), 0.5, np.float32)
+    f = np.full((1, 1, 4, 2), 0.25, np.float32)
+    y, dbg = run_dense(ax, lut.reshape(-1), x, f, (0.0, 1.0, 0.0, 1.0), (1, 1), (1, 1), "SAME")
+    qa = int(dbg["qinput"][0, 0, 0, 0])
+    assert qa == 128 and int(dbg["qfilter"][0, 0]) == 64
+    assert (dbg["acc"] == 4 * qa).all()
+
+
+# ---- depthwise -----------------------------------------------------------------------------
+def run_depthwise(ax, lut, x, f, mm, stride, dil, pad):
+    import torch
+    y, dbg = ax.approx_depthwise_conv2d_with_min_max_vars(
+        torch.from_numpy(x).cuda(), torch.from_numpy(f).cuda(), *mm, strides=[1, stride[0], stride[1], 1],
+        num_bits=8, mul_map_file=ax.Table(array=lut), padding=pad, dilations=[1, dil[0], dil[1], 1], debug=True)
+    torch.cuda.synchronize()
+    return y.cpu().numpy(), {k: v.cpu().numpy() for k, v in dbg.items()}
+
+
+@pytest.mark.parametrize("case", cases.DEPTHWISE_CASES, ids=[c[0] for c in cases.DEPTHWISE_CASES])
+def test_golden_depthwise(ax, golden, case):
+    name, ishape, (kh, kw, mult), stride, dil, pad, tspec, in_range, seed = case
+    lut = cases.make_table(tspec)
+    x, f = cases.make_inputs(ishape, (kh, kw, ishape[3], mult), in_range, seed)
+    mm = (in_range[0], in_range[1], float(f.min()), float(f.max()))
+    y, dbg = run_depthwise(ax, lut, x, f, mm, stride, dil, pad)
+    assert np.array_equal(dbg["acc"], golden["aux"][name + "_acc"])
+    # K = KH*KW <= 256 and tap-order sums: the checker's fp32 result is reproduced bit for bit
+    assert np.array_equal(y.view(np.uint32), golden["aux"][name + "_out_ref"].view(np.uint32))
+
+
+DW_SHAPES = [
+    (2, 14, 14, 32, 3, 3, 1, (1, 1), (1, 1), "SAME"),
+    (1, 15, 17, 96, 3, 3, 1, (2, 2), (1, 1), "SAME"),
+    (1, 29, 31, 33, 3, 3, 1, (1, 1), (1, 1), "VALID"),   # run tail, channel tail
+    (1, 9, 9, 7, 3, 3, 3, (2, 2), (1, 1), "VALID"),      # multiplier 3
+    (2, 8, 8, 5, 1, 1, 1, (1, 1), (1, 1), "SAME"),
+    (1, 12, 12, 16, 5, 5, 1, (1, 1), (1, 1), "SAME"),
+    (1, 12, 12, 16, 3, 3, 1, (1, 2), (1, 1), "SAME"),    # anisotropic stride -> generic kernel
+]
+
+
+@pytest.mark.parametrize("shape", DW_SHAPES, ids=["-".join(str(v) for v in s[:7]) for s in DW_SHAPES])
+def test_depthwise_shapes(ax, shape):
+    n, h, w, c, kh, kw, mult, stride, dil, pad = shape
+    rng = np.random.Generator(np.random.PCG64(hash(shape[:7]) % (1 << 30)))
+    x = rng.uniform(0, 2, (n, h, w, c)).astype(np.float32)
+    f = rng.normal(0, 0.3, (kh, kw, c, mult)).astype(np.float32)
+    mm = (0.0, 2.0, float(f.min()), float(f.max()))
+    lut = cases.make_table(("noisy", 34))
+    ref = O.depthwise_conv2d(O.desc(n, h, w, c, kh, kw, mult, stride, dil, pad), lut, x, f, *mm)
+    y, dbg = run_depthwise(ax, lut, x, f, mm, stride, dil, pad)
+    assert np.array_equal(dbg["acc"], ref["acc"])
+    assert np.array_equal(y.view(np.uint32), ref["out_ref"].view(np.uint32))
+    q = O.quant_props(*mm).input
+    want_q = np.clip(np.floor((x - np.float32(q.offset)) * np.float32(q.inv_scale) + np.float32(0.5)), 0, 255)
+    assert np.array_equal(dbg["qinput"], want_q.astype(np.uint8))
+
+
+# ---- full-size properties --------------------------------------------------------------------
+def _acc_checksum(torch, qin, qf, lut, kh, kw, stride, pad_before, pad_after, pad_q, oh, ow):
+    """Sum over all outputs of the integer accumulators, from per-tap histograms of the quantised input:
+    sum_{p,j} acc = sum_{tap,c} sum_a hist_{tap,c}(a) * sum_j LUT[a][qf[tap,c,j]]."""
+    n, h, w, c = qin.shape
+    lut_t = torch.from_numpy(lut.astype(np.int64)).cuda().view(256, 256)
+    padded = torch.nn.functional.pad(qin.permute(0, 3, 1, 2).long(),
+                                     (pad_before[1], pad_after[1], pad_before[0], pad_after[0]), value=int(pad_q))
+    total = 0
+    qf = qf.view(kh, kw, c, -1).long()
+    for ky in range(kh):
+        for kx in range(kw):
+            sl = padded[:, :, ky:ky + (oh - 1) * stride + 1:stride, kx:kx + (ow - 1) * stride + 1:stride]  # n,c,oh,ow
+            onehot_hist = torch.zeros(c, 256, dtype=torch.long, device="cuda")
+            idx = sl.permute(1, 0, 2, 3).reshape(c, -1)
+            onehot_hist.scatter_add_(1, idx, torch.ones_like(idx))
+            colsum = lut_t[:, qf[ky, kx]].sum(dim=2)          # [256, c]: sum_j LUT[a][b_cj]
+            total += int((onehot_hist * colsum.t()).sum().item())
+    return total
+
+
+@pytest.mark.parametrize("tspec", [("truncated",), ("noisy", 2)], ids=["truncated", "noisy"])
+def test_config2_full_size_checksum(ax, tspec):
+    """N=256, 56x56x64 -> 64, 3x3 SAME (2.96e10 table MACs): the sum of all int32 accumulators equals the
+    histogram identity above, the quantised operands equal a torch restatement of the quantiser, and a
+    16-image slice equals the same images convolved alone (what batch sharding relies on)."""
+    import torch
+    lut = ax.truncated_table() if tspec[0] == "truncated" else ax.noisy_table(3000 + 200 + tspec[1])
+    g = torch.Generator(device="cuda").manual_seed(1002)
+    x = torch.rand((256, 56, 56, 64), device="cuda", generator=g) * 2 - 1
+    f = torch.randn((3, 3, 64, 64), device="cuda", generator=g) * 0.1
+    mm = (-1.0, 1.0, float(f.min()), float(f.max()))
+    t = ax.Table(array=lut)
+    y, dbg = ax.approx_conv2d_with_min_max_vars(x, f, *mm, [1, 1, 1, 1], 8, t, "SAME", debug=True)
+    torch.cuda.synchronize()
+    q = O.quant_props(*mm)
+    want_q = torch.clamp(torch.floor((x - q.input.offset) * q.input.inv_scale + 0.5), 0, 255).to(torch.uint8)
+    assert torch.equal(dbg["qinput"], want_q)
+    pad_q = O.lib().axo_quantize(0.0, q.input.offset, q.input.inv_scale)
+    chk = _acc_checksum(torch, dbg["qinput"], dbg["qfilter"], lut, 3, 3, 1, (1, 1), (1, 1), pad_q, 56, 56)
+    assert int(dbg["acc"].sum(dtype=torch.int64).item()) == chk
+    y16, dbg16 = ax.approx_conv2d_with_min_max_vars(x[100:116].contiguous(), f, *mm, [1, 1, 1, 1], 8, t, "SAME", debug=True)
+    assert torch.equal(dbg16["acc"], dbg["acc"][100:116]) and torch.equal(y16, y[100:116])
+    # CPU checker on two images of the full-size problem
+    xs = x[37:39].cpu().numpy()
+    ref = O.conv2d(O.desc(2, 56, 56, 64, 3, 3, 64), lut, xs, f.cpu().numpy(), *mm, want=("acc", "out_exact"))
+    assert np.array_equal(dbg["acc"][37:39].cpu().numpy(), ref["acc"])
+    assert linf(y[37:39].cpu().numpy(), ref["out_exact"]) < TOL_EXACT
+
+
+def test_exact_table_equals_integer_convolution_full_size(ax):
+    """With the exact table the accumulators are the integer convolution of the quantised operands."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.rand((64, 56, 56, 64), device="cuda", generator=g) * 2 - 1
+    f = torch.randn((3, 3, 64, 64), device="cuda", generator=g) * 0.1
+    mm = (-1.0, 1.0, float(f.min()), float(f.max()))
+    y, dbg = ax.approx_conv2d_with_min_max_vars(x, f, *mm, [1, 1, 1, 1], 8, "", "SAME", debug=True)
+    q = O.quant_props(*mm)
+    pad_q = float(O.lib().axo_quantize(0.0, q.input.offset, q.input.inv_scale))
+    qa = torch.nn.functional.pad(dbg["qinput"].permute(0, 3, 1, 2).double(), (1, 1, 1, 1), value=pad_q)
+    qb = dbg["qfilter"].view(3, 3, 64, 64).permute(3, 2, 0, 1).double()
+    want = torch.nn.functional.conv2d(qa, qb).permute(0, 2, 3, 1)
+    assert torch.equal(dbg["acc"].double(), want)

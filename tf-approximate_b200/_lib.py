@@ -1,0 +1,62 @@
+"""ctypes view of libaxconv.so (C ABI: include/axconv.h).  There is no fallback: when the
+library is missing or does not load, every operator of this package raises."""
+import ctypes as C
+import os
+
+from . import _build
+
+# every symbol include/axconv.h declares
+SYMBOLS = [
+    "axc_table_create_from_file", "axc_table_create_from_memory", "axc_table_create_exact",
+    "axc_table_destroy", "axc_table_host_data", "axc_table_ensure_device",
+    "axc_conv2d_output_dims", "axc_depthwise_conv2d_output_dims",
+    "axc_conv2d_workspace_bytes", "axc_depthwise_conv2d_workspace_bytes",
+    "axc_conv2d_forward", "axc_depthwise_conv2d_forward",
+    "axc_quant_props", "axc_status_string", "axc_last_cuda_error", "axc_launch_count",
+]
+
+
+class ConvDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in
+                ("n", "h", "w", "c", "kh", "kw", "filter_c", "cout", "stride_h", "stride_w",
+                 "dil_h", "dil_w", "padding", "data_format")]
+
+
+class DebugOut(C.Structure):
+    _fields_ = [("qinput", C.c_void_p), ("qfilter", C.c_void_p), ("acc", C.c_void_p)]
+
+
+_lib = None
+
+
+def load():
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.LIB
+    if not os.path.exists(path):
+        raise RuntimeError("libaxconv.so is not built (%s): run `python -c \"import __graft_entry__ as g; "
+                           "g.build()\"` at the repository root; there is no CPU fallback" % path)
+    L = C.CDLL(path)
+    fwd = [C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.c_float,
+           C.c_float, C.c_void_p, C.c_void_p, C.c_size_t, C.POINTER(DebugOut), C.c_int, C.c_void_p]
+    L.axc_table_create_from_file.argtypes = [C.c_char_p, C.c_int, C.POINTER(C.c_void_p)]
+    L.axc_table_create_from_memory.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+    L.axc_table_create_exact.argtypes = [C.POINTER(C.c_void_p)]
+    L.axc_table_destroy.argtypes = [C.c_void_p]
+    L.axc_table_destroy.restype = None
+    L.axc_table_host_data.argtypes = [C.c_void_p, C.POINTER(C.POINTER(C.c_uint16))]
+    L.axc_table_ensure_device.argtypes = [C.c_void_p, C.c_int]
+    L.axc_conv2d_output_dims.argtypes = [C.POINTER(ConvDesc), C.POINTER(C.c_int64)]
+    L.axc_depthwise_conv2d_output_dims.argtypes = [C.POINTER(ConvDesc), C.POINTER(C.c_int64)]
+    L.axc_conv2d_workspace_bytes.argtypes = [C.POINTER(ConvDesc), C.POINTER(C.c_size_t)]
+    L.axc_depthwise_conv2d_workspace_bytes.argtypes = [C.POINTER(ConvDesc), C.POINTER(C.c_size_t)]
+    L.axc_conv2d_forward.argtypes = fwd
+    L.axc_depthwise_conv2d_forward.argtypes = fwd
+    L.axc_quant_props.argtypes = [C.c_float, C.c_float, C.POINTER(C.c_float)]
+    L.axc_status_string.argtypes = [C.c_int]
+    L.axc_status_string.restype = C.c_char_p
+    L.axc_last_cuda_error.restype = C.c_int
+    L.axc_launch_count.restype = C.c_uint64
+    _lib = L
+    return L

@@ -1,0 +1,401 @@
+// Host side of libaxconv: truth tables, geometry, quantisation parameters and the C ABI.
+// No TensorFlow, no torch: plain CUDA runtime.
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <vector>
+
+#include "axc_internal.h"
+
+struct axc_table {
+    std::vector<uint16_t> host;  // 65536 entries, index (a << 8) | b
+    std::mutex mu;
+    std::vector<uint16_t *> dev;  // per-device replica, lazily created
+};
+
+namespace axc {
+
+static thread_local int g_last_cuda_error = 0;
+static std::atomic<uint64_t> g_launches{0};
+
+int cuda_failed(cudaError_t e)
+{
+    g_last_cuda_error = int(e);
+    return AXC_CUDA_ERROR;
+}
+
+void count_launch(int n) { g_launches.fetch_add(uint64_t(n), std::memory_order_relaxed); }
+
+// Range nudging of TensorFlow's fake-quant as the reference restates it
+// (tf2/src/approx_ops_types.h:29-49) and the zero-range rule of
+// UpdateVarQuantProps (:135-152).  Every operation is a separately rounded fp32
+// operation; the volatile stores keep the host compiler from fusing them.
+void var_quant_props(float min_v, float max_v, float *scale, float *inv, float *offset)
+{
+    volatile float s = 0.0f, i = 0.0f, nudged_min = 0.0f;
+    if (min_v != 0.0f || max_v != 0.0f) {
+        const float qmin = 0.0f, qmax = 255.0f;
+        s = (max_v - min_v) / (qmax - qmin);
+        volatile float ratio = min_v / s;
+        volatile float zp_from_min = qmin - ratio;
+        uint16_t zp;
+        if (zp_from_min < qmin)
+            zp = 0;
+        else if (zp_from_min > qmax)
+            zp = 255;
+        else
+            zp = uint16_t(std::round(zp_from_min));
+        // a true subtraction: 0 - 0 must give +0.0 as in the reference, not the -0.0 of a negation
+        volatile float zp_f = float(zp), zero = qmin;
+        volatile float neg_zp = zero - zp_f;
+        nudged_min = neg_zp * s;
+        i = 1.0f / s;
+    }
+    *scale = s;
+    *inv = i;
+    *offset = nudged_min;
+}
+
+Quant make_quant(float in_min, float in_max, float f_min, float f_max)
+{
+    Quant q;
+    var_quant_props(in_min, in_max, &q.in_scale, &q.in_inv, &q.in_off);
+    var_quant_props(f_min, f_max, &q.f_scale, &q.f_inv, &q.f_off);
+    volatile float s1s2 = q.in_scale * q.f_scale;
+    volatile float m1m2 = q.in_off * q.f_off;
+    q.s1s2 = s1s2;
+    q.m1 = q.in_off;
+    q.m2 = q.f_off;
+    q.m1m2 = m1m2;
+    return q;
+}
+
+// One spatial dimension of TensorFlow's GetWindowedOutputSizeVerboseV2, which the
+// reference calls at tf2/src/approx_nn_conv_ops.cpp:376-382.
+static int window(int in, int k, int dil, int stride, int padding, int *out, int *pad_before)
+{
+    const long long eff = (long long)(k - 1) * dil + 1;
+    if (padding == AXC_PADDING_VALID) {
+        long long o = (in - eff + stride) / stride;
+        if (in - eff + stride < 0) o = -1;
+        *out = int(o);
+        *pad_before = 0;
+    } else {
+        *out = (in + stride - 1) / stride;
+        long long need = (long long)(*out - 1) * stride + eff - in;
+        if (need < 0) need = 0;
+        *pad_before = int(need / 2);
+    }
+    return *out < 0 ? AXC_INVALID_ARGUMENT : AXC_OK;
+}
+
+int resolve_geometry(const axc_conv_desc *d, bool depthwise, Geom *g)
+{
+    if (!d || !g) return AXC_INVALID_ARGUMENT;
+    // Attribute checks of InitApproxConv2DParameters (tf2/src/approx_nn_conv_ops.cpp:254-309).
+    if (d->data_format != AXC_FORMAT_NHWC && d->data_format != AXC_FORMAT_NCHW) return AXC_INVALID_ARGUMENT;
+    if (d->stride_h <= 0 || d->stride_w <= 0) return AXC_INVALID_ARGUMENT;
+    if (d->dil_h <= 0 || d->dil_w <= 0) return AXC_INVALID_ARGUMENT;
+    if (d->padding != AXC_PADDING_SAME && d->padding != AXC_PADDING_VALID && d->padding != AXC_PADDING_EXPLICIT)
+        return AXC_INVALID_ARGUMENT;
+    // Shape checks of ComputeApproxConv2DDimensions (:311-404).
+    if (d->n < 0 || d->h < 0 || d->w < 0 || d->c < 0) return AXC_INVALID_ARGUMENT;
+    if (d->kh <= 0 || d->kw <= 0 || d->filter_c <= 0 || d->cout < 0) return AXC_INVALID_ARGUMENT;
+    if (d->c % d->filter_c != 0) return AXC_INVALID_ARGUMENT;  // "input depth must be evenly divisible by filter depth"
+    // Layout and grouping the kernels do not cover (:160-163, 224-232, 622-625).
+    if (d->data_format != AXC_FORMAT_NHWC) return AXC_UNIMPLEMENTED;
+    if (d->padding == AXC_PADDING_EXPLICIT) return AXC_UNIMPLEMENTED;
+    if (d->c != d->filter_c) return AXC_UNIMPLEMENTED;  // grouped convolution
+
+    g->N = d->n; g->H = d->h; g->W = d->w; g->C = d->c;
+    g->KH = d->kh; g->KW = d->kw; g->Cout = d->cout;
+    g->sh = d->stride_h; g->sw = d->stride_w; g->dh = d->dil_h; g->dw = d->dil_w;
+    int rc = window(d->h, d->kh, d->dil_h, d->stride_h, d->padding, &g->OH, &g->ph);
+    if (rc) return rc;
+    rc = window(d->w, d->kw, d->dil_w, d->stride_w, d->padding, &g->OW, &g->pw);
+    if (rc) return rc;
+    const long long k = depthwise ? (long long)d->kh * d->kw : (long long)d->kh * d->kw * d->c;
+    // "Patch too large for buffer" (:120-121): the reference's im2col chunk holds 4 Mi elements.
+    if (k > (16ll * 1024 * 1024) / (long long)sizeof(float)) return AXC_INVALID_ARGUMENT;
+    g->K = int(k);
+    g->M = (long long)d->n * g->OH * g->OW;
+    const long long out_c = depthwise ? (long long)d->c * d->cout : d->cout;
+    if ((long long)d->n * d->h * d->w * d->c >= (1ll << 40) || g->M * out_c >= (1ll << 40)) return AXC_INVALID_ARGUMENT;
+    if (out_c > (1ll << 30)) return AXC_INVALID_ARGUMENT;
+    return AXC_OK;
+}
+
+static size_t round256(size_t v) { return (v + 255) & ~size_t(255); }
+
+Workspace dense_workspace(int K, int Cout)
+{
+    Workspace w;
+    const size_t kq = size_t((K + 3) / 4);
+    w.prog_bytes = round256(kq * size_t(Cout) * 16);
+    w.sums_off = w.prog_bytes;
+    w.status_off = w.sums_off + round256(size_t(Cout) * 4);
+    w.total = w.status_off + 256;
+    return w;
+}
+
+Workspace depthwise_workspace(int KHW, int C, int mult)
+{
+    Workspace w;
+    const size_t oc = size_t(C) * size_t(mult);
+    w.prog_bytes = round256(size_t(KHW) * oc * 4);
+    w.sums_off = w.prog_bytes;
+    w.status_off = w.sums_off + round256(oc * 4);
+    w.total = w.status_off + 256;
+    return w;
+}
+
+const uint16_t *table_device_ptr(axc_table *t, int device, int *status)
+{
+    *status = AXC_OK;
+    std::lock_guard<std::mutex> lock(t->mu);
+    if (device < 0) {
+        *status = AXC_INVALID_ARGUMENT;
+        return nullptr;
+    }
+    if (size_t(device) < t->dev.size() && t->dev[size_t(device)]) return t->dev[size_t(device)];
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess) {
+        *status = cuda_failed(e);
+        return nullptr;
+    }
+    if (device >= count) {
+        *status = AXC_INVALID_ARGUMENT;
+        return nullptr;
+    }
+    int prev = 0;
+    cudaGetDevice(&prev);
+    uint16_t *p = nullptr;
+    e = cudaSetDevice(device);
+    if (e == cudaSuccess) e = cudaMalloc(&p, 65536 * sizeof(uint16_t));
+    if (e == cudaSuccess) e = cudaMemcpy(p, t->host.data(), 65536 * sizeof(uint16_t), cudaMemcpyHostToDevice);
+    cudaSetDevice(prev);
+    if (e != cudaSuccess) {
+        if (p) cudaFree(p);
+        *status = cuda_failed(e);
+        return nullptr;
+    }
+    if (t->dev.size() <= size_t(device)) t->dev.resize(size_t(device) + 1, nullptr);
+    t->dev[size_t(device)] = p;
+    return p;
+}
+
+int device_info(int device, DeviceInfo *out)
+{
+    static std::mutex mu;
+    static std::vector<DeviceInfo> cache;
+    std::lock_guard<std::mutex> lock(mu);
+    if (device < 0) return AXC_INVALID_ARGUMENT;
+    if (size_t(device) < cache.size() && cache[size_t(device)].sm_count > 0) {
+        *out = cache[size_t(device)];
+        return AXC_OK;
+    }
+    DeviceInfo di;
+    AXC_CUDA(cudaDeviceGetAttribute(&di.sm_count, cudaDevAttrMultiProcessorCount, device));
+    AXC_CUDA(cudaDeviceGetAttribute(&di.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+    if (cache.size() <= size_t(device)) cache.resize(size_t(device) + 1, DeviceInfo{0, 0});
+    cache[size_t(device)] = di;
+    *out = di;
+    return AXC_OK;
+}
+
+// Shared body of the two forward entry points.
+static int forward(bool depthwise, axc_table *table, const axc_conv_desc *desc, const float *input,
+                   const float *filter, float in_min, float in_max, float f_min, float f_max,
+                   float *output, void *workspace, size_t workspace_bytes, const axc_debug_out *dbg,
+                   int device, void *stream)
+{
+    if (!table || !desc) return AXC_INVALID_ARGUMENT;
+    Geom g;
+    int rc = resolve_geometry(desc, depthwise, &g);
+    if (rc) return rc;
+    const long long out_c = depthwise ? (long long)g.C * g.Cout : g.Cout;
+    if (g.M * out_c == 0) return AXC_OK;  // empty output: nothing to do
+    if (!input || !filter || !output) return AXC_INVALID_ARGUMENT;
+    const Workspace ws = depthwise ? depthwise_workspace(g.K, g.C, g.Cout) : dense_workspace(g.K, g.Cout);
+    if (!workspace || workspace_bytes < ws.total) return AXC_INTERNAL;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return AXC_INVALID_ARGUMENT;
+
+    int status = AXC_OK;
+    const uint16_t *lut = table_device_ptr(table, device, &status);
+    if (status) return status;
+
+    int prev = 0;
+    AXC_CUDA(cudaGetDevice(&prev));
+    if (prev != device) AXC_CUDA(cudaSetDevice(device));
+    const Quant q = make_quant(in_min, in_max, f_min, f_max);
+    rc = depthwise ? launch_depthwise(lut, g, q, input, filter, output, workspace, dbg, device, cudaStream_t(stream))
+                   : launch_dense(lut, g, q, input, filter, output, workspace, dbg, device, cudaStream_t(stream));
+    if (prev != device) cudaSetDevice(prev);
+    return rc;
+}
+
+}  // namespace axc
+
+extern "C" {
+
+int axc_table_create_from_memory(const uint16_t *lut65536, axc_table **out)
+{
+    if (!lut65536 || !out) return AXC_INVALID_ARGUMENT;
+    axc_table *t = new (std::nothrow) axc_table;
+    if (!t) return AXC_INTERNAL;
+    t->host.assign(lut65536, lut65536 + 65536);
+    *out = t;
+    return AXC_OK;
+}
+
+int axc_table_create_exact(axc_table **out)
+{
+    if (!out) return AXC_INVALID_ARGUMENT;
+    axc_table *t = new (std::nothrow) axc_table;
+    if (!t) return AXC_INTERNAL;
+    t->host.resize(65536);
+    for (uint32_t i = 0; i < 65536u; ++i) t->host[i] = uint16_t((i >> 8) * (i & 0xFFu));
+    *out = t;
+    return AXC_OK;
+}
+
+int axc_table_create_from_file(const char *path, int num_bits, axc_table **out)
+{
+    if (!out) return AXC_INVALID_ARGUMENT;
+    // The table index shift and the exact-product fallback of the reference only work
+    // for 8 bits (tf2/src/approx_ops_types.h:110-117).
+    if (num_bits != 8) return AXC_INVALID_ARGUMENT;
+    if (!path || !path[0]) return axc_table_create_exact(out);
+    FILE *f = std::fopen(path, "rb");
+    if (!f) return AXC_INVALID_ARGUMENT;
+    axc_table *t = new (std::nothrow) axc_table;
+    if (!t) {
+        std::fclose(f);
+        return AXC_INTERNAL;
+    }
+    t->host.assign(65536, 0);
+    const size_t got = std::fread(t->host.data(), sizeof(uint16_t), 65536, f);
+    std::fclose(f);
+    if (got != 65536) {
+        delete t;
+        return AXC_INVALID_ARGUMENT;
+    }
+    *out = t;
+    return AXC_OK;
+}
+
+void axc_table_destroy(axc_table *t)
+{
+    if (!t) return;
+    int prev = 0;
+    cudaGetDevice(&prev);
+    for (size_t d = 0; d < t->dev.size(); ++d)
+        if (t->dev[d]) {
+            cudaSetDevice(int(d));
+            cudaFree(t->dev[d]);
+        }
+    cudaSetDevice(prev);
+    delete t;
+}
+
+int axc_table_host_data(const axc_table *t, const uint16_t **out)
+{
+    if (!t || !out) return AXC_INVALID_ARGUMENT;
+    *out = t->host.data();
+    return AXC_OK;
+}
+
+int axc_table_ensure_device(axc_table *t, int device)
+{
+    if (!t) return AXC_INVALID_ARGUMENT;
+    int status = AXC_OK;
+    axc::table_device_ptr(t, device, &status);
+    return status;
+}
+
+int axc_conv2d_output_dims(const axc_conv_desc *desc, int64_t out4[4])
+{
+    if (!out4) return AXC_INVALID_ARGUMENT;
+    axc::Geom g;
+    int rc = axc::resolve_geometry(desc, false, &g);
+    if (rc) return rc;
+    out4[0] = g.N; out4[1] = g.OH; out4[2] = g.OW; out4[3] = g.Cout;
+    return AXC_OK;
+}
+
+int axc_depthwise_conv2d_output_dims(const axc_conv_desc *desc, int64_t out4[4])
+{
+    if (!out4) return AXC_INVALID_ARGUMENT;
+    axc::Geom g;
+    int rc = axc::resolve_geometry(desc, true, &g);
+    if (rc) return rc;
+    out4[0] = g.N; out4[1] = g.OH; out4[2] = g.OW; out4[3] = int64_t(g.C) * g.Cout;
+    return AXC_OK;
+}
+
+int axc_conv2d_workspace_bytes(const axc_conv_desc *desc, size_t *bytes)
+{
+    if (!bytes) return AXC_INVALID_ARGUMENT;
+    axc::Geom g;
+    int rc = axc::resolve_geometry(desc, false, &g);
+    if (rc) return rc;
+    *bytes = axc::dense_workspace(g.K, g.Cout).total;
+    return AXC_OK;
+}
+
+int axc_depthwise_conv2d_workspace_bytes(const axc_conv_desc *desc, size_t *bytes)
+{
+    if (!bytes) return AXC_INVALID_ARGUMENT;
+    axc::Geom g;
+    int rc = axc::resolve_geometry(desc, true, &g);
+    if (rc) return rc;
+    *bytes = axc::depthwise_workspace(g.K, g.C, g.Cout).total;
+    return AXC_OK;
+}
+
+int axc_conv2d_forward(axc_table *table, const axc_conv_desc *desc, const float *input, const float *filter,
+                       float in_min, float in_max, float f_min, float f_max, float *output,
+                       void *workspace, size_t workspace_bytes, const axc_debug_out *debug, int device,
+                       void *stream)
+{
+    return axc::forward(false, table, desc, input, filter, in_min, in_max, f_min, f_max, output, workspace,
+                        workspace_bytes, debug, device, stream);
+}
+
+int axc_depthwise_conv2d_forward(axc_table *table, const axc_conv_desc *desc, const float *input,
+                                 const float *filter, float in_min, float in_max, float f_min, float f_max,
+                                 float *output, void *workspace, size_t workspace_bytes,
+                                 const axc_debug_out *debug, int device, void *stream)
+{
+    return axc::forward(true, table, desc, input, filter, in_min, in_max, f_min, f_max, output, workspace,
+                        workspace_bytes, debug, device, stream);
+}
+
+int axc_quant_props(float min_value, float max_value, float out3[3])
+{
+    if (!out3) return AXC_INVALID_ARGUMENT;
+    axc::var_quant_props(min_value, max_value, &out3[0], &out3[1], &out3[2]);
+    return AXC_OK;
+}
+
+const char *axc_status_string(int status)
+{
+    switch (status) {
+    case AXC_OK: return "OK";
+    case AXC_INVALID_ARGUMENT: return "InvalidArgument";
+    case AXC_UNIMPLEMENTED: return "Unimplemented";
+    case AXC_INTERNAL: return "Internal";
+    case AXC_CUDA_ERROR: return "CudaError";
+    default: return "Unknown";
+    }
+}
+
+int axc_last_cuda_error(void) { return axc::g_last_cuda_error; }
+
+uint64_t axc_launch_count(void) { return axc::g_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"

@@ -1,0 +1,486 @@
+// Dense table-driven convolution for sm_100a: one persistent kernel that fuses the
+// activation quantiser, the patch gather (im2col), the table GEMM with int32 accumulators
+// and the fp32 dequantisation, plus two small filter-preparation kernels.
+//
+// It replaces the reference's per-chunk sequence im2col kernel -> GEMM kernel
+// (tf2/src/cuda/approx_nn_conv_kernels.cu:415-489, 513-625) and its broken fused 1x1 kernel
+// (:323-394); the arithmetic follows the reference's CPU kernels
+// (tf2/src/approx_nn_conv_kernels.cpp:167-296).
+//
+// Shared-memory plan of the main kernel (addresses in the CTA's shared window):
+//   [dyn0, 65536)        staging: activation tiles, filter-program tiles, pixel table
+//   [65536, 131072)      table plane 0: entries with weight b < 128,  byte a*256 + 2*b
+//   [131072, 196608)     table plane 1: entries with weight b >= 128, byte a*256 + 2*(b-128)
+//   [196608, 196624)     a zero word, target of the K-tail padding
+// With the planes on 64 KiB boundaries the byte address of LUT[a][b] is the four bytes
+// {2*(b&127), a, 1+(b>>7), 0}: one PRMT builds it from the filter-program word
+// {2*(b&127), 0, 1+(b>>7), 0} and a packed activation word, so a table MAC costs
+// PRMT + LDS.U16 + IADD.
+#include <cstdio>
+
+#include "axc_internal.h"
+
+namespace axc {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kPixPerLane = 16;       // output pixels accumulated by one lane
+constexpr int kKC = 64;               // K elements per staged chunk
+constexpr int kLQ = kKC / 4;          // quads of K per chunk
+constexpr unsigned kLutBase = 65536u;
+constexpr unsigned kZeroWordAddr = 196608u;
+constexpr unsigned kSmemEnd = kZeroWordAddr + 16u;
+constexpr uint32_t kProgPadK = 0x00030000u;   // -> address kZeroWordAddr when the activation byte is 0
+constexpr uint32_t kProgPadN = 0x00010000u;   // any valid table address; result is never stored
+
+struct DenseParams {
+    const uint16_t *lut;
+    const float *input;
+    float *output;
+    const uint4 *prog;     // [ceil(K/4)][Cout] filter-program quads
+    const float *bsum;     // [Cout]
+    int32_t *acc_out;      // optional [M][Cout]
+    int *status;
+    int N, H, W, C, KH, KW, Cout;
+    int sh, sw, dh, dw, ph, pw, OH, OW, K;
+    long long M;
+    int tiles_n;
+    long long tiles_total;
+    float in_off, in_inv, s1s2, m1, m2, km1m2;
+    int vec_ok;            // C % 4 == 0 and 16-byte aligned input
+};
+
+__device__ __forceinline__ unsigned quantize_u8(float x, float off, float inv)
+{
+    // uint8((x - off) * inv + 0.5f): three separately rounded operations
+    // (tf2/src/approx_nn_conv_kernels.cpp:293), saturated to [0, 255].
+    const float v = __fadd_rn(__fmul_rn(__fsub_rn(x, off), inv), 0.5f);
+    const unsigned u = __float2uint_rz(v);  // negative and NaN -> 0
+    return u > 255u ? 255u : u;
+}
+
+__device__ __forceinline__ unsigned lds_u16(unsigned addr)
+{
+    unsigned v;
+    asm("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ uint4 lds_v4(unsigned addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ void sts_u32(unsigned addr, unsigned v)
+{
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ void sts_v4(unsigned addr, uint4 v)
+{
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__device__ __forceinline__ void sts_f32(unsigned addr, float v)
+{
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
+__device__ __forceinline__ float lds_f32(unsigned addr)
+{
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+
+// Filter preparation: quantise the fp32 filter [K][Cout] into kernel-layout program words
+// (one uint4 per (l/4, j): the four words of l = 4*lq .. 4*lq+3) and, optionally, the plain
+// uint8 matrix.  Weight quantiser as tf2/src/approx_nn_conv_kernels.cpp:243.
+__global__ void filter_prep_kernel(const float *__restrict__ filter, int K, int Cout, float f_off, float f_inv,
+                                   uint4 *__restrict__ prog, uint8_t *__restrict__ qfilter, int *status)
+{
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx == 0) *status = 0;
+    const int kq = (K + 3) / 4;
+    if (idx >= (long long)kq * Cout) return;
+    const int lq = int(idx / Cout), j = int(idx % Cout);
+    uint32_t w[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const int l = lq * 4 + e;
+        if (l < K) {
+            const unsigned b = quantize_u8(filter[(size_t)l * Cout + j], f_off, f_inv);
+            w[e] = ((b & 127u) << 1) | ((1u + (b >> 7)) << 16);
+            if (qfilter) qfilter[(size_t)l * Cout + j] = uint8_t(b);
+        } else {
+            w[e] = kProgPadK;
+        }
+    }
+    prog[idx] = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// Per output channel fp32 sum of the filter over (kh, kw, c)
+// (tf2/src/approx_nn_conv_kernels.cpp:300-306).  Block = 32 channels x 8 K-slices; each
+// thread adds its slice in l order, the slices are combined in slice order.
+__global__ void filter_sum_kernel(const float *__restrict__ filter, int K, int Cout, float *__restrict__ bsum)
+{
+    __shared__ float part[8][32];
+    const int j = blockIdx.x * 32 + threadIdx.x;
+    const int s = threadIdx.y;
+    const int per = (K + 7) / 8;
+    const int l0 = s * per, l1 = min(K, l0 + per);
+    float acc = 0.0f;
+    if (j < Cout)
+        for (int l = l0; l < l1; ++l) acc = __fadd_rn(acc, filter[(size_t)l * Cout + j]);
+    part[s][threadIdx.x] = acc;
+    __syncthreads();
+    if (s == 0 && j < Cout) {
+        float t = part[0][threadIdx.x];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) t = __fadd_rn(t, part[i][threadIdx.x]);
+        bsum[j] = t;
+    }
+}
+
+// Element-wise quantised copy of the input, for the parity taps only.
+__global__ void quantize_tensor_kernel(const float *__restrict__ x, long long n, float off, float inv,
+                                       uint8_t *__restrict__ q)
+{
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) q[i] = uint8_t(quantize_u8(x[i], off, inv));
+}
+
+// One CTA per SM, persistent over output tiles of TM pixels x TN channels
+// (TN = 32 * WN, TM = 16 * (8 / WN)).  Lane = output channel, 16 pixels per lane.
+template <int WN>
+__global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
+{
+    constexpr int WM = kWarps / WN;
+    constexpr int TM = WM * kPixPerLane;
+    constexpr int TN = WN * 32;
+    constexpr int AROW = TM + 4;                       // words per K-quad row of the activation tile
+    constexpr int A_BYTES = kLQ * AROW * 4;
+    constexpr int W_BYTES = kLQ * TN * 16;
+    constexpr int PIX_SLOTS = (TM / 4) / kWarps;       // pixel groups a loader thread visits per K-quad half
+    constexpr int A_ITERS = (kLQ / 8) * PIX_SLOTS;     // activation quads per thread per chunk
+    constexpr int W_ITERS = (kLQ * TN) / kThreads;     // program quads per thread per chunk
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const unsigned dyn0 = (unsigned)__cvta_generic_to_shared(smem_raw);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    // staging layout, from the first 16-byte boundary at or after dyn0
+    unsigned cur = (dyn0 + 15u) & ~15u;
+    const unsigned sA = cur;            cur += 2 * A_BYTES;
+    const unsigned sW = cur;            cur += 2 * W_BYTES;
+    const unsigned sPixBase = cur;      cur += TM * 8;   // long long element offset of (n, iy0, ix0, 0)
+    const unsigned sPixY = cur;         cur += TM * 4;
+    const unsigned sPixX = cur;         cur += TM * 4;
+    const unsigned sAsum = cur;         cur += TM * 4;
+    unsigned dyn_size;
+    asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
+    if (cur > kLutBase || dyn0 + dyn_size < kSmemEnd) {
+        if (tid == 0) atomicExch(P.status, 1);
+        return;
+    }
+
+    // ---- table planes --------------------------------------------------------------
+    {
+        const uint4 *src = reinterpret_cast<const uint4 *>(P.lut);
+        for (int i = tid; i < 8192; i += kThreads) {
+            const int a = i >> 5, part = i & 31;
+            const uint4 v = __ldg(src + i);
+            const unsigned dst = kLutBase + (part >= 16 ? 65536u : 0u) + unsigned(a) * 256u + unsigned(part & 15) * 16u;
+            sts_v4(dst, v);
+        }
+        if (tid == 0) sts_v4(kZeroWordAddr, make_uint4(0, 0, 0, 0));
+    }
+
+    const int wn = warp % WN, wm = warp / WN;
+    const int lq_lo = lane & 7, p_lo = lane >> 3;
+
+    for (long long tile = blockIdx.x; tile < P.tiles_total; tile += gridDim.x) {
+        const long long mt = tile / P.tiles_n;
+        const int nt = int(tile - mt * P.tiles_n);
+        const long long m0 = mt * TM;
+        const int j0 = nt * TN;
+
+        __syncthreads();  // previous tile fully consumed (also orders the table fill)
+        if (tid < TM) {
+            const long long p = m0 + tid;
+            long long base = 0;
+            int iy0 = -(1 << 28), ix0 = -(1 << 28);  // invalid pixel: every tap out of range
+            if (p < P.M) {
+                const int ow = int(p % P.OW);
+                const long long t = p / P.OW;
+                const int oh = int(t % P.OH);
+                const int n = int(t / P.OH);
+                iy0 = oh * P.sh - P.ph;
+                ix0 = ow * P.sw - P.pw;
+                base = (((long long)n * P.H + iy0) * P.W + ix0) * P.C;
+            }
+            asm volatile("st.shared.u64 [%0], %1;" ::"r"(sPixBase + tid * 8), "l"(base) : "memory");
+            sts_u32(sPixY + tid * 4, unsigned(iy0));
+            sts_u32(sPixX + tid * 4, unsigned(ix0));
+        }
+        __syncthreads();
+
+        // per-thread loader coordinates: pixel slots and their geometry
+        long long pbase[PIX_SLOTS];
+        int piy[PIX_SLOTS], pix[PIX_SLOTS];
+        float asum[PIX_SLOTS];
+#pragma unroll
+        for (int s = 0; s < PIX_SLOTS; ++s) {
+            const int p = (s * kWarps + warp) * 4 + p_lo;
+            unsigned ty, tx;
+            asm volatile("ld.shared.u64 %0, [%1];" : "=l"(pbase[s]) : "r"(sPixBase + p * 8));
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(ty) : "r"(sPixY + p * 4));
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tx) : "r"(sPixX + p * 4));
+            piy[s] = int(ty);
+            pix[s] = int(tx);
+            asum[s] = 0.0f;
+        }
+
+        int acc[kPixPerLane];
+#pragma unroll
+        for (int i = 0; i < kPixPerLane; ++i) acc[i] = 0;
+
+        const int n_chunks = (P.K + kKC - 1) / kKC;
+        const int kq_total = (P.K + 3) / 4;
+        float4 a_stage[A_ITERS];   // raw fp32 taps of the next chunk, quantised when stored
+        uint4 w_stage[W_ITERS];
+
+        // Issue the global loads of chunk `ch` (activation taps and filter-program quads).
+        auto load_chunk = [&](int ch) {
+            const int k0 = ch * kKC;
+#pragma unroll
+            for (int h = 0; h < kLQ / 8; ++h) {
+                const int l0 = k0 + (h * 8 + lq_lo) * 4;
+                if (P.vec_ok) {
+                    const int tap = l0 / P.C;
+                    const int c = l0 - tap * P.C;
+                    const int ky = tap / P.KW;
+                    const int kx = tap - ky * P.KW;
+                    const int dy = ky * P.dh, dx = kx * P.dw;
+                    const long long toff = ((long long)dy * P.W + dx) * P.C + c;
+#pragma unroll
+                    for (int s = 0; s < PIX_SLOTS; ++s) {
+                        const int iy = piy[s] + dy, ix = pix[s] + dx;
+                        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (l0 < P.K && iy >= 0 && iy < P.H && ix >= 0 && ix < P.W)
+                            v = __ldg(reinterpret_cast<const float4 *>(P.input + pbase[s] + toff));
+                        a_stage[h * PIX_SLOTS + s] = v;
+                    }
+                } else {
+                    float vals[PIX_SLOTS][4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int l = l0 + e;
+                        const int tap = l / P.C;
+                        const int c = l - tap * P.C;
+                        const int ky = tap / P.KW;
+                        const int kx = tap - ky * P.KW;
+                        const int dy = ky * P.dh, dx = kx * P.dw;
+                        const long long toff = ((long long)dy * P.W + dx) * P.C + c;
+#pragma unroll
+                        for (int s = 0; s < PIX_SLOTS; ++s) {
+                            const int iy = piy[s] + dy, ix = pix[s] + dx;
+                            float v = 0.f;
+                            if (l < P.K && iy >= 0 && iy < P.H && ix >= 0 && ix < P.W) v = __ldg(P.input + pbase[s] + toff);
+                            vals[s][e] = v;
+                        }
+                    }
+#pragma unroll
+                    for (int s = 0; s < PIX_SLOTS; ++s)
+                        a_stage[h * PIX_SLOTS + s] = make_float4(vals[s][0], vals[s][1], vals[s][2], vals[s][3]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < W_ITERS; ++i) {
+                const int e = i * kThreads + tid;
+                const int lq = e / TN, jj = e - lq * TN;
+                const int lqg = ch * kLQ + lq, j = j0 + jj;
+                uint4 v;
+                if (lqg >= kq_total) v = make_uint4(kProgPadK, kProgPadK, kProgPadK, kProgPadK);
+                else if (j >= P.Cout) v = make_uint4(kProgPadN, kProgPadN, kProgPadN, kProgPadN);
+                else v = __ldg(P.prog + (size_t)lqg * P.Cout + j);
+                w_stage[i] = v;
+            }
+        };
+
+        // Quantise the staged taps of chunk `ch`, add them to the patch sums and publish the tiles.
+        // A tap with l >= K stores byte 0: with the K-tail program word it addresses the zero word.
+        auto store_chunk = [&](int ch, int buf) {
+            const int k0 = ch * kKC;
+#pragma unroll
+            for (int h = 0; h < kLQ / 8; ++h)
+#pragma unroll
+                for (int s = 0; s < PIX_SLOTS; ++s) {
+                    const int lq = h * 8 + lq_lo;
+                    const int l0 = k0 + lq * 4;
+                    const int p = (s * kWarps + warp) * 4 + p_lo;
+                    const float4 v = a_stage[h * PIX_SLOTS + s];
+                    asum[s] = __fadd_rn(asum[s], __fadd_rn(__fadd_rn(v.x, v.y), __fadd_rn(v.z, v.w)));
+                    uint32_t packed = 0;
+                    if (l0 + 0 < P.K) packed |= quantize_u8(v.x, P.in_off, P.in_inv);
+                    if (l0 + 1 < P.K) packed |= quantize_u8(v.y, P.in_off, P.in_inv) << 8;
+                    if (l0 + 2 < P.K) packed |= quantize_u8(v.z, P.in_off, P.in_inv) << 16;
+                    if (l0 + 3 < P.K) packed |= quantize_u8(v.w, P.in_off, P.in_inv) << 24;
+                    sts_u32(sA + buf * A_BYTES + (lq * AROW + p) * 4, packed);
+                }
+#pragma unroll
+            for (int i = 0; i < W_ITERS; ++i) {
+                const int e = i * kThreads + tid;
+                sts_v4(sW + buf * W_BYTES + e * 16, w_stage[i]);
+            }
+        };
+
+        load_chunk(0);
+        store_chunk(0, 0);
+        __syncthreads();
+
+        for (int ch = 0; ch < n_chunks; ++ch) {
+            const int buf = ch & 1;
+            const bool more = ch + 1 < n_chunks;
+            if (more) load_chunk(ch + 1);
+
+            const unsigned aBase = sA + buf * A_BYTES + wm * kPixPerLane * 4;
+            const unsigned wBase = sW + buf * W_BYTES + (wn * 32 + lane) * 16;
+#pragma unroll 2
+            for (int lq = 0; lq < kLQ; ++lq) {
+                const uint4 wv = lds_v4(wBase + lq * TN * 16);
+#pragma unroll
+                for (int pg = 0; pg < kPixPerLane / 4; ++pg) {
+                    const uint4 av = lds_v4(aBase + (lq * AROW + pg * 4) * 4);
+                    const unsigned aw[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+                    for (int pp = 0; pp < 4; ++pp) {
+                        int s = acc[pg * 4 + pp];
+                        s += int(lds_u16(__byte_perm(wv.x, aw[pp], 0x3240)));
+                        s += int(lds_u16(__byte_perm(wv.y, aw[pp], 0x3250)));
+                        s += int(lds_u16(__byte_perm(wv.z, aw[pp], 0x3260)));
+                        s += int(lds_u16(__byte_perm(wv.w, aw[pp], 0x3270)));
+                        acc[pg * 4 + pp] = s;
+                    }
+                }
+            }
+
+            if (more) store_chunk(ch + 1, buf ^ 1);
+            __syncthreads();
+        }
+
+        // patch sums: combine the 8 lanes that share a pixel, in a fixed order
+#pragma unroll
+        for (int s = 0; s < PIX_SLOTS; ++s) {
+            float v = asum[s];
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
+            if (lq_lo == 0) sts_f32(sAsum + ((s * kWarps + warp) * 4 + p_lo) * 4, v);
+        }
+        __syncthreads();
+
+        // ---- dequantisation: ((S*s1s2 + m2*aSum) + m1*bSum) - K*m1m2 -----------------
+        const int j = j0 + wn * 32 + lane;
+        if (j < P.Cout) {
+            const float t2 = __fmul_rn(P.m1, __ldg(P.bsum + j));
+#pragma unroll
+            for (int i = 0; i < kPixPerLane; ++i) {
+                const long long p = m0 + wm * kPixPerLane + i;
+                if (p < P.M) {
+                    const float a_sum = lds_f32(sAsum + (wm * kPixPerLane + i) * 4);
+                    const float t0 = __fmul_rn(float(acc[i]), P.s1s2);
+                    const float t1 = __fmul_rn(P.m2, a_sum);
+                    const float o = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), P.km1m2);
+                    P.output[p * P.Cout + j] = o;
+                    if (P.acc_out) P.acc_out[p * P.Cout + j] = acc[i];
+                }
+            }
+        }
+    }
+}
+
+template <int WN>
+int launch_dense_variant(const DenseParams &P, const DeviceInfo &di, cudaStream_t stream)
+{
+    constexpr int TM = (kWarps / WN) * kPixPerLane;
+    constexpr int TN = WN * 32;
+    DenseParams Q = P;
+    Q.tiles_n = (P.Cout + TN - 1) / TN;
+    Q.tiles_total = ((P.M + TM - 1) / TM) * Q.tiles_n;
+    static bool configured[64] = {};
+    int dev = 0;
+    AXC_CUDA(cudaGetDevice(&dev));
+    if (dev < 64 && !configured[dev]) {
+        AXC_CUDA(cudaFuncSetAttribute(dense_kernel<WN>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
+        configured[dev] = true;
+    } else if (dev >= 64) {
+        AXC_CUDA(cudaFuncSetAttribute(dense_kernel<WN>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
+    }
+    const long long grid = Q.tiles_total < di.sm_count ? Q.tiles_total : di.sm_count;
+    dense_kernel<WN><<<unsigned(grid), kThreads, size_t(di.max_smem_optin), stream>>>(Q);
+    AXC_CUDA(cudaGetLastError());
+    count_launch();
+    return AXC_OK;
+}
+
+}  // namespace
+
+int launch_dense(const uint16_t *lut_dev, const Geom &g, const Quant &q, const float *input, const float *filter,
+                 float *output, void *workspace, const axc_debug_out *dbg, int device, cudaStream_t stream)
+{
+    DeviceInfo di;
+    int rc = device_info(device, &di);
+    if (rc) return rc;
+    if (di.max_smem_optin < int(kSmemEnd)) return AXC_INTERNAL;
+    const Workspace ws = dense_workspace(g.K, g.Cout);
+    unsigned char *wsb = static_cast<unsigned char *>(workspace);
+    uint4 *prog = reinterpret_cast<uint4 *>(wsb);
+    float *bsum = reinterpret_cast<float *>(wsb + ws.sums_off);
+    int *status = reinterpret_cast<int *>(wsb + ws.status_off);
+
+    {
+        const long long items = (long long)((g.K + 3) / 4) * g.Cout;
+        const unsigned blocks = unsigned((items + 255) / 256);
+        filter_prep_kernel<<<blocks, 256, 0, stream>>>(filter, g.K, g.Cout, q.f_off, q.f_inv, prog,
+                                                       dbg ? dbg->qfilter : nullptr, status);
+        AXC_CUDA(cudaGetLastError());
+        filter_sum_kernel<<<unsigned((g.Cout + 31) / 32), dim3(32, 8), 0, stream>>>(filter, g.K, g.Cout, bsum);
+        AXC_CUDA(cudaGetLastError());
+        count_launch(2);
+    }
+    if (dbg && dbg->qinput) {
+        const long long n = (long long)g.N * g.H * g.W * g.C;
+        if (n > 0) {
+            const unsigned blocks = unsigned(n / 256 + 1 < 4096 ? n / 256 + 1 : 4096);
+            quantize_tensor_kernel<<<blocks, 256, 0, stream>>>(input, n, q.in_off, q.in_inv, dbg->qinput);
+            AXC_CUDA(cudaGetLastError());
+            count_launch();
+        }
+    }
+
+    DenseParams P;
+    P.lut = lut_dev; P.input = input; P.output = output; P.prog = prog; P.bsum = bsum;
+    P.acc_out = dbg ? dbg->acc : nullptr;
+    P.status = status;
+    P.N = g.N; P.H = g.H; P.W = g.W; P.C = g.C; P.KH = g.KH; P.KW = g.KW; P.Cout = g.Cout;
+    P.sh = g.sh; P.sw = g.sw; P.dh = g.dh; P.dw = g.dw; P.ph = g.ph; P.pw = g.pw; P.OH = g.OH; P.OW = g.OW;
+    P.K = g.K; P.M = g.M;
+    P.tiles_n = 0; P.tiles_total = 0;
+    P.in_off = q.in_off; P.in_inv = q.in_inv; P.s1s2 = q.s1s2; P.m1 = q.m1; P.m2 = q.m2;
+    {
+        volatile float kf = float(g.K);
+        volatile float t3 = kf * q.m1m2;
+        P.km1m2 = t3;
+    }
+    P.vec_ok = (g.C % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
+    if (g.Cout <= 32) return launch_dense_variant<1>(P, di, stream);
+    return launch_dense_variant<2>(P, di, stream);
+}
+
+}  // namespace axc

@@ -1,0 +1,73 @@
+// Internal declarations shared by the translation units of libaxconv.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "axconv.h"
+
+namespace axc {
+
+// Quantisation state of one call: what the reference keeps in
+// BaseTableApproxOpType_t::quantProps (tf2/src/approx_ops_types.h:84-96).
+struct Quant {
+    float in_scale, in_inv, in_off;
+    float f_scale, f_inv, f_off;
+    float s1s2, m1, m2, m1m2;
+};
+
+// Resolved geometry (TensorFlow window arithmetic applied).
+struct Geom {
+    int N, H, W, C;
+    int KH, KW, Cout;  // depthwise: Cout = channel multiplier
+    int sh, sw, dh, dw;
+    int ph, pw;        // padding before (rows, cols)
+    int OH, OW;
+    int K;             // dense: KH*KW*C; depthwise: KH*KW
+    long long M;       // N*OH*OW
+};
+
+void var_quant_props(float min_v, float max_v, float *scale, float *inv, float *offset);
+Quant make_quant(float in_min, float in_max, float f_min, float f_max);
+
+// Validates `d` the way the reference op does and fills `g`.  depthwise selects the
+// grouped interpretation of the filter.
+int resolve_geometry(const axc_conv_desc *d, bool depthwise, Geom *g);
+
+// Records a failed CUDA call for axc_last_cuda_error() and returns AXC_CUDA_ERROR.
+int cuda_failed(cudaError_t e);
+void count_launch(int n = 1);
+
+#define AXC_CUDA(expr)                                        \
+    do {                                                      \
+        cudaError_t _e = (expr);                              \
+        if (_e != cudaSuccess) return ::axc::cuda_failed(_e); \
+    } while (0)
+
+// Device replica of a table (native [a][b] order, 65536 uint16).
+const uint16_t *table_device_ptr(axc_table *t, int device, int *status);
+
+struct DeviceInfo {
+    int sm_count;
+    int max_smem_optin;
+};
+int device_info(int device, DeviceInfo *out);
+
+// ---- workspace layout (dense) ---------------------------------------------------------
+//   [0, prog_bytes)            kernel-layout filter program: uint4 per (l/4, j)
+//   [prog_bytes, +4*Cout)      per-channel fp32 filter sums
+//   [.., +16)                  status word (0 = fine)
+struct Workspace {
+    size_t prog_bytes, sums_off, status_off, total;
+};
+Workspace dense_workspace(int K, int Cout);
+Workspace depthwise_workspace(int KHW, int C, int mult);
+
+// Kernel launchers (axc_conv.cu / axc_depthwise.cu).
+int launch_dense(const uint16_t *lut_dev, const Geom &g, const Quant &q, const float *input,
+                 const float *filter, float *output, void *workspace, const axc_debug_out *dbg,
+                 int device, cudaStream_t stream);
+int launch_depthwise(const uint16_t *lut_dev, const Geom &g, const Quant &q, const float *input,
+                     const float *filter, float *output, void *workspace, const axc_debug_out *dbg,
+                     int device, cudaStream_t stream);
+
+}  // namespace axc

@@ -1,0 +1,211 @@
+"""Host-side mirror of the reference op on torch CUDA tensors.
+
+`approx_conv2d_with_min_max_vars` keeps the name, the argument order and the error behaviour of
+the generated TensorFlow wrapper of `ApproxConv2DWithMinMaxVars`
+(tf2/src/approx_nn_ops.cpp:38-54; call site tf2/test/test_table_approx_conv_2d.py:46-49).
+torch is used for device memory and streams only."""
+import ctypes as C
+import threading
+
+import numpy as np
+import torch
+
+from . import _lib
+from .errors import InvalidArgumentError, raise_for_status
+
+_PADDING = {"SAME": 0, "VALID": 1, "EXPLICIT": 2}
+_FORMAT = {"NHWC": 0, "NCHW": 1}
+
+
+class Table:
+    """A truth table handle: host copy plus lazily created per-GPU replicas
+    (reference: BaseTableApproxOpType_t, tf2/src/approx_ops_types.h:99-122)."""
+
+    def __init__(self, mul_map_file="", num_bits=8, array=None):
+        L = _lib.load()
+        h = C.c_void_p()
+        if array is not None:
+            a = np.ascontiguousarray(array, dtype=np.uint16).reshape(-1)
+            if a.size != 65536:
+                raise InvalidArgumentError("a truth table has 65536 entries")
+            st = L.axc_table_create_from_memory(a.ctypes.data, C.byref(h))
+        else:
+            if isinstance(mul_map_file, bytes):
+                mul_map_file = mul_map_file.decode()
+            st = L.axc_table_create_from_file(mul_map_file.encode(), int(num_bits), C.byref(h))
+        raise_for_status(st, "table", "ApproxTF: Couldn't read the lookup table!" if num_bits == 8 else
+                         "only num_bits == 8 is supported")
+        self._h = h
+
+    @property
+    def handle(self):
+        return self._h
+
+    def numpy(self):
+        p = C.POINTER(C.c_uint16)()
+        raise_for_status(_lib.load().axc_table_host_data(self._h, C.byref(p)), "table data")
+        return np.ctypeslib.as_array(p, shape=(65536,)).copy()
+
+    def ensure_device(self, device):
+        raise_for_status(_lib.load().axc_table_ensure_device(self._h, int(device)), "table upload", _cuda_detail())
+
+    def __del__(self):
+        try:
+            if getattr(self, "_h", None):
+                _lib.load().axc_table_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+
+_tables = {}
+_tables_lock = threading.Lock()
+
+
+def _table_for(mul_map_file, num_bits):
+    if isinstance(mul_map_file, Table):
+        return mul_map_file
+    key = (mul_map_file or "", int(num_bits))
+    with _tables_lock:
+        t = _tables.get(key)
+        if t is None:
+            t = Table(mul_map_file or "", num_bits)
+            _tables[key] = t
+        return t
+
+
+def _cuda_detail():
+    return "cudaError %d" % _lib.load().axc_last_cuda_error()
+
+
+def _scalar(v):
+    if isinstance(v, torch.Tensor):
+        return float(v.item())  # host-memory scalar input of the op (tf2/src/approx_nn_conv_ops.cpp:691-694)
+    return float(v)
+
+
+def _desc(input_shape, filter_shape, strides, padding, data_format, dilations, explicit_paddings):
+    if len(input_shape) != 4:
+        raise InvalidArgumentError("input must be 4-dimensional %s" % (tuple(input_shape),))
+    if len(filter_shape) != 4:
+        raise InvalidArgumentError("filter must be 4-dimensional %s" % (tuple(filter_shape),))
+    if data_format not in _FORMAT:
+        raise InvalidArgumentError("Invalid data format")
+    if len(strides) != 4:
+        raise InvalidArgumentError("Sliding window strides must specify 4 dimensions")
+    if len(dilations) != 4:
+        raise InvalidArgumentError("Sliding window dilations field must specify 4 dimensions")
+    pad = padding.upper() if isinstance(padding, str) else padding
+    if pad not in _PADDING:
+        raise InvalidArgumentError("unknown padding %r" % (padding,))
+    if pad != "EXPLICIT" and len(explicit_paddings) != 0:
+        raise InvalidArgumentError("explicit_paddings attribute must be empty if the padding attribute is not EXPLICIT")
+    # NHWC positions; an NCHW request is rejected by the library as Unimplemented
+    n_i, h_i, w_i, c_i = (0, 1, 2, 3) if data_format == "NHWC" else (0, 2, 3, 1)
+    if strides[n_i] != 1 or strides[c_i] != 1:
+        raise InvalidArgumentError("Current implementation does not yet support strides in the batch and depth dimensions.")
+    if dilations[n_i] != 1 or dilations[c_i] != 1:
+        raise InvalidArgumentError("Current implementation does not yet support dilations in the batch and depth dimensions.")
+    return _lib.ConvDesc(int(input_shape[n_i]), int(input_shape[h_i]), int(input_shape[w_i]), int(input_shape[c_i]),
+                         int(filter_shape[0]), int(filter_shape[1]), int(filter_shape[2]), int(filter_shape[3]),
+                         int(strides[h_i]), int(strides[w_i]), int(dilations[h_i]), int(dilations[w_i]),
+                         _PADDING[pad], _FORMAT[data_format])
+
+
+def conv2d_output_shape(input_shape, filter_shape, strides, padding, data_format="NHWC", dilations=(1, 1, 1, 1),
+                        depthwise=False):
+    """Output shape as the op's shape function gives it (tf2/src/approx_nn_conv_ops.cpp:311-404)."""
+    d = _desc(input_shape, filter_shape, strides, padding, data_format, dilations, [])
+    out = (C.c_int64 * 4)()
+    L = _lib.load()
+    fn = L.axc_depthwise_conv2d_output_dims if depthwise else L.axc_conv2d_output_dims
+    raise_for_status(fn(C.byref(d), out), "output dims")
+    return tuple(int(v) for v in out)
+
+
+_ws_cache = {}
+
+
+def _workspace(device, nbytes):
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _ws_cache.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _ws_cache[key] = buf
+    return buf
+
+
+def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
+             mul_map_file, padding, explicit_paddings, data_format, dilations, out, debug):
+    L = _lib.load()
+    if not isinstance(input, torch.Tensor) or not isinstance(filter, torch.Tensor):
+        raise InvalidArgumentError("input and filter must be torch tensors")
+    if not input.is_cuda or not filter.is_cuda:
+        raise InvalidArgumentError("input and filter must live on a CUDA device (this build has no CPU kernel)")
+    if input.dtype != torch.float32 or filter.dtype != torch.float32:
+        raise InvalidArgumentError("only T = float is registered for the table op")
+    if filter.device != input.device:
+        raise InvalidArgumentError("input and filter are on different devices")
+    table = _table_for(mul_map_file, num_bits)
+    d = _desc(input.shape, filter.shape, strides, padding, data_format, dilations, explicit_paddings)
+    dims = (C.c_int64 * 4)()
+    dims_fn = L.axc_depthwise_conv2d_output_dims if depthwise else L.axc_conv2d_output_dims
+    raise_for_status(dims_fn(C.byref(d), dims), "ApproxConv2D")
+    oshape = tuple(int(v) for v in dims)
+    dev = input.device
+    x = input.contiguous()
+    f = filter.contiguous()
+    if out is None:
+        out = torch.empty(oshape, dtype=torch.float32, device=dev)
+    elif tuple(out.shape) != oshape or out.dtype != torch.float32 or not out.is_contiguous() or out.device != dev:
+        raise InvalidArgumentError("out has the wrong shape, dtype, layout or device")
+    wsz = C.c_size_t()
+    ws_fn = L.axc_depthwise_conv2d_workspace_bytes if depthwise else L.axc_conv2d_workspace_bytes
+    raise_for_status(ws_fn(C.byref(d), C.byref(wsz)), "workspace size")
+    ws = _workspace(dev, wsz.value)
+    dbg_ptr = None
+    dbg_t = None
+    if debug:
+        kdim = int(f.shape[0] * f.shape[1] * (1 if depthwise else f.shape[2]))
+        ncol = int(f.shape[2] * f.shape[3]) if depthwise else int(f.shape[3])
+        dbg_t = {"qinput": torch.empty(tuple(x.shape), dtype=torch.uint8, device=dev),
+                 "qfilter": torch.empty((kdim, ncol), dtype=torch.uint8, device=dev),
+                 "acc": torch.empty(oshape, dtype=torch.int32, device=dev)}
+        dbg = _lib.DebugOut(dbg_t["qinput"].data_ptr(), dbg_t["qfilter"].data_ptr(), dbg_t["acc"].data_ptr())
+        dbg_ptr = C.byref(dbg)
+    fwd = L.axc_depthwise_conv2d_forward if depthwise else L.axc_conv2d_forward
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    st = fwd(table.handle, C.byref(d), x.data_ptr(), f.data_ptr(), _scalar(input_min), _scalar(input_max),
+             _scalar(filter_min), _scalar(filter_max), out.data_ptr(), ws.data_ptr(), ws.numel(), dbg_ptr,
+             dev.index if dev.index is not None else torch.cuda.current_device(), C.c_void_p(stream))
+    raise_for_status(st, "ApproxConv2D", _cuda_detail() if st == 100 else "")
+    if debug:
+        return out, dbg_t
+    return out
+
+
+def approx_conv2d_with_min_max_vars(input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
+                                    mul_map_file, padding, explicit_paddings=(), data_format="NHWC",
+                                    dilations=(1, 1, 1, 1), name=None, out=None, debug=False):
+    """Forward pass of `ApproxConv2DWithMinMaxVars`.
+
+    input [N,H,W,C] and filter [KH,KW,C,Cout] are fp32 CUDA tensors; the four min/max values are
+    host scalars (Python floats or 0-d tensors); `mul_map_file` is the raw uint16[65536] table file
+    ('' = exact products) or a `Table`.  Returns the fp32 output [N,OH,OW,Cout]; with `debug=True`
+    also the quantised operands and the int32 accumulators."""
+    return _forward(False, input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
+                    mul_map_file, padding, list(explicit_paddings), data_format, list(dilations), out, debug)
+
+
+def approx_depthwise_conv2d_with_min_max_vars(input, filter, input_min, input_max, filter_min, filter_max, strides,
+                                              num_bits, mul_map_file, padding, explicit_paddings=(),
+                                              data_format="NHWC", dilations=(1, 1, 1, 1), name=None, out=None,
+                                              debug=False):
+    """Depthwise variant: filter [KH,KW,C,mult] (DepthwiseConv2dNative layout), output [N,OH,OW,C*mult]."""
+    return _forward(True, input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
+                    mul_map_file, padding, list(explicit_paddings), data_format, list(dilations), out, debug)
+
+
+def launch_count():
+    """Kernels launched by libaxconv in this process so far."""
+    return int(_lib.load().axc_launch_count())
