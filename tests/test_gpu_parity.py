@@ -1,9 +1,12 @@
 """GPU: the CUDA path, called through the C ABI (ctypes -> libaxconv.so), against the CPU checker.
 
-Bars: quantised uint8 operands and int32 accumulators bit for bit; fp32 output within 1e-6 of the
-checker's epilogue on the exact integer sum, and within 1e-5 of the reference-order fp32 result
-wherever the reference's fp32 running total is itself exact (K <= 256) - both measured with the
-reference's own metric max|out - ref| / max|ref| (tf2/test/test_table_approx_conv_2d.py:62)."""
+Bars: quantised uint8 operands and int32 accumulators bit for bit.  The fp32 output is compared
+ - bit for bit with the checker's epilogue applied to the exact integer sum (the kernels add the patch
+   and filter sums in the reference's order and round every operation separately), and
+ - with the reference-order fp32 result (fp32 running total): bit for bit while that running total is
+   itself exact (K <= 256), else within the residual the reference's own rounding leaves, and in any
+   case reported with the reference's metric max|out - ref| / max|ref|
+   (tf2/test/test_table_approx_conv_2d.py:62) against the stated tolerance 1e-5."""
 import numpy as np
 import pytest
 
@@ -12,7 +15,6 @@ from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
 
-TOL_EXACT = 1e-6   # vs. the epilogue applied to the exact integer sum
 TOL_REF = 1e-5     # vs. the reference-order fp32 arithmetic (north-star tolerance)
 
 
@@ -51,8 +53,9 @@ def check_dense(ax, lut, x, f, mm, stride=(1, 1), dil=(1, 1), pad="SAME"):
     assert np.array_equal(dbg["qinput"], ref["qinput"])
     assert np.array_equal(dbg["qfilter"], ref["qfilter"])
     assert np.array_equal(dbg["acc"], ref["acc"])
-    assert linf(y, ref["out_exact"]) < TOL_EXACT
+    assert np.array_equal(y.view(np.uint32), ref["out_exact"].view(np.uint32))
     if kh * kw * c <= 256:
+        assert np.array_equal(y.view(np.uint32), ref["out_ref"].view(np.uint32))
         assert linf(y, ref["out_ref"]) < TOL_REF
     return y, ref
 
@@ -67,20 +70,22 @@ def test_golden_dense(ax, golden, case):
     assert np.array_equal(dbg["acc"], golden["aux"][name + "_acc"])
     assert np.array_equal(dbg["qinput"], golden["aux"][name + "_qinput"])
     assert np.array_equal(dbg["qfilter"], golden["aux"][name + "_qfilter"])
-    assert linf(y, golden["aux"][name + "_out_exact"]) < TOL_EXACT
+    exact = golden["aux"][name + "_out_exact"]
+    assert np.array_equal(y.view(np.uint32), exact.view(np.uint32))
     want = golden["ref"][name]   # output of the reference's own CPU kernels
     if kh * kw * ishape[3] <= 256:
-        assert linf(y, want) < TOL_REF
+        assert np.array_equal(y.view(np.uint32), want.view(np.uint32))
     else:
-        # K > 256: the reference's fp32 running total rounds; the residual is its rounding, not ours
-        exact = golden["aux"][name + "_out_exact"]
-        assert linf(y, want) <= linf(exact, want) + TOL_EXACT
+        # K > 256: the reference's fp32 running total rounds (partial sums pass 2^24); what is left is
+        # its rounding of the integer sum, not a difference in the operands or the epilogue
+        assert linf(y, want) == linf(exact, want) and linf(y, want) < 1e-4
 
 
 def test_reference_recipe(ax, golden):
     """tf2/test/test_table_approx_conv_2d.py: exact table, fake-quantised [0,1] operands, SAME, 8x8 window."""
     xq, fq = cases.recipe_inputs()
     y, _ = run_dense(ax, ax.exact_table(), xq, fq, (0.0, 1.0, 0.0, 1.0), (1, 1), (1, 1), "SAME")
+    assert np.array_equal(y.view(np.uint32), golden["ref"]["recipe"].view(np.uint32))
     assert linf(y, golden["ref"]["recipe"]) < TOL_REF
 
 
@@ -151,8 +156,8 @@ def test_non_symmetric_table_pins_operand_order(ax):
     x = np.full((1, 3, 3, 4), 0.5, np.float32)
     f = np.full((1, 1, 4, 2), 0.25, np.float32)
     y, dbg = run_dense(ax, lut.reshape(-1), x, f, (0.0, 1.0, 0.0, 1.0), (1, 1), (1, 1), "SAME")
-    qa = int(dbg["qinput"][0, 0, 0, 0])
-    assert qa == 128 and int(dbg["qfilter"][0, 0]) == 64
+    qa, qb = int(dbg["qinput"][0, 0, 0, 0]), int(dbg["qfilter"][0, 0])
+    assert qa in (127, 128) and qb in (63, 64) and qa != qb
     assert (dbg["acc"] == 4 * qa).all()
 
 
@@ -253,7 +258,7 @@ def test_config2_full_size_checksum(ax, tspec):
     xs = x[37:39].cpu().numpy()
     ref = O.conv2d(O.desc(2, 56, 56, 64, 3, 3, 64), lut, xs, f.cpu().numpy(), *mm, want=("acc", "out_exact"))
     assert np.array_equal(dbg["acc"][37:39].cpu().numpy(), ref["acc"])
-    assert linf(y[37:39].cpu().numpy(), ref["out_exact"]) < TOL_EXACT
+    assert np.array_equal(y[37:39].cpu().numpy().view(np.uint32), ref["out_exact"].view(np.uint32))
 
 
 def test_exact_table_equals_integer_convolution_full_size(ax):

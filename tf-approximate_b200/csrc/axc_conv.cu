@@ -123,27 +123,24 @@ __global__ void filter_prep_kernel(const float *__restrict__ filter, int K, int 
     prog[idx] = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// Per output channel fp32 sum of the filter over (kh, kw, c)
-// (tf2/src/approx_nn_conv_kernels.cpp:300-306).  Block = 32 channels x 8 K-slices; each
-// thread adds its slice in l order, the slices are combined in slice order.
+// Per output channel fp32 sum of the filter over (kh, kw, c), added in l order like the
+// reference's fused form (tf2/src/approx_nn_conv_kernels.cpp:187-197; the Eigen reduction of
+// :300-306 leaves the order open).  One thread per channel; loads are batched, adds are serial.
 __global__ void filter_sum_kernel(const float *__restrict__ filter, int K, int Cout, float *__restrict__ bsum)
 {
-    __shared__ float part[8][32];
-    const int j = blockIdx.x * 32 + threadIdx.x;
-    const int s = threadIdx.y;
-    const int per = (K + 7) / 8;
-    const int l0 = s * per, l1 = min(K, l0 + per);
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= Cout) return;
     float acc = 0.0f;
-    if (j < Cout)
-        for (int l = l0; l < l1; ++l) acc = __fadd_rn(acc, filter[(size_t)l * Cout + j]);
-    part[s][threadIdx.x] = acc;
-    __syncthreads();
-    if (s == 0 && j < Cout) {
-        float t = part[0][threadIdx.x];
+    int l = 0;
+    for (; l + 8 <= K; l += 8) {
+        float v[8];
 #pragma unroll
-        for (int i = 1; i < 8; ++i) t = __fadd_rn(t, part[i][threadIdx.x]);
-        bsum[j] = t;
+        for (int e = 0; e < 8; ++e) v[e] = __ldg(filter + (size_t)(l + e) * Cout + j);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc = __fadd_rn(acc, v[e]);
     }
+    for (; l < K; ++l) acc = __fadd_rn(acc, __ldg(filter + (size_t)l * Cout + j));
+    bsum[j] = acc;
 }
 
 // Element-wise quantised copy of the input, for the parity taps only.
@@ -169,6 +166,8 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
     constexpr int PIX_SLOTS = (TM / 4) / kWarps;       // pixel groups a loader thread visits per K-quad half
     constexpr int A_ITERS = (kLQ / 8) * PIX_SLOTS;     // activation quads per thread per chunk
     constexpr int W_ITERS = (kLQ * TN) / kThreads;     // program quads per thread per chunk
+    constexpr int SUM_WARPS = TM / 32;                 // warps that carry the patch sums of one chunk
+    constexpr int SUM_GROUPS = kWarps / SUM_WARPS;
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const unsigned dyn0 = (unsigned)__cvta_generic_to_shared(smem_raw);
@@ -233,7 +232,6 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
         // per-thread loader coordinates: pixel slots and their geometry
         long long pbase[PIX_SLOTS];
         int piy[PIX_SLOTS], pix[PIX_SLOTS];
-        float asum[PIX_SLOTS];
 #pragma unroll
         for (int s = 0; s < PIX_SLOTS; ++s) {
             const int p = (s * kWarps + warp) * 4 + p_lo;
@@ -243,7 +241,6 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
             asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tx) : "r"(sPixX + p * 4));
             piy[s] = int(ty);
             pix[s] = int(tx);
-            asum[s] = 0.0f;
         }
 
         int acc[kPixPerLane];
@@ -313,7 +310,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
             }
         };
 
-        // Quantise the staged taps of chunk `ch`, add them to the patch sums and publish the tiles.
+        // Quantise the staged taps of chunk `ch` and publish the tiles.
         // A tap with l >= K stores byte 0: with the K-tail program word it addresses the zero word.
         auto store_chunk = [&](int ch, int buf) {
             const int k0 = ch * kKC;
@@ -325,7 +322,6 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
                     const int l0 = k0 + lq * 4;
                     const int p = (s * kWarps + warp) * 4 + p_lo;
                     const float4 v = a_stage[h * PIX_SLOTS + s];
-                    asum[s] = __fadd_rn(asum[s], __fadd_rn(__fadd_rn(v.x, v.y), __fadd_rn(v.z, v.w)));
                     uint32_t packed = 0;
                     if (l0 + 0 < P.K) packed |= quantize_u8(v.x, P.in_off, P.in_inv);
                     if (l0 + 1 < P.K) packed |= quantize_u8(v.y, P.in_off, P.in_inv) << 8;
@@ -340,6 +336,67 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
             }
         };
 
+        // Patch sums (the reference's outCoeffs, tf2/src/approx_nn_conv_kernels.cpp:294): one thread per
+        // pixel adds the raw taps of chunk `ch` in l order, so the fp32 sum has the reference's rounding.
+        // The running value lives in shared memory; successive chunks are taken by different warps.
+        auto patch_sum_chunk = [&](int ch) {
+            const int p = (warp % SUM_WARPS) * 32 + lane;
+            long long base;
+            unsigned ty, tx;
+            asm volatile("ld.shared.u64 %0, [%1];" : "=l"(base) : "r"(sPixBase + p * 8));
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(ty) : "r"(sPixY + p * 4));
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tx) : "r"(sPixX + p * 4));
+            const int iy0 = int(ty), ix0 = int(tx);
+            float sum = ch == 0 ? 0.0f : lds_f32(sAsum + p * 4);
+            const int l_begin = ch * kKC;
+            const int l_end = min(P.K, l_begin + kKC);
+            int tap = l_begin / P.C;
+            int c = l_begin - tap * P.C;
+            int ky = tap / P.KW;
+            int kx = tap - ky * P.KW;
+            if (P.vec_ok) {
+                for (int l = l_begin; l < l_end; l += 16) {
+                    float4 v[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        v[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (l + 4 * e < l_end) {
+                            const int iy = iy0 + ky * P.dh, ix = ix0 + kx * P.dw;
+                            if (iy >= 0 && iy < P.H && ix >= 0 && ix < P.W)
+                                v[e] = __ldg(reinterpret_cast<const float4 *>(
+                                    P.input + base + ((long long)(ky * P.dh) * P.W + kx * P.dw) * P.C + c));
+                            c += 4;
+                            if (c >= P.C) { c = 0; if (++kx >= P.KW) { kx = 0; ++ky; } }
+                        }
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        sum = __fadd_rn(sum, v[e].x);
+                        sum = __fadd_rn(sum, v[e].y);
+                        sum = __fadd_rn(sum, v[e].z);
+                        sum = __fadd_rn(sum, v[e].w);
+                    }
+                }
+            } else {
+                for (int l = l_begin; l < l_end; l += 4) {
+                    float v[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        v[e] = 0.f;
+                        if (l + e < l_end) {
+                            const int iy = iy0 + ky * P.dh, ix = ix0 + kx * P.dw;
+                            if (iy >= 0 && iy < P.H && ix >= 0 && ix < P.W)
+                                v[e] = __ldg(P.input + base + ((long long)(ky * P.dh) * P.W + kx * P.dw) * P.C + c);
+                            if (++c >= P.C) { c = 0; if (++kx >= P.KW) { kx = 0; ++ky; } }
+                        }
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) sum = __fadd_rn(sum, v[e]);
+                }
+            }
+            sts_f32(sAsum + p * 4, sum);
+        };
+
         load_chunk(0);
         store_chunk(0, 0);
         __syncthreads();
@@ -348,6 +405,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
             const int buf = ch & 1;
             const bool more = ch + 1 < n_chunks;
             if (more) load_chunk(ch + 1);
+            if (warp / SUM_WARPS == ch % SUM_GROUPS) patch_sum_chunk(ch);
 
             const unsigned aBase = sA + buf * A_BYTES + wm * kPixPerLane * 4;
             const unsigned wBase = sW + buf * W_BYTES + (wn * 32 + lane) * 16;
@@ -373,17 +431,6 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
             if (more) store_chunk(ch + 1, buf ^ 1);
             __syncthreads();
         }
-
-        // patch sums: combine the 8 lanes that share a pixel, in a fixed order
-#pragma unroll
-        for (int s = 0; s < PIX_SLOTS; ++s) {
-            float v = asum[s];
-            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
-            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
-            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
-            if (lq_lo == 0) sts_f32(sAsum + ((s * kWarps + warp) * 4 + p_lo) * 4, v);
-        }
-        __syncthreads();
 
         // ---- dequantisation: ((S*s1s2 + m2*aSum) + m1*bSum) - K*m1m2 -----------------
         const int j = j0 + wn * 32 + lane;
@@ -450,7 +497,7 @@ int launch_dense(const uint16_t *lut_dev, const Geom &g, const Quant &q, const f
         filter_prep_kernel<<<blocks, 256, 0, stream>>>(filter, g.K, g.Cout, q.f_off, q.f_inv, prog,
                                                        dbg ? dbg->qfilter : nullptr, status);
         AXC_CUDA(cudaGetLastError());
-        filter_sum_kernel<<<unsigned((g.Cout + 31) / 32), dim3(32, 8), 0, stream>>>(filter, g.K, g.Cout, bsum);
+        filter_sum_kernel<<<unsigned((g.Cout + 31) / 32), 32, 0, stream>>>(filter, g.K, g.Cout, bsum);
         AXC_CUDA(cudaGetLastError());
         count_launch(2);
     }
