@@ -1,0 +1,354 @@
+"""Benchmark of the table-driven convolution path on the ResNet-50-shaped workload.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W]            this build (CUDA, one process per GPU)
+  python bench.py --impl reference [--steps K] [--warmup W]      the reference's CPU kernels on host cores
+
+A step is one forward pass over one batch: the 53 convolutions of an ImageNet-shaped ResNet-50
+(every one a table convolution with the truncated truth table, batch 256 per GPU) plus the ReLU /
+residual / max-pool glue.  `value` is table MACs per second of the whole job with the batch already in
+HBM; `e2e` repeats the measurement with the batch in pinned host memory, copied in every step, and the
+result copied back.  Prints one JSON line on rank 0.
+"""
+import argparse
+import json
+import multiprocessing as mp
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+CFG_INDEX = 4          # seeds follow 1000+cfg (input), 2000+100*cfg+layer (filters)
+SM_COUNT = 148
+LOOKUPS_PER_CLK_PER_SM = 32   # one 32-bit shared-memory bank transaction per lane per clock
+
+
+def build_params(kind):
+    from tf_approximate_b200 import workloads as W
+    import tf_approximate_b200 as ax
+    net = W.Network(kind)
+    filters = W.make_filters(net.convs, 2000 + 100 * CFG_INDEX)
+    return net, filters, ax.truncated_table()
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the reference's CPU kernels (oracle/_ref) or the C restatement
+# ------------------------------------------------------------------------------------------------
+def _cpu_worker(args):
+    """One image through all convolutions on one host core.  Returns (seconds, macs, kind)."""
+    kind, seed = args
+    os.environ["OMP_NUM_THREADS"] = "1"
+    from tf_approximate_b200 import workloads as W
+    from oracle import oracle as O
+    import tf_approximate_b200 as ax
+    net, filters, lut = build_params(kind)
+    x = W.make_input(1, net.hw, net.in_channels, seed)
+    use_ref = O.ref_available()
+    tmp = None
+    if use_ref:
+        tmp = tempfile.NamedTemporaryFile(suffix=".bin", delete=False)
+        tmp.close()
+        ax.write_table(tmp.name, lut)
+        op = O.RefOp(tmp.name)
+    conv_time = [0.0]
+
+    def conv(spec, table_index, xx, f, lo, hi, flo, fhi):
+        lo, hi = float(xx.min()), float(xx.max())   # per-call range: a single image calibrates itself
+        d = O.desc(xx.shape[0], xx.shape[1], xx.shape[2], xx.shape[3], f.shape[0], f.shape[1], f.shape[3],
+                   (spec.stride, spec.stride), (1, 1), "SAME")
+        t0 = time.perf_counter()
+        if use_ref:
+            y = op.conv2d(d, xx, f, lo, hi, flo, fhi)
+        else:
+            y = O.conv2d(d, lut, xx, f, lo, hi, flo, fhi, want=("out_ref",), nthreads=1)["out_ref"]
+        conv_time[0] += time.perf_counter() - t0
+        return y
+
+    runner = W.CpuRunner(net, filters, [(0.0, 0.0)] * len(filters), conv)
+    t0 = time.perf_counter()
+    runner.forward(x)
+    dt = time.perf_counter() - t0
+    if tmp is not None:
+        op.close()
+        os.unlink(tmp.name)
+    return dt, net.macs_per_image(), "reference" if use_ref else "port"
+
+
+def run_cpu(kind, steps, warmup, workers=None):
+    """Each step: `workers` images, one per process, through the reference's single-threaded kernels."""
+    workers = workers or max(1, min(os.cpu_count() or 1, 32))
+    ctx = mp.get_context("spawn")
+    times, macs, impl_kind = [], 0, "port"
+    with ctx.Pool(workers) as pool:
+        for s in range(warmup + steps):
+            res = pool.map(_cpu_worker, [(kind, 1000 + CFG_INDEX + 17 * i) for i in range(workers)])
+            if s >= warmup:
+                times.append(max(r[0] for r in res))   # the workers run side by side: slowest forward pass
+            macs = sum(r[1] for r in res)
+            impl_kind = res[0][2]
+    sec = sum(times) / len(times)
+    return {"value": macs / sec, "unit": "LUT-MAC/s", "cores": workers, "kind": impl_kind,
+            "sample": "%d images of the same ResNet-50 forward per step, one per process (the reference's "
+                      "kernels are single-threaded)" % workers,
+            "seconds_per_step": sec, "images_per_s": workers / sec, "macs_per_step": macs}
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile(suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=f,
+                                         stderr=subprocess.DEVNULL)
+            f.close()
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, reasons, smax = [], set(), None
+        try:
+            for line in open(self.path):
+                p = [v.strip() for v in line.split(",")]
+                if len(p) < 9:
+                    continue
+                try:
+                    sm.append(float(p[1]))
+                    smax = float(p[2])
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            busy = [v for v in sm if v >= 0.5 * max(sm)]
+            out.update(sm_mhz=statistics.median(busy), sm_max_mhz=smax, reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ------------------------------------------------------------------------------------------------
+# this build
+# ------------------------------------------------------------------------------------------------
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    import tf_approximate_b200 as ax
+    from tf_approximate_b200 import workloads as W
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    net, filters, lut = build_params(args.workload)
+    batch = args.batch
+    runner = W.GpuRunner(net, [lut], filters, dev)
+    x_host = torch.from_numpy(W.make_input(batch, net.hw, net.in_channels, 1000 + CFG_INDEX + rank)).pin_memory()
+    x = x_host.to(dev)
+
+    # Frozen per-layer input ranges: calibrated on rank 0's batch, identical on every rank, so that
+    # no collective sits on the compute path.
+    if rank == 0:
+        runner.calibrate(x)
+    if world > 1:
+        box = [runner.in_ranges]
+        dist.broadcast_object_list(box, src=0)
+        runner.in_ranges = box[0]
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        y = runner.forward(x)
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    # ---- timed region 1: batch resident in HBM --------------------------------------------------
+    runner.conv_events = []
+    launches0 = ax.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        y = runner.forward(x)
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    launches = ax.launch_count() - launches0
+    conv_events, runner.conv_events = runner.conv_events, None
+
+    # ---- timed region 2: end to end from pinned host memory ----------------------------------------
+    y_host = torch.empty(tuple(y.shape), dtype=y.dtype).pin_memory()
+    x_dev = torch.empty_like(x)
+    for _ in range(2):
+        x_dev.copy_(x_host, non_blocking=True)
+        y_host.copy_(runner.forward(x_dev), non_blocking=True)
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+        x_dev.copy_(x_host, non_blocking=True)
+        y_host.copy_(runner.forward(x_dev), non_blocking=True)
+    f1.record()
+    barrier()
+    ms_e2e = f0.elapsed_time(f1)
+    clocks = sampler.stop() if rank == 0 else None
+
+    t = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, ms_e2e = float(t[0]), float(t[1])
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    macs_step = net.macs_per_image() * batch * world
+    ms_step = ms_total / args.steps
+    value = macs_step / (ms_step * 1e-3)
+
+    # per-layer conv time on rank 0 (filter preparation + main kernel), from the same timed region
+    per_layer = {}
+    for i, a, b in conv_events:
+        per_layer[i] = per_layer.get(i, 0.0) + a.elapsed_time(b)
+    dense_ms = sum(v for i, v in per_layer.items() if not net.convs[i][0].depthwise) / args.steps
+    dense_macs = sum(W.conv_macs(s, h, batch) for s, h in net.convs if not s.depthwise)
+    dense_launches = sum(1 for s, _ in net.convs if not s.depthwise)
+    io_bytes = sum(W.conv_io_bytes(s, h, batch) for s, h in net.convs if not s.depthwise)
+    sm_mhz = clocks["sm_mhz"] or 1965.0
+    achieved = dense_macs / (dense_ms * 1e-3)
+    peak = SM_COUNT * LOOKUPS_PER_CLK_PER_SM * sm_mhz * 1e6
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    traffic = None
+    try:
+        traffic = json.load(open(os.path.join(ROOT, "profiles", "dense_kernel_traffic.json"))).get("dram_bytes_per_launch_resnet50_bs256")
+    except Exception:
+        pass
+    slowest = sorted(per_layer.items(), key=lambda kv: -kv[1])[:3]
+    roofline = {
+        "kernel": "dense_kernel (table convolution, %d launches per step)" % dense_launches,
+        "bound": "smem_lookup",
+        "achieved": achieved / 1e9, "peak": peak / 1e9, "unit": "GLUT-MAC/s", "frac": achieved / peak,
+        "peak_basis": "148 SMs x 32 shared-memory lookups/clk x %.0f MHz (median SM clock sampled during this run); "
+                      "%.0f GLUT-MAC/s at the 1965 MHz maximum" % (sm_mhz, SM_COUNT * 32 * 1965e6 / 1e9),
+        "units_per_launch": dense_macs / dense_launches, "ms_per_launch": dense_ms / dense_launches,
+        "traffic": traffic,
+        "hbm": {"algorithmic_bytes_per_step": io_bytes, "achieved_gbs": io_bytes / (dense_ms * 1e-3) / 1e9,
+                "peak_gbs": hbm_peak, "frac": io_bytes / (dense_ms * 1e-3) / 1e9 / hbm_peak,
+                "peak_source": "measured" if "hbm_gbs" in peaks else "fallback"},
+        "slowest_layers_ms": [[net.convs[i][0].name, v / args.steps] for i, v in slowest],
+    }
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        cpu = run_cpu(args.workload, 1, 0)
+
+    in_bytes = x_host.numel() * 4
+    out_bytes = y_host.numel() * 4
+    ms_e2e_step = ms_e2e / args.steps
+    line = {
+        "metric": "lut_macs_per_s", "value": value, "unit": "LUT-MAC/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "u8 operands, u16 table entries, i32 accumulate", "data": "synthetic",
+        "config": {"workload": "resnet50_approx_conv (BASELINE config 4): ImageNet-shaped ResNet-50 v1.5, 53 table "
+                               "convolutions, truncated truth table, random He-init filters, frozen per-layer ranges",
+                   "batch_per_gpu": batch, "global_batch": batch * world, "input": "224x224x3 fp32 NHWC",
+                   "parallelism": "dp%d (batch shards, per-GPU table replica, no collective in the step)" % world,
+                   "l2": "not flushed: every layer's input and output are larger than the 126 MB L2"},
+        "images_per_s": batch * world / (ms_step * 1e-3),
+        "conv_only_lut_macs_per_s_rank0": achieved,
+        "e2e": {"value": macs_step / (ms_e2e_step * 1e-3), "unit": "LUT-MAC/s", "ms_per_step": ms_e2e_step,
+                "images_per_s": batch * world / (ms_e2e_step * 1e-3),
+                "h2d_bytes_per_step": in_bytes * world, "d2h_bytes_per_step": out_bytes * world},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": roofline,
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    r = run_cpu(args.workload, args.steps, max(args.warmup, 0))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    line = {
+        "impl": "reference", "metric": "lut_macs_per_s", "value": r["value"], "unit": "LUT-MAC/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["seconds_per_step"] * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u8 operands, u16 table entries, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": "resnet50_approx_conv (BASELINE config 4), bounded sample: %s" % r["sample"]},
+        "images_per_s": r["images_per_s"],
+        "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": r["value"], "unit": "LUT-MAC/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=256, help="images per GPU")
+    ap.add_argument("--workload", default="resnet50", choices=["resnet50", "resnet20", "mobilenet_stack"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()
