@@ -315,6 +315,41 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_layer(args):
+    """One convolution, repeated: `--layer N,H,W,C,K,Cout,stride[,dw]` (SAME padding, seeded inputs as in the
+    single-layer configurations: input uniform[-1,1], filter normal(0,0.1), input range [-1,1])."""
+    import torch
+    import tf_approximate_b200 as ax
+    v = args.layer.split(",")
+    n, h, w, c, k, cout, stride = (int(t) for t in v[:7])
+    dw = len(v) > 7 and v[7] == "dw"
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(1002)
+    x = torch.rand((n, h, w, c), device=dev, generator=g) * 2 - 1
+    f = torch.randn((k, k, c, 1 if dw else cout), device=dev, generator=g) * 0.1
+    lut = {"truncated": ax.truncated_table(), "noisy": ax.noisy_table(3202), "exact": ax.exact_table()}[args.table]
+    table = ax.Table(array=lut)
+    mm = (-1.0, 1.0, float(f.min()), float(f.max()))
+    fn = ax.approx_depthwise_conv2d_with_min_max_vars if dw else ax.approx_conv2d_with_min_max_vars
+    out = None
+    for _ in range(args.warmup):
+        out = fn(x, f, *mm, [1, stride, stride, 1], 8, table, "SAME", out=out)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        out = fn(x, f, *mm, [1, stride, stride, 1], 8, table, "SAME", out=out)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    oh, ow = -(-h // stride), -(-w // stride)
+    macs = n * oh * ow * k * k * c * (1 if dw else cout)
+    io = 4 * (x.numel() + out.numel() + f.numel())
+    print(json.dumps({"layer": args.layer, "table": args.table, "ms": ms, "lut_macs": macs,
+                      "glut_macs_per_s": macs / ms / 1e6, "lookups_per_clk_per_sm_at_1965MHz": macs / (ms * 1e-3) / (SM_COUNT * 1965e6),
+                      "io_gbs": io / ms / 1e6}))
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -343,8 +378,12 @@ def main():
     ap.add_argument("--batch", type=int, default=256, help="images per GPU")
     ap.add_argument("--workload", default="resnet50", choices=["resnet50", "resnet20", "mobilenet_stack"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layer", default=None, help="time one layer instead: N,H,W,C,K,Cout,stride[,dw]")
+    ap.add_argument("--table", default="truncated", choices=["truncated", "noisy", "exact"])
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.layer:
+        run_layer(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)
