@@ -9,8 +9,10 @@
 #include <vector>
 
 #include "axc_internal.h"
+#include "axc_sched.h"
 
 struct axc_table {
+    unsigned uid;
     std::vector<uint16_t> host;  // 65536 entries, index (a << 8) | b
     std::mutex mu;
     std::vector<uint16_t *> dev;  // per-device replica, lazily created
@@ -20,6 +22,10 @@ namespace axc {
 
 static thread_local int g_last_cuda_error = 0;
 static std::atomic<uint64_t> g_launches{0};
+static std::atomic<unsigned> g_table_uid{1};
+
+unsigned table_uid(const axc_table *t) { return t->uid; }
+void stamp(axc_table *t) { t->uid = g_table_uid.fetch_add(1); }
 
 int cuda_failed(cudaError_t e)
 {
@@ -141,6 +147,8 @@ Workspace dense_workspace(int K, int Cout)
     return w;
 }
 
+size_t dense_workspace_total(int K, int Cout) { return plan_layout(K, Cout).total + dense_workspace(K, Cout).total; }
+
 Workspace depthwise_workspace(int KHW, int C, int mult)
 {
     Workspace w;
@@ -220,8 +228,8 @@ static int forward(bool depthwise, axc_table *table, const axc_conv_desc *desc, 
     const long long out_c = depthwise ? (long long)g.C * g.Cout : g.Cout;
     if (g.M * out_c == 0) return AXC_OK;  // empty output: nothing to do
     if (!input || !filter || !output) return AXC_INVALID_ARGUMENT;
-    const Workspace ws = depthwise ? depthwise_workspace(g.K, g.C, g.Cout) : dense_workspace(g.K, g.Cout);
-    if (!workspace || workspace_bytes < ws.total) return AXC_INTERNAL;
+    const size_t ws_total = depthwise ? depthwise_workspace(g.K, g.C, g.Cout).total : dense_workspace_total(g.K, g.Cout);
+    if (!workspace || workspace_bytes < ws_total) return AXC_INTERNAL;
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return AXC_INVALID_ARGUMENT;
 
     int status = AXC_OK;
@@ -233,7 +241,7 @@ static int forward(bool depthwise, axc_table *table, const axc_conv_desc *desc, 
     if (prev != device) AXC_CUDA(cudaSetDevice(device));
     const Quant q = make_quant(in_min, in_max, f_min, f_max);
     rc = depthwise ? launch_depthwise(lut, g, q, input, filter, output, workspace, dbg, device, cudaStream_t(stream))
-                   : launch_dense(lut, g, q, input, filter, output, workspace, dbg, device, cudaStream_t(stream));
+                   : launch_dense(lut, table_uid(table), g, q, input, filter, output, workspace, dbg, device, cudaStream_t(stream));
     if (prev != device) cudaSetDevice(prev);
     return rc;
 }
@@ -248,6 +256,7 @@ int axc_table_create_from_memory(const uint16_t *lut65536, axc_table **out)
     axc_table *t = new (std::nothrow) axc_table;
     if (!t) return AXC_INTERNAL;
     t->host.assign(lut65536, lut65536 + 65536);
+    axc::stamp(t);
     *out = t;
     return AXC_OK;
 }
@@ -259,6 +268,7 @@ int axc_table_create_exact(axc_table **out)
     if (!t) return AXC_INTERNAL;
     t->host.resize(65536);
     for (uint32_t i = 0; i < 65536u; ++i) t->host[i] = uint16_t((i >> 8) * (i & 0xFFu));
+    axc::stamp(t);
     *out = t;
     return AXC_OK;
 }
@@ -284,6 +294,7 @@ int axc_table_create_from_file(const char *path, int num_bits, axc_table **out)
         delete t;
         return AXC_INVALID_ARGUMENT;
     }
+    axc::stamp(t);
     *out = t;
     return AXC_OK;
 }
@@ -343,7 +354,7 @@ int axc_conv2d_workspace_bytes(const axc_conv_desc *desc, size_t *bytes)
     axc::Geom g;
     int rc = axc::resolve_geometry(desc, false, &g);
     if (rc) return rc;
-    *bytes = axc::dense_workspace(g.K, g.Cout).total;
+    *bytes = axc::dense_workspace_total(g.K, g.Cout);
     return AXC_OK;
 }
 

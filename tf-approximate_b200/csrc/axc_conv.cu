@@ -17,8 +17,10 @@
 // {2*(b&127), 0, 1+(b>>7), 0} and a packed activation word, so a table MAC costs
 // PRMT + LDS.U16 + IADD.
 #include <cstdio>
+#include <cstdlib>
 
 #include "axc_internal.h"
+#include "axc_sched.h"
 
 namespace axc {
 
@@ -50,6 +52,7 @@ struct DenseParams {
     long long tiles_total;
     float in_off, in_inv, s1s2, m1, m2, km1m2;
     int vec_ok;            // C % 4 == 0 and 16-byte aligned input
+    const int *gate;       // when set: run only if *gate != 0 (the scheduled kernel handed the call over)
 };
 
 __device__ __forceinline__ unsigned quantize_u8(float x, float off, float inv)
@@ -101,8 +104,10 @@ __device__ __forceinline__ float lds_f32(unsigned addr)
 // (one uint4 per (l/4, j): the four words of l = 4*lq .. 4*lq+3) and, optionally, the plain
 // uint8 matrix.  Weight quantiser as tf2/src/approx_nn_conv_kernels.cpp:243.
 __global__ void filter_prep_kernel(const float *__restrict__ filter, int K, int Cout, float f_off, float f_inv,
-                                   uint4 *__restrict__ prog, uint8_t *__restrict__ qfilter, int *status)
+                                   uint4 *__restrict__ prog, uint8_t *__restrict__ qfilter, int *status,
+                                   const int *gate)
 {
+    if (gate && *gate == 0) return;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx == 0) *status = 0;
     const int kq = (K + 3) / 4;
@@ -126,8 +131,10 @@ __global__ void filter_prep_kernel(const float *__restrict__ filter, int K, int 
 // Per output channel fp32 sum of the filter over (kh, kw, c), added in l order like the
 // reference's fused form (tf2/src/approx_nn_conv_kernels.cpp:187-197; the Eigen reduction of
 // :300-306 leaves the order open).  One thread per channel; loads are batched, adds are serial.
-__global__ void filter_sum_kernel(const float *__restrict__ filter, int K, int Cout, float *__restrict__ bsum)
+__global__ void filter_sum_kernel(const float *__restrict__ filter, int K, int Cout, float *__restrict__ bsum,
+                                  const int *gate)
 {
+    if (gate && *gate == 0) return;
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= Cout) return;
     float acc = 0.0f;
@@ -170,6 +177,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
     constexpr int SUM_GROUPS = kWarps / SUM_WARPS;
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    if (P.gate && *P.gate == 0) return;
     const unsigned dyn0 = (unsigned)__cvta_generic_to_shared(smem_raw);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
@@ -478,29 +486,36 @@ int launch_dense_variant(const DenseParams &P, const DeviceInfo &di, cudaStream_
 
 }  // namespace
 
-int launch_dense(const uint16_t *lut_dev, const Geom &g, const Quant &q, const float *input, const float *filter,
-                 float *output, void *workspace, const axc_debug_out *dbg, int device, cudaStream_t stream)
+// 0 = bank-scheduled kernel with the common-K kernel as its device-side fallback (default),
+// 1 = common-K kernel only.  Read once from AXC_DENSE_VARIANT.
+static int dense_variant()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("AXC_DENSE_VARIANT");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v;
+}
+
+int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const Quant &q, const float *input,
+                 const float *filter, float *output, void *workspace, const axc_debug_out *dbg, int device,
+                 cudaStream_t stream)
 {
     DeviceInfo di;
     int rc = device_info(device, &di);
     if (rc) return rc;
-    if (di.max_smem_optin < int(kSmemEnd)) return AXC_INTERNAL;
+    if (di.max_smem_optin < 232448) return AXC_INTERNAL;   // the kernels are laid out for the 227 KiB of sm_100
+    const bool scheduled = dense_variant() == 0;
+    const PlanLayout L = plan_layout(g.K, g.Cout);
     const Workspace ws = dense_workspace(g.K, g.Cout);
-    unsigned char *wsb = static_cast<unsigned char *>(workspace);
+    unsigned char *plan = static_cast<unsigned char *>(workspace);
+    unsigned char *wsb = plan + L.total;
     uint4 *prog = reinterpret_cast<uint4 *>(wsb);
     float *bsum = reinterpret_cast<float *>(wsb + ws.sums_off);
     int *status = reinterpret_cast<int *>(wsb + ws.status_off);
+    const int *gate = nullptr;
 
-    {
-        const long long items = (long long)((g.K + 3) / 4) * g.Cout;
-        const unsigned blocks = unsigned((items + 255) / 256);
-        filter_prep_kernel<<<blocks, 256, 0, stream>>>(filter, g.K, g.Cout, q.f_off, q.f_inv, prog,
-                                                       dbg ? dbg->qfilter : nullptr, status);
-        AXC_CUDA(cudaGetLastError());
-        filter_sum_kernel<<<unsigned((g.Cout + 31) / 32), 32, 0, stream>>>(filter, g.K, g.Cout, bsum);
-        AXC_CUDA(cudaGetLastError());
-        count_launch(2);
-    }
     if (dbg && dbg->qinput) {
         const long long n = (long long)g.N * g.H * g.W * g.C;
         if (n > 0) {
@@ -510,11 +525,29 @@ int launch_dense(const uint16_t *lut_dev, const Geom &g, const Quant &q, const f
             count_launch();
         }
     }
+    if (scheduled) {
+        rc = launch_plan(lut_dev, table_uid, g, q, filter, plan, L, dbg ? dbg->qfilter : nullptr, stream);
+        if (rc) return rc;
+        rc = launch_dense_sched(g, q, input, output, plan, L, dbg ? dbg->acc : nullptr, di, stream);
+        if (rc) return rc;
+        gate = &reinterpret_cast<const PlanHeader *>(plan)->fallback;
+    }
+    {
+        const long long items = (long long)((g.K + 3) / 4) * g.Cout;
+        const unsigned blocks = unsigned((items + 255) / 256);
+        filter_prep_kernel<<<blocks, 256, 0, stream>>>(filter, g.K, g.Cout, q.f_off, q.f_inv, prog,
+                                                       (dbg && !scheduled) ? dbg->qfilter : nullptr, status, gate);
+        AXC_CUDA(cudaGetLastError());
+        filter_sum_kernel<<<unsigned((g.Cout + 31) / 32), 32, 0, stream>>>(filter, g.K, g.Cout, bsum, gate);
+        AXC_CUDA(cudaGetLastError());
+        count_launch(2);
+    }
 
     DenseParams P;
     P.lut = lut_dev; P.input = input; P.output = output; P.prog = prog; P.bsum = bsum;
     P.acc_out = dbg ? dbg->acc : nullptr;
     P.status = status;
+    P.gate = gate;
     P.N = g.N; P.H = g.H; P.W = g.W; P.C = g.C; P.KH = g.KH; P.KW = g.KW; P.Cout = g.Cout;
     P.sh = g.sh; P.sw = g.sw; P.dh = g.dh; P.dw = g.dw; P.ph = g.ph; P.pw = g.pw; P.OH = g.OH; P.OW = g.OW;
     P.K = g.K; P.M = g.M;

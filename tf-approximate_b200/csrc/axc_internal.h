@@ -45,6 +45,8 @@ void count_launch(int n = 1);
 
 // Device replica of a table (native [a][b] order, 65536 uint16).
 const uint16_t *table_device_ptr(axc_table *t, int device, int *status);
+// Process-unique id of a table handle (tables are immutable after creation).
+unsigned table_uid(const axc_table *t);
 
 struct DeviceInfo {
     int sm_count;
@@ -59,11 +61,12 @@ int device_info(int device, DeviceInfo *out);
 struct Workspace {
     size_t prog_bytes, sums_off, status_off, total;
 };
-Workspace dense_workspace(int K, int Cout);
+Workspace dense_workspace(int K, int Cout);      // region of the common-K kernel
+size_t dense_workspace_total(int K, int Cout);   // plan of the scheduled kernel + that region
 Workspace depthwise_workspace(int KHW, int C, int mult);
 
 // Kernel launchers (axc_conv.cu / axc_depthwise.cu).
-int launch_dense(const uint16_t *lut_dev, const Geom &g, const Quant &q, const float *input,
+int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const Quant &q, const float *input,
                  const float *filter, float *output, void *workspace, const axc_debug_out *dbg,
                  int device, cudaStream_t stream);
 int launch_depthwise(const uint16_t *lut_dev, const Geom &g, const Quant &q, const float *input,

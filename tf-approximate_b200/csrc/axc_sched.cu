@@ -1,0 +1,784 @@
+// Bank-scheduled dense table convolution for sm_100a.
+//
+// Why: with lanes = output channels and all lanes on the same K index, the 32 table lookups of a
+// warp instruction hit the 32 shared-memory banks at random (the bank of LUT[a][b] is a function of the
+// weight b alone), which costs about 2.1 wavefronts per instruction.  Integer accumulation is exact and
+// commutative, so every lane may walk its K elements in its own order.  For each group of 32 output
+// channels and each K chunk a schedule is built (once per filter, kept in the caller's workspace) in which,
+// at every step, the 32 lanes look up 32 different banks: a step is one conflict-free wavefront per pixel.
+//
+//   plan_check_kernel   quantise the filter, compare with the stored copy -> `dirty`
+//   plan_sigma_kernel   column permutation sigma of the table that spreads the weight histogram evenly
+//                       over the 32 banks (8 table columns per bank)
+//   plan_build_kernel   per (channel group, chunk): greedy edge colouring lanes x banks (banks by
+//                       remaining load, lane with most remaining work first); also the permuted table
+//                       image and the sequential per-channel filter sums
+//   dense_sched_kernel  the convolution: 16 pixels per tile, activation bytes stored 8 times side by side
+//                       so that a lane can fetch "its" K row with one conflict-free LDS.128
+//
+// Arithmetic (quantiser, table index, dequantisation) is the reference's,
+// tf2/src/approx_nn_conv_kernels.cpp:167-296; results are bit-identical to the common-K kernel.
+#include "axc_internal.h"
+#include "axc_sched.h"
+
+namespace axc {
+
+namespace {
+
+constexpr unsigned kLutBase = 65536u;          // table planes at 64 KiB and 128 KiB
+constexpr unsigned kBuf1Base = 196608u;        // activation buffer 1 starts with the zero row
+constexpr unsigned kWindowEnd = 233472u;       // 228 KiB shared window of an SM
+constexpr int kComputeWarps = 8;
+constexpr int kLoaderWarps = 4;
+constexpr int kLoaderThreads = kLoaderWarps * 32;
+constexpr int kSchedThreads = (kComputeWarps + kLoaderWarps + 1) * 32;   // + the sums warp
+constexpr int kTilePix = 16;
+
+__device__ __forceinline__ unsigned q_u8(float x, float off, float inv)
+{
+    const float v = __fadd_rn(__fmul_rn(__fsub_rn(x, off), inv), 0.5f);
+    const unsigned u = __float2uint_rz(v);
+    return u > 255u ? 255u : u;
+}
+
+// prmt.b32 with an immediate selector; a selector nibble with bit 3 set replicates the sign of the byte
+template <unsigned SEL>
+__device__ __forceinline__ unsigned prmt(unsigned a, unsigned b)
+{
+    unsigned d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "n"(SEL));
+    return d;
+}
+
+__device__ __forceinline__ unsigned lds16(unsigned addr)
+{
+    unsigned v;
+    asm("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(unsigned addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128(unsigned addr, uint4 v)
+{
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void sts8(unsigned addr, unsigned v)
+{
+    asm volatile("st.shared.u8 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void sts32(unsigned addr, unsigned v)
+{
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned lds32(unsigned addr)
+{
+    unsigned v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ int slot_bank(int s) { return ((s & 127) >> 1) & 31; }
+
+// ------------------------------------------------------------------------------------------------
+// plan_check: quantised filter vs. stored copy
+// ------------------------------------------------------------------------------------------------
+__global__ void plan_check_kernel(const float *__restrict__ filter, long long count, float f_off, float f_inv,
+                                  uint8_t *__restrict__ qf, uint8_t *__restrict__ qf_debug, PlanHeader *hdr,
+                                  PlanHeader want)
+{
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx == 0) {
+        const bool same = hdr->magic == want.magic && hdr->K == want.K && hdr->Cout == want.Cout && hdr->G == want.G &&
+                          hdr->NCH == want.NCH && hdr->KC == want.KC && hdr->sqcap == want.sqcap &&
+                          hdr->table_uid == want.table_uid && hdr->f_off_bits == want.f_off_bits &&
+                          hdr->f_inv_bits == want.f_inv_bits;
+        if (!same) atomicOr(&hdr->dirty, 1);
+        hdr->status = 0;
+    }
+    if (idx >= count) return;
+    const unsigned b = q_u8(filter[idx], f_off, f_inv);
+    if (qf[idx] != b) {
+        qf[idx] = uint8_t(b);
+        atomicOr(&hdr->dirty, 1);
+    }
+    if (qf_debug) qf_debug[idx] = uint8_t(b);
+}
+
+// ------------------------------------------------------------------------------------------------
+// plan_sigma: histogram of the quantised weights -> balanced assignment of the 256 table columns to
+// the 32 banks (largest first, into the bank with the smallest mass that still has one of its 8 slots)
+// ------------------------------------------------------------------------------------------------
+__global__ void plan_sigma_kernel(const uint8_t *__restrict__ qf, long long count, uint8_t *__restrict__ sigma,
+                                  PlanHeader *hdr, PlanHeader want)
+{
+    if (hdr->dirty == 0) return;
+    __shared__ unsigned hist[256];
+    __shared__ int value_at_rank[256];
+    __shared__ unsigned long long mass[32];
+    __shared__ int used[32];
+    const int t = threadIdx.x;
+    hist[t] = 0;
+    __syncthreads();
+    for (long long i = t; i < count; i += 256) atomicAdd(&hist[qf[i]], 1u);
+    __syncthreads();
+    {
+        const unsigned h = hist[t];
+        int rank = 0;
+        for (int u = 0; u < 256; ++u) {
+            const unsigned hu = hist[u];
+            rank += (hu > h || (hu == h && u < t)) ? 1 : 0;
+        }
+        value_at_rank[rank] = t;
+    }
+    if (t < 32) { mass[t] = 0; used[t] = 0; }
+    __syncthreads();
+    if (t < 32) {
+        for (int r = 0; r < 256; ++r) {
+            const int v = value_at_rank[r];
+            // bank with the smallest mass among those with a free slot; ties -> lowest bank
+            unsigned long long key = used[t] < 8 ? ((mass[t] << 5) | (unsigned long long)t) : ~0ull;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
+                key = other < key ? other : key;
+            }
+            const int bank = int(key & 31ull);
+            if (t == bank) {
+                const int k = used[t];
+                // the 8 slots of a bank: word bank or bank+32 of a plane row, low/high half, plane 0/1
+                const int slot = (k >> 2) * 128 + 2 * (bank + 32 * ((k >> 1) & 1)) + (k & 1);
+                sigma[v] = uint8_t(slot);
+                used[t] = k + 1;
+                mass[t] += hist[v];
+            }
+            __syncwarp();
+        }
+    }
+    if (t == 0) {
+        hdr->magic = want.magic; hdr->K = want.K; hdr->Cout = want.Cout; hdr->G = want.G; hdr->NCH = want.NCH;
+        hdr->KC = want.KC; hdr->sqcap = want.sqcap; hdr->table_uid = want.table_uid;
+        hdr->f_off_bits = want.f_off_bits; hdr->f_inv_bits = want.f_inv_bits;
+        hdr->fallback = 0;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// plan_build.  blockIdx.x < G*NCH: schedule of (group, chunk), one warp.  Then 256 blocks that write the
+// permuted table image, then ceil(Cout/32) blocks for the filter sums.
+//
+// Program word of a step:  byte0 = 2*(slot&127)  byte1 = row >> 8  byte2 = 1 + (slot>>7)  byte3 = row & 255
+// with row = 1 + (l - chunk start); an idle lane gets byte0 = 4*bank, byte2 = 3, row 0 (the zero row), which
+// addresses one of 32 zero words, one per bank.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(32) plan_build_kernel(const float *__restrict__ filter, const uint16_t *__restrict__ lut,
+                                                        unsigned char *__restrict__ plan, PlanLayout L, int K, int Cout)
+{
+    PlanHeader *hdr = reinterpret_cast<PlanHeader *>(plan);
+    if (hdr->dirty == 0) return;
+    const uint8_t *qf = plan + L.qf_off;
+    const uint8_t *sigma = plan + L.sigma_off;
+    const int lane = threadIdx.x;
+    const int n_sched = L.G * L.NCH;
+
+    if (int(blockIdx.x) >= n_sched) {
+        const int rest = int(blockIdx.x) - n_sched;
+        if (rest < 256) {
+            // table image: plane p = slot>>7 at p*65536, row a at a*256, column 2*(slot&127)
+            const int a = rest;
+            uint16_t *img = reinterpret_cast<uint16_t *>(plan + L.lut_off);
+            for (int b = lane; b < 256; b += 32) {
+                const int s = sigma[b];
+                img[((s >> 7) * 65536 + a * 256 + 2 * (s & 127)) >> 1] = lut[a * 256 + b];
+            }
+        } else {
+            // filter sums in l order (tf2/src/approx_nn_conv_kernels.cpp:187-197)
+            const int j = (rest - 256) * 32 + lane;
+            if (j < Cout) {
+                float acc = 0.0f;
+                int l = 0;
+                for (; l + 8 <= K; l += 8) {
+                    float v[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] = __ldg(filter + (size_t)(l + e) * Cout + j);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc = __fadd_rn(acc, v[e]);
+                }
+                for (; l < K; ++l) acc = __fadd_rn(acc, __ldg(filter + (size_t)l * Cout + j));
+                reinterpret_cast<float *>(plan + L.bsum_off)[j] = acc;
+            }
+        }
+        return;
+    }
+
+    __shared__ unsigned short cnt[32][33];      // items of lane x in bank y still to schedule
+    __shared__ unsigned short pos[32][33];      // next entry of `order` for (lane, bank)
+    __shared__ unsigned short order[32][kMaxChunk];  // chunk-local l, sorted by bank, per lane
+    __shared__ int bank_at_rank[32];
+
+    const int g = int(blockIdx.x) / L.NCH, c = int(blockIdx.x) % L.NCH;
+    const int l_base = c * L.KC;
+    const int kc = min(L.KC, K - l_base);
+    const int j = g * 32 + lane;
+    const bool live = j < Cout;
+
+    for (int b = 0; b < 32; ++b) cnt[lane][b] = 0;
+    if (live)
+        for (int i = 0; i < kc; ++i) cnt[lane][slot_bank(sigma[qf[(size_t)(l_base + i) * Cout + j]])]++;
+    {
+        int run = 0;
+        for (int b = 0; b < 32; ++b) { pos[lane][b] = (unsigned short)run; run += cnt[lane][b]; }
+    }
+    if (live) {
+        unsigned short fill[32];
+#pragma unroll
+        for (int b = 0; b < 32; ++b) fill[b] = 0;
+        for (int i = 0; i < kc; ++i) {
+            const int b = slot_bank(sigma[qf[(size_t)(l_base + i) * Cout + j]]);
+            // position = start of the bank's run + entries already placed (kept in local memory)
+            order[lane][pos[lane][b] + fill[b]] = (unsigned short)i;
+            fill[b]++;
+        }
+    }
+    __syncwarp();
+    int lane_rem = live ? kc : 0;
+    int load = 0;                                  // lane b: remaining items of bank b over all lanes
+    for (int x = 0; x < 32; ++x) load += cnt[x][lane];
+    int total = 0;
+    {
+        int v = lane_rem;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        total = v;
+    }
+
+    uint4 *prog = reinterpret_cast<uint4 *>(plan + L.prog_off) + (size_t)blockIdx.x * L.sqcap * 32;
+    const int step_cap = L.sqcap * 4;
+    uint32_t wq[4] = {0, 0, 0, 0};
+    int step = 0;
+    bool overflow = false;
+    while (total > 0) {
+        if (step >= step_cap) { overflow = true; break; }
+        // banks by remaining load, largest first
+        int rank = 0;
+        for (int x = 0; x < 32; ++x) {
+            const int lx = __shfl_sync(0xffffffffu, load, x);
+            rank += (lx > load || (lx == load && x < lane)) ? 1 : 0;
+        }
+        bank_at_rank[rank] = lane;
+        __syncwarp();
+        unsigned used = 0, taken = 0;
+        int my_bank = -1, my_l = 0;
+        for (int r = 0; r < 32; ++r) {
+            const int b = bank_at_rank[r];
+            if (__shfl_sync(0xffffffffu, load, b) == 0) break;
+            const bool has = cnt[lane][b] > 0 && !((used >> lane) & 1u);
+            const unsigned key = has ? ((unsigned(lane_rem) << 5) | unsigned(31 - lane)) : 0u;
+            const unsigned best = __reduce_max_sync(0xffffffffu, key);
+            if (best == 0u) continue;
+            const int chosen = 31 - int(best & 31u);
+            if (lane == chosen) {
+                cnt[lane][b]--;
+                my_l = order[lane][pos[lane][b]];
+                pos[lane][b]++;
+                my_bank = b;
+                lane_rem--;
+            }
+            if (lane == b) load--;
+            used |= 1u << chosen;
+            taken |= 1u << b;
+            total--;
+        }
+        __syncwarp();
+        uint32_t w;
+        if (my_bank >= 0) {
+            const int s = sigma[qf[(size_t)(l_base + my_l) * Cout + j]];
+            const int row = my_l + 1;
+            w = uint32_t(2 * (s & 127)) | (uint32_t(row >> 8) << 8) | (uint32_t(1 + (s >> 7)) << 16) | (uint32_t(row & 255) << 24);
+        } else {
+            const unsigned idle = ~used;
+            const int k = __popc(idle & ((1u << lane) - 1u));
+            const int bank = __fns(~taken, 0, k + 1);   // k-th bank nobody looks up in this step
+            w = uint32_t(4 * bank) | (3u << 16);
+        }
+        wq[step & 3] = w;
+        if ((step & 3) == 3) prog[(size_t)(step >> 2) * 32 + lane] = make_uint4(wq[0], wq[1], wq[2], wq[3]);
+        ++step;
+    }
+    if (step & 3) {
+        for (int e = step & 3; e < 4; ++e) wq[e] = uint32_t(4 * lane) | (3u << 16);
+        prog[(size_t)(step >> 2) * 32 + lane] = make_uint4(wq[0], wq[1], wq[2], wq[3]);
+    }
+    if (lane == 0) {
+        reinterpret_cast<int *>(plan + L.steps_off)[blockIdx.x] = (step + 3) >> 2;
+        if (overflow) atomicOr(&hdr->fallback, 1);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// the convolution
+// ------------------------------------------------------------------------------------------------
+struct SchedParams {
+    const unsigned char *plan;
+    PlanLayout L;
+    const float *input;
+    float *output;
+    int32_t *acc_out;
+    int N, H, W, C, KH, KW, Cout;
+    int sh, sw, dh, dw, ph, pw, OH, OW, K;
+    long long M;
+    int tiles_n;              // channel tiles of 32*GW channels
+    long long tiles_total;
+    float in_off, in_inv, s1s2, m1, m2, km1m2;
+    int vec_ok;
+};
+
+// Named barriers of dense_sched_kernel (barrier 0 is used once, after the table fill).
+#define AXC_BAR(id, count) asm volatile("bar.sync %0, %1;" ::"n"(id), "n"(count) : "memory")
+constexpr int kBarLoad = 1;   // loaders: byte staging complete
+constexpr int kBarIter = 2;   // consumers + loaders: next activation buffer complete, current one released
+constexpr int kBarEpi = 3;    // consumers: reduction scratch released
+constexpr int kBarTile = 4;   // consumers + sums warp: patch sums of the tile visible
+
+// GW = channel groups per tile (tile = 16 pixels x 32*GW channels).
+// Warps 0..7  "consumers": GW groups x (8/GW) slices of every schedule; nothing but lookups.
+// Warps 8..11 "loaders": prepare the activation rows of the next (tile, chunk) while the consumers work on
+//             the current one: gather + quantise into a byte staging area, then copy every K row 8 times
+//             side by side into the other activation buffer.
+// Warp 12     "sums": one lane per pixel adds the patch sums of the tile in flight, in the reference's order.
+template <int GW>
+__global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const SchedParams P)
+{
+    constexpr int KS = kComputeWarps / GW;           // schedule slices per group
+    constexpr int PPW = kTilePix / KS;               // pixels a warp finalises
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const PlanHeader *hdr = reinterpret_cast<const PlanHeader *>(P.plan);
+    if (hdr->fallback != 0) return;                  // the common-K kernel takes this call
+
+    const unsigned dyn0 = (unsigned)__cvta_generic_to_shared(smem_raw);
+    unsigned dyn_size;
+    asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
+    // staging below the table: buffer 0 (zero row + KC rows), byte staging, reduction, patch sums
+    const int KC = P.L.KC;
+    unsigned cur = (dyn0 + 127u) & ~127u;
+    const unsigned sBuf0 = cur;              cur += unsigned(KC + 1) * 128u;
+    const unsigned sStage = cur;             cur += unsigned(KC) * 16u;
+    const unsigned sRed = cur;               cur += kComputeWarps * kTilePix * 32u * 4u;
+    const unsigned sAsum = cur;              cur += 2u * kTilePix * 4u;
+    const unsigned sBuf1 = kBuf1Base;        // its row 0 is the zero-word row
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (cur > kLutBase || sBuf1 + unsigned(KC + 1) * 128u > kWindowEnd || dyn0 + dyn_size < kWindowEnd) {
+        if (tid == 0) atomicExch(const_cast<int *>(&hdr->status), 2);
+        return;
+    }
+
+    // table image (already permuted and in plane layout) and the two zero rows
+    {
+        const uint4 *src = reinterpret_cast<const uint4 *>(P.plan + P.L.lut_off);
+        for (int i = tid; i < 8192; i += kSchedThreads) sts128(kLutBase + unsigned(i) * 16u, __ldg(src + i));
+        if (tid < 8) {
+            sts128(sBuf0 + tid * 16, make_uint4(0, 0, 0, 0));
+            sts128(sBuf1 + tid * 16, make_uint4(0, 0, 0, 0));
+        }
+    }
+    __syncthreads();
+
+    const int NCH = P.L.NCH;
+    const long long my_tiles = P.tiles_total > blockIdx.x ? (P.tiles_total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+    // tile number tl of this CTA -> first pixel and channel tile
+    auto tile_coords = [&](long long tl, long long *m0, int *nt) {
+        const long long tile = blockIdx.x + tl * gridDim.x;
+        const long long mt = tile / P.tiles_n;
+        *nt = int(tile - mt * P.tiles_n);
+        *m0 = mt * kTilePix;
+    };
+    auto geometry = [&](long long pix, int *y0, int *x0, long long *b) {
+        *y0 = -(1 << 28); *x0 = -(1 << 28); *b = 0;
+        if (pix < P.M) {
+            const int ow = int(pix % P.OW);
+            const long long t = pix / P.OW;
+            const int oh = int(t % P.OH);
+            const int n = int(t / P.OH);
+            *y0 = oh * P.sh - P.ph;
+            *x0 = ow * P.sw - P.pw;
+            *b = (((long long)n * P.H + *y0) * P.W + *x0) * P.C;
+        }
+    };
+
+    if (warp == kComputeWarps + kLoaderWarps) {
+        // ========================================= sums =========================================
+        for (long long tl = 0; tl < my_tiles; ++tl) {
+            long long m0; int nt;
+            tile_coords(tl, &m0, &nt);
+            float sum = 0.0f;
+            if (lane < kTilePix) {
+                int iy0, ix0; long long base;
+                geometry(m0 + lane, &iy0, &ix0, &base);
+                int cc = 0, kx = 0, ky = 0;
+                if (P.vec_ok) {
+                    // two batches of 8 quads in flight: the loads of batch b+1 are issued before the adds of b
+                    auto fetch = [&](float4 *v, int l) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            v[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (l + 4 * e < P.K) {
+                                const int iy = iy0 + ky * P.dh, ix = ix0 + kx * P.dw;
+                                if (iy >= 0 && iy < P.H && ix >= 0 && ix < P.W)
+                                    v[e] = __ldg(reinterpret_cast<const float4 *>(
+                                        P.input + base + ((long long)(ky * P.dh) * P.W + kx * P.dw) * P.C + cc));
+                                cc += 4;
+                                if (cc >= P.C) { cc = 0; if (++kx >= P.KW) { kx = 0; ++ky; } }
+                            }
+                        }
+                    };
+                    auto add = [&](const float4 *v) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            sum = __fadd_rn(sum, v[e].x);
+                            sum = __fadd_rn(sum, v[e].y);
+                            sum = __fadd_rn(sum, v[e].z);
+                            sum = __fadd_rn(sum, v[e].w);
+                        }
+                    };
+                    float4 va[8], vb[8];
+                    fetch(va, 0);
+                    for (int l = 0; l < P.K; l += 64) {
+                        fetch(vb, l + 32);
+                        add(va);
+                        fetch(va, l + 64);
+                        add(vb);
+                    }
+                } else {
+                    for (int l = 0; l < P.K; l += 4) {
+                        float v[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            v[e] = 0.f;
+                            if (l + e < P.K) {
+                                const int iy = iy0 + ky * P.dh, ix = ix0 + kx * P.dw;
+                                if (iy >= 0 && iy < P.H && ix >= 0 && ix < P.W)
+                                    v[e] = __ldg(P.input + base + ((long long)(ky * P.dh) * P.W + kx * P.dw) * P.C + cc);
+                                if (++cc >= P.C) { cc = 0; if (++kx >= P.KW) { kx = 0; ++ky; } }
+                            }
+                        }
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) sum = __fadd_rn(sum, v[e]);
+                    }
+                }
+                sts32(sAsum + unsigned((int(tl) & 1) * kTilePix + lane) * 4u, __float_as_uint(sum));
+            }
+            AXC_BAR(kBarTile, (kComputeWarps + 1) * 32);
+        }
+        return;
+    }
+
+    if (warp >= kComputeWarps) {
+        // ======================================== loaders ========================================
+        const int ptid = tid - kComputeWarps * 32;          // 0..127
+        const int p = ptid & 15;                            // this thread's pixel of the tile
+        const int LQ = (KC + 3) >> 2;
+        const int quads = LQ * kTilePix;
+        constexpr int kStages = (((kMaxChunk + 3) / 4) * kTilePix + kLoaderThreads - 1) / kLoaderThreads;   // 9
+        constexpr int kRepl = (kMaxChunk * 8 + kLoaderThreads - 1) / kLoaderThreads;                         // 18
+        int iy0 = 0, ix0 = 0;
+        long long base = 0;
+
+        auto produce = [&](long long tl, int c, unsigned buf_base) {
+            if (c == 0) {
+                long long m0; int nt;
+                tile_coords(tl, &m0, &nt);
+                geometry(m0 + p, &iy0, &ix0, &base);
+            }
+            const int l_base = c * KC;
+            float4 st[kStages];
+            if (P.vec_ok) {
+                // this thread's quads are lq = (ptid >> 4) + 8 * s: walk the tap position incrementally
+                int l0 = l_base + (ptid >> 4) * 4;
+                int tap = l0 / P.C;
+                int cc = l0 - tap * P.C;
+                int ky = tap / P.KW;
+                int kx = tap - ky * P.KW;
+#pragma unroll
+                for (int s = 0; s < kStages; ++s) {
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (s * kLoaderThreads + ptid < quads && l0 < P.K) {
+                        const int iy = iy0 + ky * P.dh, ix = ix0 + kx * P.dw;
+                        if (iy >= 0 && iy < P.H && ix >= 0 && ix < P.W)
+                            v = __ldg(reinterpret_cast<const float4 *>(
+                                P.input + base + ((long long)(ky * P.dh) * P.W + kx * P.dw) * P.C + cc));
+                    }
+                    st[s] = v;
+                    l0 += (kLoaderThreads / kTilePix) * 4;
+                    cc += (kLoaderThreads / kTilePix) * 4;
+                    while (cc >= P.C) { cc -= P.C; if (++kx >= P.KW) { kx = 0; ++ky; } }
+                }
+            } else {
+#pragma unroll
+                for (int s = 0; s < kStages; ++s) {
+                    float e4[4] = {0.f, 0.f, 0.f, 0.f};
+                    const int q = s * kLoaderThreads + ptid;
+                    if (q < quads) {
+                        const int lq = q >> 4;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int l = l_base + lq * 4 + e;
+                            if (l < P.K && lq * 4 + e < KC) {
+                                const int tap = l / P.C;
+                                const int cc = l - tap * P.C;
+                                const int ky = tap / P.KW;
+                                const int kx = tap - ky * P.KW;
+                                const int iy = iy0 + ky * P.dh, ix = ix0 + kx * P.dw;
+                                if (iy >= 0 && iy < P.H && ix >= 0 && ix < P.W)
+                                    e4[e] = __ldg(P.input + base + ((long long)(ky * P.dh) * P.W + kx * P.dw) * P.C + cc);
+                            }
+                        }
+                    }
+                    st[s] = make_float4(e4[0], e4[1], e4[2], e4[3]);
+                }
+            }
+            // quantise -> byte staging [chunk-local l][pixel]; lanes = pixels, so the byte stores of a warp
+            // fall into two groups of four consecutive words
+#pragma unroll
+            for (int s = 0; s < kStages; ++s) {
+                const int q = s * kLoaderThreads + ptid;
+                if (q < quads) {
+                    const int lq = q >> 4;
+                    const float4 v = st[s];
+                    const unsigned a = sStage + unsigned(lq * 4) * 16u + unsigned(p);
+                    sts8(a, q_u8(v.x, P.in_off, P.in_inv));
+                    if (lq * 4 + 1 < KC) sts8(a + 16, q_u8(v.y, P.in_off, P.in_inv));
+                    if (lq * 4 + 2 < KC) sts8(a + 32, q_u8(v.z, P.in_off, P.in_inv));
+                    if (lq * 4 + 3 < KC) sts8(a + 48, q_u8(v.w, P.in_off, P.in_inv));
+                }
+            }
+            AXC_BAR(kBarLoad, kLoaderThreads);
+            // byte staging -> rows of 8 copies of the 16 pixel bytes (buffer row = chunk-local l + 1); the 8
+            // lanes of a quarter warp write one 128-byte row.  All reads are issued before the writes.
+            uint4 rows[kRepl];
+#pragma unroll
+            for (int i = 0; i < kRepl; ++i) {
+                const int x = ptid + i * kLoaderThreads;
+                if (x < KC * 8) rows[i] = lds128(sStage + unsigned(x >> 3) * 16u);
+            }
+#pragma unroll
+            for (int i = 0; i < kRepl; ++i) {
+                const int x = ptid + i * kLoaderThreads;
+                if (x < KC * 8) sts128(buf_base + unsigned((x >> 3) + 1) * 128u + unsigned(x & 7) * 16u, rows[i]);
+            }
+        };
+
+        if (my_tiles > 0) produce(0, 0, sBuf0);
+        AXC_BAR(kBarIter, (kComputeWarps + kLoaderWarps) * 32);
+        long long tl = 0;
+        int c = 0;
+        unsigned parity = 0;
+        const long long total_iters = my_tiles * NCH;
+        for (long long it = 0; it < total_iters; ++it) {
+            if (++c == NCH) { c = 0; ++tl; }
+            parity ^= 1u;
+            if (it + 1 < total_iters) produce(tl, c, parity ? sBuf1 : sBuf0);
+            AXC_BAR(kBarIter, (kComputeWarps + kLoaderWarps) * 32);
+        }
+        return;
+    }
+
+    // ========================================= consumers =========================================
+    const int gl = warp % GW, ks = warp / GW;
+    const int *steps_q = reinterpret_cast<const int *>(P.plan + P.L.steps_off);
+    const uint4 *prog = reinterpret_cast<const uint4 *>(P.plan + P.L.prog_off);
+    const float *bsum = reinterpret_cast<const float *>(P.plan + P.L.bsum_off);
+    int acc[kTilePix];
+#pragma unroll
+    for (int i = 0; i < kTilePix; ++i) acc[i] = 0;
+
+    // the slice of the schedule of (channel tile nt, chunk c) that this warp walks
+    auto slice_of = [&](int nt, int c, const uint4 **pp, int *nq) {
+        const int g = nt * GW + gl;
+        *nq = 0;
+        *pp = prog;
+        if (g < P.L.G) {
+            const int sc = g * NCH + c;
+            const int Q = __ldg(steps_q + sc);
+            const int q0 = (ks * Q) / KS, q1 = ((ks + 1) * Q) / KS;
+            *pp = prog + ((size_t)sc * P.L.sqcap + q0) * 32 + lane;
+            *nq = q1 - q0;
+        }
+    };
+
+    const uint4 *pp = prog;
+    int nq = 0;
+    uint4 w_a = make_uint4(0, 0, 0, 0), w_b = make_uint4(0, 0, 0, 0);   // two quads of look-ahead
+    long long m0 = 0;
+    int nt = 0;
+    if (my_tiles > 0) {
+        tile_coords(0, &m0, &nt);
+        slice_of(nt, 0, &pp, &nq);
+        if (nq > 0) w_a = __ldg(pp);
+        if (nq > 1) w_b = __ldg(pp + 32);
+    }
+    AXC_BAR(kBarIter, (kComputeWarps + kLoaderWarps) * 32);
+
+    unsigned parity = 0;
+    for (long long tl = 0; tl < my_tiles; ++tl) {
+        long long m0_next = 0;
+        int nt_next = 0;
+        if (tl + 1 < my_tiles) tile_coords(tl + 1, &m0_next, &nt_next);
+        for (int c = 0; c < NCH; ++c) {
+            const unsigned rep = (parity ? sBuf1 : sBuf0) + unsigned(lane & 7) * 16u;
+            for (int q = 0; q < nq; ++q) {
+                const uint4 wq = w_a;
+                w_a = w_b;
+                if (q + 2 < nq) w_b = __ldg(pp + (size_t)(q + 2) * 32);
+                const uint32_t ws[4] = {wq.x, wq.y, wq.z, wq.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const uint32_t w = ws[e];
+                    const unsigned row = (w >> 24) | (w & 0x300u);
+                    const uint4 av = lds128(rep + row * 128u);
+                    const unsigned aw[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+                    for (int i4 = 0; i4 < kTilePix / 4; ++i4) {
+                        // table address = {column byte of w, activation byte, plane byte of w, 0}
+                        acc[i4 * 4 + 0] += int(lds16(prmt<0xA240>(w, aw[i4])));
+                        acc[i4 * 4 + 1] += int(lds16(prmt<0xA250>(w, aw[i4])));
+                        acc[i4 * 4 + 2] += int(lds16(prmt<0xA260>(w, aw[i4])));
+                        acc[i4 * 4 + 3] += int(lds16(prmt<0xA270>(w, aw[i4])));
+                    }
+                }
+            }
+            // look-ahead into the next (tile, chunk), issued before the barrier
+            nq = 0;
+            if (c + 1 < NCH) slice_of(nt, c + 1, &pp, &nq);
+            else if (tl + 1 < my_tiles) slice_of(nt_next, 0, &pp, &nq);
+            if (nq > 0) w_a = __ldg(pp);
+            if (nq > 1) w_b = __ldg(pp + 32);
+            if (c == NCH - 1 && KS > 1) {
+#pragma unroll
+                for (int i = 0; i < kTilePix; ++i)
+                    sts32(sRed + unsigned(((ks * GW + gl) * kTilePix + i) * 32 + lane) * 4u, unsigned(acc[i]));
+            }
+            AXC_BAR(kBarIter, (kComputeWarps + kLoaderWarps) * 32);
+            parity ^= 1u;
+        }
+        // ---- the tile is complete: reduce the slices, dequantise, store --------------------------
+        AXC_BAR(kBarTile, (kComputeWarps + 1) * 32);
+        {
+            const int g = nt * GW + gl;
+            const int j = g * 32 + lane;
+            if (g < P.L.G && j < P.Cout) {
+                const float t2 = __fmul_rn(P.m1, __ldg(bsum + j));
+#pragma unroll
+                for (int ii = 0; ii < PPW; ++ii) {
+                    const int i = ks * PPW + ii;
+                    int s = 0;
+                    if (KS > 1) {
+#pragma unroll
+                        for (int k2 = 0; k2 < KS; ++k2)
+                            s += int(lds32(sRed + unsigned(((k2 * GW + gl) * kTilePix + i) * 32 + lane) * 4u));
+                    } else {
+                        s = acc[i];
+                    }
+                    const long long pix = m0 + i;
+                    if (pix < P.M) {
+                        const float a_sum = __uint_as_float(lds32(sAsum + unsigned((int(tl) & 1) * kTilePix + i) * 4u));
+                        const float t0 = __fmul_rn(float(s), P.s1s2);
+                        const float t1 = __fmul_rn(P.m2, a_sum);
+                        P.output[pix * P.Cout + j] = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), P.km1m2);
+                        if (P.acc_out) P.acc_out[pix * P.Cout + j] = s;
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kTilePix; ++i) acc[i] = 0;
+        }
+        if (KS > 1) AXC_BAR(kBarEpi, kComputeWarps * 32);
+        m0 = m0_next;
+        nt = nt_next;
+    }
+}
+
+template <int GW>
+int launch_sched_variant(SchedParams P, const DeviceInfo &di, cudaStream_t stream)
+{
+    P.tiles_n = (P.L.G + GW - 1) / GW;
+    P.tiles_total = ((P.M + kTilePix - 1) / kTilePix) * P.tiles_n;
+    AXC_CUDA(cudaFuncSetAttribute(dense_sched_kernel<GW>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
+    const long long grid = P.tiles_total < di.sm_count ? P.tiles_total : di.sm_count;
+    dense_sched_kernel<GW><<<unsigned(grid), kSchedThreads, size_t(di.max_smem_optin), stream>>>(P);
+    AXC_CUDA(cudaGetLastError());
+    count_launch();
+    return AXC_OK;
+}
+
+}  // namespace
+
+PlanLayout plan_layout(int K, int Cout)
+{
+    PlanLayout L;
+    L.G = (Cout + 31) / 32;
+    L.NCH = (K + kMaxChunk - 1) / kMaxChunk;
+    L.KC = (((K + L.NCH - 1) / L.NCH) + 3) & ~3;
+    if (L.KC > kMaxChunk) L.KC = kMaxChunk;
+    L.sqcap = (2 * L.KC + 3) / 4 + 1;               // room for twice the ideal number of steps
+    auto r256 = [](size_t v) { return (v + 255) & ~size_t(255); };
+    size_t off = 256;
+    L.qf_off = off;      off += r256(size_t(K) * Cout);
+    L.sigma_off = off;   off += 256;
+    L.lut_off = off;     off += 131072;
+    L.bsum_off = off;    off += r256(size_t(Cout) * 4);
+    L.steps_off = off;   off += r256(size_t(L.G) * L.NCH * 4);
+    L.prog_off = off;    off += size_t(L.G) * L.NCH * L.sqcap * 512;
+    L.total = off;
+    return L;
+}
+
+int launch_plan(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const Quant &q, const float *filter,
+                unsigned char *plan, const PlanLayout &L, uint8_t *qf_debug, cudaStream_t stream)
+{
+    PlanHeader want = {};
+    want.magic = 0x41584332u;  // "AXC2"
+    want.K = g.K; want.Cout = g.Cout; want.G = L.G; want.NCH = L.NCH; want.KC = L.KC; want.sqcap = L.sqcap;
+    want.table_uid = table_uid;
+    memcpy(&want.f_off_bits, &q.f_off, 4);
+    memcpy(&want.f_inv_bits, &q.f_inv, 4);
+    PlanHeader *hdr = reinterpret_cast<PlanHeader *>(plan);
+    AXC_CUDA(cudaMemsetAsync(&hdr->dirty, 0, sizeof(int), stream));
+    const long long count = (long long)g.K * g.Cout;
+    plan_check_kernel<<<unsigned((count + 255) / 256), 256, 0, stream>>>(filter, count, q.f_off, q.f_inv,
+                                                                       plan + L.qf_off, qf_debug, hdr, want);
+    AXC_CUDA(cudaGetLastError());
+    plan_sigma_kernel<<<1, 256, 0, stream>>>(plan + L.qf_off, count, plan + L.sigma_off, hdr, want);
+    AXC_CUDA(cudaGetLastError());
+    const unsigned blocks = unsigned(L.G * L.NCH + 256 + (g.Cout + 31) / 32);
+    plan_build_kernel<<<blocks, 32, 0, stream>>>(filter, lut_dev, plan, L, g.K, g.Cout);
+    AXC_CUDA(cudaGetLastError());
+    count_launch(3);
+    return AXC_OK;
+}
+
+int launch_dense_sched(const Geom &g, const Quant &q, const float *input, float *output, const unsigned char *plan,
+                       const PlanLayout &L, int32_t *acc_out, const DeviceInfo &di, cudaStream_t stream)
+{
+    SchedParams P;
+    P.plan = plan; P.L = L; P.input = input; P.output = output; P.acc_out = acc_out;
+    P.N = g.N; P.H = g.H; P.W = g.W; P.C = g.C; P.KH = g.KH; P.KW = g.KW; P.Cout = g.Cout;
+    P.sh = g.sh; P.sw = g.sw; P.dh = g.dh; P.dw = g.dw; P.ph = g.ph; P.pw = g.pw; P.OH = g.OH; P.OW = g.OW;
+    P.K = g.K; P.M = g.M; P.tiles_n = 0; P.tiles_total = 0;
+    P.in_off = q.in_off; P.in_inv = q.in_inv; P.s1s2 = q.s1s2; P.m1 = q.m1; P.m2 = q.m2;
+    {
+        volatile float kf = float(g.K);
+        volatile float t3 = kf * q.m1m2;
+        P.km1m2 = t3;
+    }
+    P.vec_ok = (g.C % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
+    if (L.G <= 1) return launch_sched_variant<1>(P, di, stream);
+    if (L.G <= 2) return launch_sched_variant<2>(P, di, stream);
+    if (L.G <= 4) return launch_sched_variant<4>(P, di, stream);
+    return launch_sched_variant<8>(P, di, stream);
+}
+
+}  // namespace axc

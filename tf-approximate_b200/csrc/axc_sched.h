@@ -1,0 +1,41 @@
+// Plan (per-filter schedule) kept in the caller's workspace for the bank-scheduled dense kernel.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <string.h>
+
+namespace axc {
+
+struct Geom;
+struct Quant;
+struct DeviceInfo;
+
+// K elements per schedule chunk: row index + 1 must fit the activation buffer above the table
+// ((kMaxChunk + 1) * 128 bytes in the 36 KiB between the table and the end of the shared window).
+constexpr int kMaxChunk = 284;
+
+struct PlanHeader {
+    uint32_t magic;
+    int K, Cout, G, NCH, KC, sqcap;
+    uint32_t table_uid;
+    uint32_t f_off_bits, f_inv_bits;
+    int dirty;      // set by plan_check when the stored plan does not belong to this filter / table
+    int fallback;   // set when a schedule did not fit: the common-K kernel serves the call
+    int status;     // 0 fine; 2 shared-memory layout check failed
+};
+
+struct PlanLayout {
+    int G, NCH, KC, sqcap;   // channel groups of 32, K chunks, chunk length, step-quads reserved per (group, chunk)
+    size_t qf_off, sigma_off, lut_off, bsum_off, steps_off, prog_off, total;
+};
+
+PlanLayout plan_layout(int K, int Cout);
+
+int launch_plan(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const Quant &q, const float *filter,
+                unsigned char *plan, const PlanLayout &L, uint8_t *qf_debug, cudaStream_t stream);
+
+int launch_dense_sched(const Geom &g, const Quant &q, const float *input, float *output, const unsigned char *plan,
+                       const PlanLayout &L, int32_t *acc_out, const DeviceInfo &di, cudaStream_t stream);
+
+}  // namespace axc

@@ -4,6 +4,7 @@
 the generated TensorFlow wrapper of `ApproxConv2DWithMinMaxVars`
 (tf2/src/approx_nn_ops.cpp:38-54; call site tf2/test/test_table_approx_conv_2d.py:46-49).
 torch is used for device memory and streams only."""
+import collections
 import ctypes as C
 import threading
 
@@ -123,15 +124,24 @@ def conv2d_output_shape(input_shape, filter_shape, strides, padding, data_format
     return tuple(int(v) for v in out)
 
 
-_ws_cache = {}
+_ws_cache = collections.OrderedDict()
+_WS_CACHE_ENTRIES = 256
 
 
-def _workspace(device, nbytes):
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+def _workspace(device, nbytes, key):
+    """Per-filter workspace.  The library keeps the prepared filter (quantised copy, lookup schedule, filter
+    sums) in it and re-uses that preparation while the filter values it was built from are unchanged, so
+    every (device, filter storage, shape, table) gets its own buffer, the way the reference's op instance
+    owns its table (tf2/src/approx_ops_types.h:222).  The buffer belongs to one stream at a time."""
+    key = (device.index,) + key
     buf = _ws_cache.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
         _ws_cache[key] = buf
+        while len(_ws_cache) > _WS_CACHE_ENTRIES:
+            _ws_cache.popitem(last=False)
+    else:
+        _ws_cache.move_to_end(key)
     return buf
 
 
@@ -162,7 +172,7 @@ def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_
     wsz = C.c_size_t()
     ws_fn = L.axc_depthwise_conv2d_workspace_bytes if depthwise else L.axc_conv2d_workspace_bytes
     raise_for_status(ws_fn(C.byref(d), C.byref(wsz)), "workspace size")
-    ws = _workspace(dev, wsz.value)
+    ws = _workspace(dev, wsz.value, (f.data_ptr(), tuple(f.shape), id(table), depthwise))
     dbg_ptr = None
     dbg_t = None
     if debug:
