@@ -147,7 +147,10 @@ Workspace dense_workspace(int K, int Cout)
     return w;
 }
 
-size_t dense_workspace_total(int K, int Cout) { return plan_layout(K, Cout).total + dense_workspace(K, Cout).total; }
+size_t dense_workspace_total(int K, int Cout, long long M)
+{
+    return plan_layout(K, Cout).total + dense_workspace(K, Cout).total + round256(size_t(M) * 4);
+}
 
 Workspace depthwise_workspace(int KHW, int C, int mult)
 {
@@ -228,7 +231,7 @@ static int forward(bool depthwise, axc_table *table, const axc_conv_desc *desc, 
     const long long out_c = depthwise ? (long long)g.C * g.Cout : g.Cout;
     if (g.M * out_c == 0) return AXC_OK;  // empty output: nothing to do
     if (!input || !filter || !output) return AXC_INVALID_ARGUMENT;
-    const size_t ws_total = depthwise ? depthwise_workspace(g.K, g.C, g.Cout).total : dense_workspace_total(g.K, g.Cout);
+    const size_t ws_total = depthwise ? depthwise_workspace(g.K, g.C, g.Cout).total : dense_workspace_total(g.K, g.Cout, g.M);
     if (!workspace || workspace_bytes < ws_total) return AXC_INTERNAL;
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return AXC_INVALID_ARGUMENT;
 
@@ -354,7 +357,7 @@ int axc_conv2d_workspace_bytes(const axc_conv_desc *desc, size_t *bytes)
     axc::Geom g;
     int rc = axc::resolve_geometry(desc, false, &g);
     if (rc) return rc;
-    *bytes = axc::dense_workspace_total(g.K, g.Cout);
+    *bytes = axc::dense_workspace_total(g.K, g.Cout, g.M);
     return AXC_OK;
 }
 

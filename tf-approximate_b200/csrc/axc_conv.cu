@@ -506,7 +506,8 @@ int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, con
     int rc = device_info(device, &di);
     if (rc) return rc;
     if (di.max_smem_optin < 232448) return AXC_INTERNAL;   // the kernels are laid out for the 227 KiB of sm_100
-    const bool scheduled = dense_variant() == 0;
+    // the scheduled kernel divides by C and KW with 40-bit reciprocals, exact while K * max(C, KW) < 2^40
+    const bool scheduled = dense_variant() == 0 && (long long)g.K * (g.C > g.KW ? g.C : g.KW) < (1ll << 40);
     const PlanLayout L = plan_layout(g.K, g.Cout);
     const Workspace ws = dense_workspace(g.K, g.Cout);
     unsigned char *plan = static_cast<unsigned char *>(workspace);
@@ -528,7 +529,10 @@ int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, con
     if (scheduled) {
         rc = launch_plan(lut_dev, table_uid, g, q, filter, plan, L, dbg ? dbg->qfilter : nullptr, stream);
         if (rc) return rc;
-        rc = launch_dense_sched(g, q, input, output, plan, L, dbg ? dbg->acc : nullptr, di, stream);
+        float *asum = reinterpret_cast<float *>(wsb + ws.total);
+        rc = launch_patch_sums(g, input, asum, stream);
+        if (rc) return rc;
+        rc = launch_dense_sched(g, q, input, asum, output, plan, L, dbg ? dbg->acc : nullptr, di, stream);
         if (rc) return rc;
         gate = &reinterpret_cast<const PlanHeader *>(plan)->fallback;
     }

@@ -31,8 +31,10 @@ constexpr unsigned kWindowEnd = 233472u;       // 228 KiB shared window of an SM
 constexpr int kComputeWarps = 8;
 constexpr int kLoaderWarps = 4;
 constexpr int kLoaderThreads = kLoaderWarps * 32;
-constexpr int kSchedThreads = (kComputeWarps + kLoaderWarps + 1) * 32;   // + the sums warp
+constexpr int kSchedThreads = (kComputeWarps + kLoaderWarps) * 32;
 constexpr int kTilePix = 16;
+constexpr int kTapTableMax = 512;
+constexpr int kStepsInSmemMax = 1024;
 
 __device__ __forceinline__ unsigned q_u8(float x, float off, float inv)
 {
@@ -325,6 +327,7 @@ struct SchedParams {
     const unsigned char *plan;
     PlanLayout L;
     const float *input;
+    const float *asum;        // [M] patch sums from patch_sum_kernel
     float *output;
     int32_t *acc_out;
     int N, H, W, C, KH, KW, Cout;
@@ -334,21 +337,26 @@ struct SchedParams {
     long long tiles_total;
     float in_off, in_inv, s1s2, m1, m2, km1m2;
     int vec_ok;
+    unsigned long long magic_c, magic_kw;   // ceil(2^40 / C), ceil(2^40 / KW): n / d == (n * magic) >> 40 for n*d < 2^40
 };
+
+__device__ __forceinline__ int fast_div(int n, unsigned long long magic)
+{
+    return int((static_cast<unsigned long long>(static_cast<unsigned>(n)) * magic) >> 40);
+}
 
 // Named barriers of dense_sched_kernel (barrier 0 is used once, after the table fill).
 #define AXC_BAR(id, count) asm volatile("bar.sync %0, %1;" ::"n"(id), "n"(count) : "memory")
 constexpr int kBarLoad = 1;   // loaders: byte staging complete
 constexpr int kBarIter = 2;   // consumers + loaders: next activation buffer complete, current one released
 constexpr int kBarEpi = 3;    // consumers: reduction scratch released
-constexpr int kBarTile = 4;   // consumers + sums warp: patch sums of the tile visible
 
 // GW = channel groups per tile (tile = 16 pixels x 32*GW channels).
 // Warps 0..7  "consumers": GW groups x (8/GW) slices of every schedule; nothing but lookups.
 // Warps 8..11 "loaders": prepare the activation rows of the next (tile, chunk) while the consumers work on
 //             the current one: gather + quantise into a byte staging area, then copy every K row 8 times
 //             side by side into the other activation buffer.
-// Warp 12     "sums": one lane per pixel adds the patch sums of the tile in flight, in the reference's order.
+// The patch sums come from patch_sum_kernel, which runs before this kernel.
 template <int GW>
 __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const SchedParams P)
 {
@@ -361,13 +369,21 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
     const unsigned dyn0 = (unsigned)__cvta_generic_to_shared(smem_raw);
     unsigned dyn_size;
     asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
-    // staging below the table: buffer 0 (zero row + KC rows), byte staging, reduction, patch sums
+    // staging below the table: buffer 0 (zero row + KC rows), byte staging, reduction scratch
     const int KC = P.L.KC;
     unsigned cur = (dyn0 + 127u) & ~127u;
     const unsigned sBuf0 = cur;              cur += unsigned(KC + 1) * 128u;
     const unsigned sStage = cur;             cur += unsigned(KC) * 16u;
     const unsigned sRed = cur;               cur += kComputeWarps * kTilePix * 32u * 4u;
-    const unsigned sAsum = cur;              cur += 2u * kTilePix * 4u;
+    // tap table for inputs whose channel count is not a multiple of 4 (scalar gathers): per K element the
+    // element offset of the tap relative to the patch origin and its (dy, dx), so that the gather loops need
+    // no divisions
+    const bool tap_table = !P.vec_ok && P.K <= kTapTableMax;
+    const unsigned sTap = cur;               cur += tap_table ? unsigned(P.K) * 8u : 0u;
+    // schedule lengths of every (group, chunk), so that the consumers' look-ahead does not wait on global memory
+    const int n_sched = P.L.G * P.L.NCH;
+    const bool steps_in_smem = n_sched <= kStepsInSmemMax;
+    const unsigned sSteps = cur;             cur += steps_in_smem ? unsigned(n_sched) * 4u : 0u;
     const unsigned sBuf1 = kBuf1Base;        // its row 0 is the zero-word row
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (cur > kLutBase || sBuf1 + unsigned(KC + 1) * 128u > kWindowEnd || dyn0 + dyn_size < kWindowEnd) {
@@ -383,8 +399,32 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
             sts128(sBuf0 + tid * 16, make_uint4(0, 0, 0, 0));
             sts128(sBuf1 + tid * 16, make_uint4(0, 0, 0, 0));
         }
+        if (steps_in_smem) {
+            const int *sq = reinterpret_cast<const int *>(P.plan + P.L.steps_off);
+            for (int i = tid; i < n_sched; i += kSchedThreads) sts32(sSteps + unsigned(i) * 4u, unsigned(__ldg(sq + i)));
+        }
+        if (tap_table) {
+            for (int l = tid; l < P.K; l += kSchedThreads) {
+                const int tap = l / P.C;
+                const int cc = l - tap * P.C;
+                const int ky = tap / P.KW;
+                const int kx = tap - ky * P.KW;
+                const int dy = ky * P.dh, dx = kx * P.dw;
+                const int off = (dy * P.W + dx) * P.C + cc;     // fits: the table is only built for K <= 512
+                sts32(sTap + unsigned(l) * 8u, unsigned(off));
+                sts32(sTap + unsigned(l) * 8u + 4u, (unsigned(dy) & 0xFFFFu) | (unsigned(dx) << 16));
+            }
+        }
     }
     __syncthreads();
+
+    // one scalar tap through the table: value of K element l for the patch at (iy0, ix0, base)
+    auto tap_value = [&](int l, int iy0, int ix0, long long base) -> float {
+        unsigned off, dd;
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(off), "=r"(dd) : "r"(sTap + unsigned(l) * 8u));
+        const unsigned iy = unsigned(iy0 + int(dd & 0xFFFFu)), ix = unsigned(ix0 + int(dd >> 16));
+        return (iy < unsigned(P.H) && ix < unsigned(P.W)) ? __ldg(P.input + base + int(off)) : 0.0f;
+    };
 
     const int NCH = P.L.NCH;
     const long long my_tiles = P.tiles_total > blockIdx.x ? (P.tiles_total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
@@ -408,73 +448,6 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
             *b = (((long long)n * P.H + *y0) * P.W + *x0) * P.C;
         }
     };
-
-    if (warp == kComputeWarps + kLoaderWarps) {
-        // ========================================= sums =========================================
-        for (long long tl = 0; tl < my_tiles; ++tl) {
-            long long m0; int nt;
-            tile_coords(tl, &m0, &nt);
-            float sum = 0.0f;
-            if (lane < kTilePix) {
-                int iy0, ix0; long long base;
-                geometry(m0 + lane, &iy0, &ix0, &base);
-                int cc = 0, kx = 0, ky = 0;
-                if (P.vec_ok) {
-                    // two batches of 8 quads in flight: the loads of batch b+1 are issued before the adds of b
-                    auto fetch = [&](float4 *v, int l) {
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            v[e] = make_float4(0.f, 0.f, 0.f, 0.f);
-                            if (l + 4 * e < P.K) {
-                                const int iy = iy0 + ky * P.dh, ix = ix0 + kx * P.dw;
-                                if (iy >= 0 && iy < P.H && ix >= 0 && ix < P.W)
-                                    v[e] = __ldg(reinterpret_cast<const float4 *>(
-                                        P.input + base + ((long long)(ky * P.dh) * P.W + kx * P.dw) * P.C + cc));
-                                cc += 4;
-                                if (cc >= P.C) { cc = 0; if (++kx >= P.KW) { kx = 0; ++ky; } }
-                            }
-                        }
-                    };
-                    auto add = [&](const float4 *v) {
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            sum = __fadd_rn(sum, v[e].x);
-                            sum = __fadd_rn(sum, v[e].y);
-                            sum = __fadd_rn(sum, v[e].z);
-                            sum = __fadd_rn(sum, v[e].w);
-                        }
-                    };
-                    float4 va[8], vb[8];
-                    fetch(va, 0);
-                    for (int l = 0; l < P.K; l += 64) {
-                        fetch(vb, l + 32);
-                        add(va);
-                        fetch(va, l + 64);
-                        add(vb);
-                    }
-                } else {
-                    for (int l = 0; l < P.K; l += 4) {
-                        float v[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            v[e] = 0.f;
-                            if (l + e < P.K) {
-                                const int iy = iy0 + ky * P.dh, ix = ix0 + kx * P.dw;
-                                if (iy >= 0 && iy < P.H && ix >= 0 && ix < P.W)
-                                    v[e] = __ldg(P.input + base + ((long long)(ky * P.dh) * P.W + kx * P.dw) * P.C + cc);
-                                if (++cc >= P.C) { cc = 0; if (++kx >= P.KW) { kx = 0; ++ky; } }
-                            }
-                        }
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) sum = __fadd_rn(sum, v[e]);
-                    }
-                }
-                sts32(sAsum + unsigned((int(tl) & 1) * kTilePix + lane) * 4u, __float_as_uint(sum));
-            }
-            AXC_BAR(kBarTile, (kComputeWarps + 1) * 32);
-        }
-        return;
-    }
 
     if (warp >= kComputeWarps) {
         // ======================================== loaders ========================================
@@ -521,20 +494,27 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
                 for (int s = 0; s < kStages; ++s) {
                     float e4[4] = {0.f, 0.f, 0.f, 0.f};
                     const int q = s * kLoaderThreads + ptid;
-                    if (q < quads) {
+                    if (q < quads && tap_table) {
                         const int lq = q >> 4;
+                        const int l0 = l_base + lq * 4;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (l0 + e < P.K && lq * 4 + e < KC) e4[e] = tap_value(l0 + e, iy0, ix0, base);
+                    } else if (q < quads) {
+                        const int lq = q >> 4;
+                        const int l0 = l_base + lq * 4;
+                        int tap = fast_div(l0, P.magic_c);
+                        int cc = l0 - tap * P.C;
+                        int ky = fast_div(tap, P.magic_kw);
+                        int kx = tap - ky * P.KW;
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const int l = l_base + lq * 4 + e;
-                            if (l < P.K && lq * 4 + e < KC) {
-                                const int tap = l / P.C;
-                                const int cc = l - tap * P.C;
-                                const int ky = tap / P.KW;
-                                const int kx = tap - ky * P.KW;
+                            if (l0 + e < P.K && lq * 4 + e < KC) {
                                 const int iy = iy0 + ky * P.dh, ix = ix0 + kx * P.dw;
                                 if (iy >= 0 && iy < P.H && ix >= 0 && ix < P.W)
                                     e4[e] = __ldg(P.input + base + ((long long)(ky * P.dh) * P.W + kx * P.dw) * P.C + cc);
                             }
+                            if (++cc >= P.C) { cc = 0; if (++kx >= P.KW) { kx = 0; ++ky; } }
                         }
                     }
                     st[s] = make_float4(e4[0], e4[1], e4[2], e4[3]);
@@ -602,7 +582,7 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
         *pp = prog;
         if (g < P.L.G) {
             const int sc = g * NCH + c;
-            const int Q = __ldg(steps_q + sc);
+            const int Q = steps_in_smem ? int(lds32(sSteps + unsigned(sc) * 4u)) : __ldg(steps_q + sc);
             const int q0 = (ks * Q) / KS, q1 = ((ks + 1) * Q) / KS;
             *pp = prog + ((size_t)sc * P.L.sqcap + q0) * 32 + lane;
             *nq = q1 - q0;
@@ -623,11 +603,28 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
     AXC_BAR(kBarIter, (kComputeWarps + kLoaderWarps) * 32);
 
     unsigned parity = 0;
+    float t2 = 0.0f;          // m1 * bSum[j] of this lane's channel
+    int t2_nt = -1;
     for (long long tl = 0; tl < my_tiles; ++tl) {
         long long m0_next = 0;
         int nt_next = 0;
         if (tl + 1 < my_tiles) tile_coords(tl + 1, &m0_next, &nt_next);
+        // epilogue operands, requested a whole tile ahead of their use
+        const float asum_lane = (lane < kTilePix && m0 + lane < P.M) ? __ldg(P.asum + m0 + lane) : 0.0f;
+        {
+            const int j = (nt * GW + gl) * 32 + lane;
+            if (nt != t2_nt) { t2 = j < P.Cout ? __fmul_rn(P.m1, __ldg(bsum + j)) : 0.0f; t2_nt = nt; }
+        }
         for (int c = 0; c < NCH; ++c) {
+            // first two quads of the next (tile, chunk): requested now, consumed after the barrier
+            const uint4 *pp_n = prog;
+            int nq_n = 0;
+            uint4 n_a = make_uint4(0, 0, 0, 0), n_b = make_uint4(0, 0, 0, 0);
+            if (c + 1 < NCH) slice_of(nt, c + 1, &pp_n, &nq_n);
+            else if (tl + 1 < my_tiles) slice_of(nt_next, 0, &pp_n, &nq_n);
+            if (nq_n > 0) n_a = __ldg(pp_n);
+            if (nq_n > 1) n_b = __ldg(pp_n + 32);
+
             const unsigned rep = (parity ? sBuf1 : sBuf0) + unsigned(lane & 7) * 16u;
             for (int q = 0; q < nq; ++q) {
                 const uint4 wq = w_a;
@@ -650,12 +647,7 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
                     }
                 }
             }
-            // look-ahead into the next (tile, chunk), issued before the barrier
-            nq = 0;
-            if (c + 1 < NCH) slice_of(nt, c + 1, &pp, &nq);
-            else if (tl + 1 < my_tiles) slice_of(nt_next, 0, &pp, &nq);
-            if (nq > 0) w_a = __ldg(pp);
-            if (nq > 1) w_b = __ldg(pp + 32);
+            pp = pp_n; nq = nq_n; w_a = n_a; w_b = n_b;
             if (c == NCH - 1 && KS > 1) {
 #pragma unroll
                 for (int i = 0; i < kTilePix; ++i)
@@ -665,31 +657,28 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
             parity ^= 1u;
         }
         // ---- the tile is complete: reduce the slices, dequantise, store --------------------------
-        AXC_BAR(kBarTile, (kComputeWarps + 1) * 32);
         {
             const int g = nt * GW + gl;
             const int j = g * 32 + lane;
-            if (g < P.L.G && j < P.Cout) {
-                const float t2 = __fmul_rn(P.m1, __ldg(bsum + j));
+            const bool live = g < P.L.G && j < P.Cout;
 #pragma unroll
-                for (int ii = 0; ii < PPW; ++ii) {
-                    const int i = ks * PPW + ii;
-                    int s = 0;
-                    if (KS > 1) {
+            for (int ii = 0; ii < PPW; ++ii) {
+                const int i = ks * PPW + ii;
+                int s = 0;
+                if (KS > 1) {
 #pragma unroll
-                        for (int k2 = 0; k2 < KS; ++k2)
-                            s += int(lds32(sRed + unsigned(((k2 * GW + gl) * kTilePix + i) * 32 + lane) * 4u));
-                    } else {
-                        s = acc[i];
-                    }
-                    const long long pix = m0 + i;
-                    if (pix < P.M) {
-                        const float a_sum = __uint_as_float(lds32(sAsum + unsigned((int(tl) & 1) * kTilePix + i) * 4u));
-                        const float t0 = __fmul_rn(float(s), P.s1s2);
-                        const float t1 = __fmul_rn(P.m2, a_sum);
-                        P.output[pix * P.Cout + j] = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), P.km1m2);
-                        if (P.acc_out) P.acc_out[pix * P.Cout + j] = s;
-                    }
+                    for (int k2 = 0; k2 < KS; ++k2)
+                        s += int(lds32(sRed + unsigned(((k2 * GW + gl) * kTilePix + i) * 32 + lane) * 4u));
+                } else {
+                    s = acc[i];
+                }
+                const long long pix = m0 + i;
+                const float a_sum = __shfl_sync(0xffffffffu, asum_lane, i);   // lane i holds pixel i's patch sum
+                if (live && pix < P.M) {
+                    const float t0 = __fmul_rn(float(s), P.s1s2);
+                    const float t1 = __fmul_rn(P.m2, a_sum);
+                    P.output[pix * P.Cout + j] = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), P.km1m2);
+                    if (P.acc_out) P.acc_out[pix * P.Cout + j] = s;
                 }
             }
 #pragma unroll
@@ -699,6 +688,91 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
         m0 = m0_next;
         nt = nt_next;
     }
+}
+
+// ------------------------------------------------------------------------------------------------
+// patch sums: aSum[p] = sum over the patch of output pixel p of the raw fp32 taps, added in K order
+// (ky, kx, c) like the reference (tf2/src/approx_nn_conv_kernels.cpp:272-295).  A block owns up to 64
+// consecutive output pixels of one output row; per filter row ky it stages the input row segment they
+// touch in shared memory (coalesced), then one thread per pixel walks its taps.  Out-of-image taps are
+// zeros in the reference; adding +0.0 never changes a sum that started at +0.0, so they are skipped.
+// When a whole row segment does not fit, the segment of one kx (and one channel chunk, for 1-wide
+// filters) is staged at a time; the order of additions is the same.
+// ------------------------------------------------------------------------------------------------
+constexpr int kPsPixels = 64;
+constexpr int kPsThreads = 128;
+constexpr int kPsFloats = 11 * 1024;   // 44 KiB of staging
+
+struct PatchSumParams {
+    const float *input;
+    float *asum;
+    int N, H, W, C, KH, KW, sh, sw, dh, dw, ph, pw, OH, OW;
+    int tiles_per_row;
+    int kx_group;     // KW (whole row segment staged) or 1
+    int cc;           // channels staged at a time
+    int ccp;          // shared-memory pixel stride (odd, to spread banks)
+    int vec;          // C % 4 == 0, 16-byte aligned input, cc % 4 == 0
+};
+
+__global__ void __launch_bounds__(kPsThreads) patch_sum_kernel(const PatchSumParams P)
+{
+    __shared__ float tile[kPsFloats];
+    const int tid = threadIdx.x;
+    long long b = blockIdx.x;
+    const int tr = int(b % P.tiles_per_row); b /= P.tiles_per_row;
+    const int oh = int(b % P.OH);
+    const int n = int(b / P.OH);
+    const int ow0 = tr * kPsPixels;
+    const int tp = min(kPsPixels, P.OW - ow0);
+    const int ix_base = ow0 * P.sw - P.pw;
+    float sum = 0.0f;
+    for (int ky = 0; ky < P.KH; ++ky) {
+        const int iy = oh * P.sh - P.ph + ky * P.dh;
+        if (iy < 0 || iy >= P.H) continue;                       // uniform over the block
+        const float *row = P.input + (((long long)n * P.H + iy) * P.W) * P.C;
+        for (int kx0 = 0; kx0 < P.KW; kx0 += P.kx_group) {
+            const int nkx = min(P.kx_group, P.KW - kx0);
+            const int ix_lo = ix_base + kx0 * P.dw;
+            const int span = (tp - 1) * P.sw + (nkx - 1) * P.dw + 1;   // input pixels staged
+            for (int c0 = 0; c0 < P.C; c0 += P.cc) {
+                const int ccn = min(P.cc, P.C - c0);
+                __syncthreads();
+                if (P.vec) {
+                    const int q4 = ccn >> 2;
+                    for (int i = tid; i < span * q4; i += kPsThreads) {
+                        const int x = i / q4, c4 = (i - x * q4) * 4;
+                        const int ix = ix_lo + x;
+                        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (ix >= 0 && ix < P.W) v = __ldg(reinterpret_cast<const float4 *>(row + (long long)ix * P.C + c0 + c4));
+                        float *d = tile + x * P.ccp + c4;
+                        d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+                    }
+                } else {
+                    for (int i = tid; i < span * ccn; i += kPsThreads) {
+                        const int x = i / ccn, c = i - x * ccn;
+                        const int ix = ix_lo + x;
+                        tile[x * P.ccp + c] = (ix >= 0 && ix < P.W) ? __ldg(row + (long long)ix * P.C + c0 + c) : 0.0f;
+                    }
+                }
+                __syncthreads();
+                if (tid < tp) {
+                    for (int kx = 0; kx < nkx; ++kx) {
+                        const float *src = tile + (tid * P.sw + kx * P.dw) * P.ccp;
+                        int c = 0;
+                        for (; c + 8 <= ccn; c += 8) {
+                            float v[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) v[e] = src[c + e];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) sum = __fadd_rn(sum, v[e]);
+                        }
+                        for (; c < ccn; ++c) sum = __fadd_rn(sum, src[c]);
+                    }
+                }
+            }
+        }
+    }
+    if (tid < tp) P.asum[((long long)n * P.OH + oh) * P.OW + ow0 + tid] = sum;
 }
 
 template <int GW>
@@ -760,11 +834,42 @@ int launch_plan(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, cons
     return AXC_OK;
 }
 
-int launch_dense_sched(const Geom &g, const Quant &q, const float *input, float *output, const unsigned char *plan,
-                       const PlanLayout &L, int32_t *acc_out, const DeviceInfo &di, cudaStream_t stream)
+int launch_patch_sums(const Geom &g, const float *input, float *asum, cudaStream_t stream)
+{
+    PatchSumParams S;
+    S.input = input; S.asum = asum;
+    S.N = g.N; S.H = g.H; S.W = g.W; S.C = g.C; S.KH = g.KH; S.KW = g.KW;
+    S.sh = g.sh; S.sw = g.sw; S.dh = g.dh; S.dw = g.dw; S.ph = g.ph; S.pw = g.pw; S.OH = g.OH; S.OW = g.OW;
+    S.tiles_per_row = (g.OW + kPsPixels - 1) / kPsPixels;
+    const int tp = g.OW < kPsPixels ? g.OW : kPsPixels;
+    auto odd = [](int v) { return v | 1; };
+    const long long full_span = (long long)(tp - 1) * g.sw + (long long)(g.KW - 1) * g.dw + 1;
+    if (full_span * odd(g.C) <= kPsFloats) {
+        S.kx_group = g.KW; S.cc = g.C;                      // the whole row segment of a filter row
+    } else {
+        S.kx_group = 1;
+        const long long span1 = (long long)(tp - 1) * g.sw + 1;
+        long long cc = kPsFloats / span1 - 1;               // room for the odd stride
+        if (cc >= g.C) cc = g.C;
+        else cc &= ~3ll;
+        if (cc < 4) return AXC_INVALID_ARGUMENT;            // stride > ~170: no layer of the reference's nets
+        S.cc = int(cc);
+    }
+    S.ccp = odd(S.cc);
+    S.vec = (g.C % 4 == 0) && (S.cc % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
+    const long long blocks = (long long)g.N * g.OH * S.tiles_per_row;
+    patch_sum_kernel<<<unsigned(blocks), kPsThreads, 0, stream>>>(S);
+    AXC_CUDA(cudaGetLastError());
+    count_launch();
+    return AXC_OK;
+}
+
+int launch_dense_sched(const Geom &g, const Quant &q, const float *input, const float *asum, float *output,
+                       const unsigned char *plan, const PlanLayout &L, int32_t *acc_out, const DeviceInfo &di,
+                       cudaStream_t stream)
 {
     SchedParams P;
-    P.plan = plan; P.L = L; P.input = input; P.output = output; P.acc_out = acc_out;
+    P.plan = plan; P.L = L; P.input = input; P.asum = asum; P.output = output; P.acc_out = acc_out;
     P.N = g.N; P.H = g.H; P.W = g.W; P.C = g.C; P.KH = g.KH; P.KW = g.KW; P.Cout = g.Cout;
     P.sh = g.sh; P.sw = g.sw; P.dh = g.dh; P.dw = g.dw; P.ph = g.ph; P.pw = g.pw; P.OH = g.OH; P.OW = g.OW;
     P.K = g.K; P.M = g.M; P.tiles_n = 0; P.tiles_total = 0;
@@ -775,6 +880,9 @@ int launch_dense_sched(const Geom &g, const Quant &q, const float *input, float 
         P.km1m2 = t3;
     }
     P.vec_ok = (g.C % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
+    // n / d == (n * magic) >> 40 holds while n * d < 2^40; launch_dense keeps shapes beyond that on the common-K kernel
+    P.magic_c = ((1ull << 40) + unsigned(g.C) - 1) / unsigned(g.C);
+    P.magic_kw = ((1ull << 40) + unsigned(g.KW) - 1) / unsigned(g.KW);
     if (L.G <= 1) return launch_sched_variant<1>(P, di, stream);
     if (L.G <= 2) return launch_sched_variant<2>(P, di, stream);
     if (L.G <= 4) return launch_sched_variant<4>(P, di, stream);
