@@ -116,6 +116,29 @@ int axc_depthwise_conv2d_forward(axc_table *table, const axc_conv_desc *desc,
                                  float *output, void *workspace, size_t workspace_bytes,
                                  const axc_debug_out *debug, int device, void *stream);
 
+/* Depthwise forward for callers that must not allocate device memory - an op kernel inside a framework
+ * whose allocator has reserved the whole GPU up front (a plugin's own cudaMalloc then fails or steals from
+ * the pool), or a serving loop that cannot afford cudaMalloc's implicit device-wide synchronisation.  It has
+ * no counterpart in the reference.  Same arithmetic and results as axc_depthwise_conv2d_forward, but no
+ * workspace argument: the scratch is a 1 MiB array that every GPU using this library carries until the
+ * process exits.  Limits and rules:
+ *   - the scratch a call needs - what axc_depthwise_conv2d_workspace_bytes() reports: 4 bytes per filter
+ *     element, 4 bytes per output channel and under 1 KiB of padding - must fit in 1 MiB (3x3 filters: up to
+ *     about 26 000 channels), else AXC_INVALID_ARGUMENT; nothing is launched;
+ *   - the table replica must already be on `device`: call axc_table_ensure_device() beforehand (that call
+ *     allocates 128 KiB); otherwise AXC_INTERNAL;
+ *   - the first call on a device looks up the array's device address; make that call before any stream
+ *     capture starts;
+ *   - all calls on a device share the one array and each call overwrites what the previous one left, so
+ *     two calls may not be in flight on the same GPU at the same time (different streams or threads): they
+ *     would race on the scratch.  Nothing in it has to be cleared by the caller: every call rewrites the
+ *     part it reads, including the status word, before using it.
+ * No cudaMalloc/cudaFree or other allocating routine is called. */
+int axc_depthwise_conv2d_forward_noalloc(axc_table *table, const axc_conv_desc *desc,
+                                         const float *input, const float *filter,
+                                         float in_min, float in_max, float f_min, float f_max,
+                                         float *output, int device, void *stream);
+
 /* ---- quantisation parameters: Nudge + UpdateVarQuantProps
  *      (tf2/src/approx_ops_types.h:29-49, 135-152).  out3 = {scale, 1/scale, nudged_min}. */
 int axc_quant_props(float min_value, float max_value, float out3[3]);

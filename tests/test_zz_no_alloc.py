@@ -1,0 +1,58 @@
+"""GPU: the depthwise entry point that allocates nothing (scratch in a fixed array inside the library)
+against the ordinary depthwise entry point, both called through the C ABI.
+
+It is for callers that cannot allocate device memory themselves - an op kernel inside a framework whose
+allocator owns the whole GPU, or a latency-critical loop that must not hit cudaMalloc's device-wide
+synchronisation.  The file name sorts last on purpose, so a run that stops at the first failure has
+already executed every other test."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def test_noalloc_depthwise_matches_workspace_entry_point(built):
+    import torch
+    import tf_approximate_b200 as ax
+    from tf_approximate_b200 import _lib
+    assert torch.cuda.is_available()
+    L = _lib.load()
+    dev = torch.device("cuda", 0)
+    table = ax.Table(array=ax.noisy_table(3999))
+    table.ensure_device(0)                       # the only allocation: done by a caller who may allocate
+
+    rng = np.random.Generator(np.random.PCG64(4242))
+    for call, (n, h, w, c, k, stride) in enumerate([(2, 20, 20, 96, 3, 1), (1, 17, 19, 40, 3, 2)]):
+        x = torch.from_numpy(rng.uniform(0, 2, (n, h, w, c)).astype(np.float32)).to(dev)
+        f = torch.from_numpy(rng.normal(0, 0.3, (k, k, c, 1)).astype(np.float32)).to(dev)
+        mm = (0.0, 2.0, float(f.min()), float(f.max()))
+        d = _lib.ConvDesc(n, h, w, c, k, k, c, 1, stride, stride, 1, 1, 0, 0)
+        dims = (C.c_int64 * 4)()
+        assert L.axc_depthwise_conv2d_output_dims(C.byref(d), dims) == 0
+        want = torch.empty(tuple(dims), dtype=torch.float32, device=dev)
+        got = torch.full(tuple(dims), float("nan"), dtype=torch.float32, device=dev)
+        wsz = C.c_size_t()
+        assert L.axc_depthwise_conv2d_workspace_bytes(C.byref(d), C.byref(wsz)) == 0
+        ws = torch.empty(wsz.value, dtype=torch.uint8, device=dev)
+        stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        st = L.axc_depthwise_conv2d_forward(table.handle, C.byref(d), x.data_ptr(), f.data_ptr(), *mm,
+                                            want.data_ptr(), ws.data_ptr(), ws.numel(), None, 0, stream)
+        assert st == 0
+        st = L.axc_depthwise_conv2d_forward_noalloc(table.handle, C.byref(d), x.data_ptr(), f.data_ptr(), *mm,
+                                                    got.data_ptr(), 0, stream)
+        assert st == 0, L.axc_status_string(st)
+        torch.cuda.synchronize()
+        # integer table sums and tap-order fp32 sums: the two entry points agree bit for bit
+        assert torch.equal(got.view(torch.int32), want.view(torch.int32)), "call %d differs" % call
+
+    # a filter beyond the fixed scratch is refused before anything is launched
+    big = _lib.ConvDesc(1, 8, 8, 40000, 3, 3, 40000, 1, 1, 1, 1, 1, 0, 0)   # 1.6 MB of scratch
+    assert L.axc_depthwise_conv2d_forward_noalloc(table.handle, C.byref(big), 256, 256, 0.0, 1.0, 0.0, 1.0, 256,
+                                                  0, None) == 3
+    # a table that was never uploaded to the device is refused too (uploading would allocate)
+    cold = ax.Table(array=ax.exact_table())
+    small = _lib.ConvDesc(1, 8, 8, 8, 3, 3, 8, 1, 1, 1, 1, 1, 0, 0)
+    assert L.axc_depthwise_conv2d_forward_noalloc(cold.handle, C.byref(small), 256, 256, 0.0, 1.0, 0.0, 1.0, 256,
+                                                  0, None) == 13

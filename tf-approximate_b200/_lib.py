@@ -11,7 +11,7 @@ SYMBOLS = [
     "axc_table_destroy", "axc_table_host_data", "axc_table_ensure_device",
     "axc_conv2d_output_dims", "axc_depthwise_conv2d_output_dims",
     "axc_conv2d_workspace_bytes", "axc_depthwise_conv2d_workspace_bytes",
-    "axc_conv2d_forward", "axc_depthwise_conv2d_forward",
+    "axc_conv2d_forward", "axc_depthwise_conv2d_forward", "axc_depthwise_conv2d_forward_noalloc",
     "axc_quant_props", "axc_status_string", "axc_last_cuda_error", "axc_launch_count",
 ]
 
@@ -53,6 +53,8 @@ def load():
     L.axc_depthwise_conv2d_workspace_bytes.argtypes = [C.POINTER(ConvDesc), C.POINTER(C.c_size_t)]
     L.axc_conv2d_forward.argtypes = fwd
     L.axc_depthwise_conv2d_forward.argtypes = fwd
+    L.axc_depthwise_conv2d_forward_noalloc.argtypes = [C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.c_float,
+                                                       C.c_float, C.c_float, C.c_float, C.c_void_p, C.c_int, C.c_void_p]
     L.axc_quant_props.argtypes = [C.c_float, C.c_float, C.POINTER(C.c_float)]
     L.axc_status_string.argtypes = [C.c_int]
     L.axc_status_string.restype = C.c_char_p

@@ -199,6 +199,13 @@ const uint16_t *table_device_ptr(axc_table *t, int device, int *status)
     return p;
 }
 
+const uint16_t *table_device_ptr_if_resident(axc_table *t, int device)
+{
+    std::lock_guard<std::mutex> lock(t->mu);
+    if (device < 0 || size_t(device) >= t->dev.size()) return nullptr;
+    return t->dev[size_t(device)];
+}
+
 int device_info(int device, DeviceInfo *out)
 {
     static std::mutex mu;

@@ -10,6 +10,8 @@
 // image row and keeps the 3x3 input window in registers, so an input element is read once
 // per output row it touches.  The table lives in shared memory in the two-plane layout of
 // the dense kernel (plane p at 65536*(1+p), byte a*256 + 2*(b&127)).
+#include <mutex>
+
 #include "axc_internal.h"
 
 namespace axc {
@@ -300,4 +302,61 @@ int launch_depthwise(const uint16_t *lut_dev, const Geom &g, const Quant &q, con
     return launch_dw(depthwise_generic_kernel, P, di, stream);
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Entry point that allocates nothing: the scratch of the depthwise path (filter program words, filter
+// sums, status word) lives in a file-scope device array instead of a caller-provided workspace.
+// ---------------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticScratchBytes = size_t(1) << 20;   // 1 MiB per GPU that loads the library
+static __device__ __align__(256) unsigned char g_dw_static_scratch[kStaticScratchBytes];
+
+// Device address of g_dw_static_scratch on `device` (which must be current).  In host code the array's name
+// is only a handle for the runtime, not an address a kernel could use, so the address is asked for once per
+// device and remembered.
+int static_scratch_address(int device, void **out)
+{
+    static std::mutex mu;
+    static void *addr[64] = {};
+    if (device < 0 || device >= 64) return AXC_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!addr[device]) {
+        void *p = nullptr;
+        AXC_CUDA(cudaGetSymbolAddress(&p, g_dw_static_scratch));
+        addr[device] = p;
+    }
+    *out = addr[device];
+    return AXC_OK;
+}
+
+}  // namespace
+
 }  // namespace axc
+
+extern "C" int axc_depthwise_conv2d_forward_noalloc(axc_table *table, const axc_conv_desc *desc, const float *input,
+                                                    const float *filter, float in_min, float in_max, float f_min,
+                                                    float f_max, float *output, int device, void *stream)
+{
+    using namespace axc;
+    if (!table || !desc) return AXC_INVALID_ARGUMENT;
+    Geom g;
+    int rc = resolve_geometry(desc, true, &g);
+    if (rc) return rc;
+    if (g.M * (long long)g.C * g.Cout == 0) return AXC_OK;
+    if (!input || !filter || !output) return AXC_INVALID_ARGUMENT;
+    // the scratch this shape needs must fit the fixed array
+    if (depthwise_workspace(g.K, g.C, g.Cout).total > kStaticScratchBytes) return AXC_INVALID_ARGUMENT;
+    const uint16_t *lut = table_device_ptr_if_resident(table, device);
+    if (!lut) return AXC_INTERNAL;   // axc_table_ensure_device(table, device) has to run first: it allocates
+    int prev = 0;
+    AXC_CUDA(cudaGetDevice(&prev));
+    if (prev != device) AXC_CUDA(cudaSetDevice(device));
+    void *scratch = nullptr;
+    rc = static_scratch_address(device, &scratch);
+    if (rc == AXC_OK) {
+        const Quant q = make_quant(in_min, in_max, f_min, f_max);
+        rc = launch_depthwise(lut, g, q, input, filter, output, scratch, nullptr, device, cudaStream_t(stream));
+    }
+    if (prev != device) cudaSetDevice(prev);
+    return rc;
+}

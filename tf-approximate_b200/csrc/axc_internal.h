@@ -45,6 +45,8 @@ void count_launch(int n = 1);
 
 // Device replica of a table (native [a][b] order, 65536 uint16).
 const uint16_t *table_device_ptr(axc_table *t, int device, int *status);
+// The replica on `device` if it has been uploaded already, else NULL.  Never allocates.
+const uint16_t *table_device_ptr_if_resident(axc_table *t, int device);
 // Process-unique id of a table handle (tables are immutable after creation).
 unsigned table_uid(const axc_table *t);
 
