@@ -181,12 +181,10 @@ def run_gpu(args):
 
     # Frozen per-layer input ranges: calibrated on rank 0's batch, identical on every rank, so that
     # no collective sits on the compute path.
+    from tf_approximate_b200 import parallel
     if rank == 0:
         runner.calibrate(x)
-    if world > 1:
-        box = [runner.in_ranges]
-        dist.broadcast_object_list(box, src=0)
-        runner.in_ranges = box[0]
+    runner.in_ranges = parallel.broadcast_ranges(runner.in_ranges, src=0)
     torch.cuda.synchronize()
 
     def barrier():
