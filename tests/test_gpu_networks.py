@@ -1,0 +1,71 @@
+"""GPU: the five benchmark configurations as layer stacks.  Every convolution of the network is run on the
+GPU and re-run by the CPU checker ON THE SAME INPUT TENSOR (the GPU's own activation of the previous layer),
+so each layer is compared bit for bit - int32 accumulators and fp32 output - without errors compounding.
+Spatial size and batch are reduced so that the checker finishes in seconds; channel counts, kernel sizes,
+strides and table kinds are those of the configurations."""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _run_network(kind, hw, batch, table_for_layer, seed_cfg):
+    import torch
+    import tf_approximate_b200 as ax
+    from tf_approximate_b200 import workloads as W
+    net = W.Network(kind, hw)
+    filters = W.make_filters(net.convs, 2000 + 100 * seed_cfg)
+    tables = [table_for_layer(i) for i in range(len(net.convs))]
+    handles = [ax.Table(array=t) for t in tables]
+    x0 = torch.from_numpy(W.make_input(batch, net.hw, net.in_channels, 1000 + seed_cfg)).cuda()
+    checked = []
+
+    def conv(i, x):
+        spec, _ = net.convs[i]
+        f = filters[i]
+        lo, hi = float(x.min()), float(x.max())
+        mm = (lo, hi, float(f.min()), float(f.max()))
+        fn = ax.approx_depthwise_conv2d_with_min_max_vars if spec.depthwise else ax.approx_conv2d_with_min_max_vars
+        y, dbg = fn(x, torch.from_numpy(f).cuda(), *mm, [1, spec.stride, spec.stride, 1], 8, handles[i], "SAME",
+                    debug=True)
+        xn = x.cpu().numpy()
+        d = O.desc(xn.shape[0], xn.shape[1], xn.shape[2], xn.shape[3], spec.k, spec.k, f.shape[3],
+                   (spec.stride, spec.stride), (1, 1), "SAME")
+        if spec.depthwise:
+            ref = O.depthwise_conv2d(d, tables[i], xn, f, *mm)
+        else:
+            ref = O.conv2d(d, tables[i], xn, f, *mm, want=("out_exact", "acc"))
+        assert np.array_equal(dbg["acc"].cpu().numpy(), ref["acc"]), "layer %d (%s): accumulators" % (i, spec.name)
+        assert np.array_equal(y.cpu().numpy().view(np.uint32), ref["out_exact"].view(np.uint32)), \
+            "layer %d (%s): fp32 output" % (i, spec.name)
+        checked.append(spec.name)
+        return y
+
+    out = net.forward(x0, conv, torch.relu, W.torch_maxpool3s2)
+    assert len(checked) == len(net.convs)
+    assert torch.isfinite(out).all()
+    return out
+
+
+def test_config3_resnet20_layers(built):
+    """CIFAR ResNet-20: 3x3 convs, 16/32/64 channels, stride 2 at the stage transitions, a noisy table per layer."""
+    import tf_approximate_b200 as ax
+    _run_network("resnet20", 32, 4, lambda i: ax.noisy_table(3000 + 300 + i), 3)
+
+
+def test_config4_resnet50_layers(built):
+    """ImageNet ResNet-50 layer shapes (7x7/2 stem, 1x1/3x3/1x1 bottlenecks, widths 64..2048), truncated table;
+    64x64 input instead of 224x224."""
+    import tf_approximate_b200 as ax
+    t = ax.truncated_table()
+    _run_network("resnet50", 64, 1, lambda i: t, 4)
+
+
+def test_config5_depthwise_separable_stack(built):
+    """3x3 depthwise (stride 1 and 2, 32..384 channels) interleaved with 1x1 pointwise convs, noisy table;
+    28x28 input instead of 112x112."""
+    import tf_approximate_b200 as ax
+    t = ax.noisy_table(3000 + 500)
+    _run_network("mobilenet_stack", 28, 2, lambda i: t, 5)
