@@ -26,7 +26,7 @@ namespace axc {
 namespace {
 
 constexpr unsigned kLutBase = 65536u;          // table planes at 64 KiB and 128 KiB
-constexpr unsigned kBuf1Base = 196608u;        // activation buffer 1 starts with the zero row
+constexpr unsigned kBuf1Base = 196608u;        // 32 zero words (one per bank), then activation buffers
 constexpr unsigned kWindowEnd = 233472u;       // 228 KiB shared window of an SM
 constexpr int kComputeWarps = 8;
 constexpr int kLoaderWarps = 4;
@@ -172,9 +172,16 @@ __global__ void plan_sigma_kernel(const uint8_t *__restrict__ qf, long long coun
 // plan_build.  blockIdx.x < G*NCH: schedule of (group, chunk), one warp.  Then 256 blocks that write the
 // permuted table image, then ceil(Cout/32) blocks for the filter sums.
 //
-// Program word of a step:  byte0 = 2*(slot&127)  byte1 = row >> 8  byte2 = 1 + (slot>>7)  byte3 = row & 255
-// with row = 1 + (l - chunk start); an idle lane gets byte0 = 4*bank, byte2 = 3, row 0 (the zero row), which
-// addresses one of 32 zero words, one per bank.
+// A step assigns to every lane (= output channel of the group) one K element of the chunk such that
+//   (1) the 32 table columns looked up lie in 32 different banks, and
+//   (2) within each quarter warp the 8 activation rows read (16 bytes each, one LDS.128) lie in 8
+//       different 16-byte bank groups, i.e. have different (row mod 8);
+// greedy: banks by remaining load, largest first; among the lanes that still have an element in the bank
+// with an admissible row class, the lane with the most remaining elements.  Idle lanes look up one of 32
+// zero words (one per bank) through one of 8 all-zero activation rows (one per row class).
+//
+// Program word of a step:  byte0 = 2*(slot&127)  byte2 = 1 + (slot>>7)   {byte1:byte3} = 16 * row
+// with row = 8 + (l - chunk start); idle: byte0 = 4*bank, byte2 = 3, row = an unused row class 0..7.
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(32) plan_build_kernel(const float *__restrict__ filter, const uint16_t *__restrict__ lut,
                                                         unsigned char *__restrict__ plan, PlanLayout L, int K, int Cout)
@@ -216,9 +223,13 @@ __global__ void __launch_bounds__(32) plan_build_kernel(const float *__restrict_
         return;
     }
 
-    __shared__ unsigned short cnt[32][33];      // items of lane x in bank y still to schedule
-    __shared__ unsigned short pos[32][33];      // next entry of `order` for (lane, bank)
-    __shared__ unsigned short order[32][kMaxChunk];  // chunk-local l, sorted by bank, per lane
+    // dynamic shared memory: per lane, the chunk's elements sorted by (bank, row class), and for each of the
+    // 256 (bank, class) runs a cursor and an end
+    extern __shared__ __align__(16) unsigned char sched_smem[];
+    unsigned short *order = reinterpret_cast<unsigned short *>(sched_smem);   // [32][KC]
+    unsigned short *pos = order + 32 * L.KC;                                  // [32][256] next element of the run
+    unsigned short *end = pos + 32 * 256;                                     // [32][256] one past its last element
+    unsigned char *rmask = reinterpret_cast<unsigned char *>(end + 32 * 256); // [32][32]  classes with elements left, per bank
     __shared__ int bank_at_rank[32];
 
     const int g = int(blockIdx.x) / L.NCH, c = int(blockIdx.x) % L.NCH;
@@ -226,29 +237,41 @@ __global__ void __launch_bounds__(32) plan_build_kernel(const float *__restrict_
     const int kc = min(L.KC, K - l_base);
     const int j = g * 32 + lane;
     const bool live = j < Cout;
+    unsigned short *my_order = order + lane * L.KC;
+    unsigned short *my_pos = pos + lane * 256;
+    unsigned short *my_end = end + lane * 256;
+    unsigned char *my_rmask = rmask + lane * 32;
 
-    for (int b = 0; b < 32; ++b) cnt[lane][b] = 0;
+    for (int key = 0; key < 256; ++key) my_pos[key] = 0;   // histogram first
     if (live)
-        for (int i = 0; i < kc; ++i) cnt[lane][slot_bank(sigma[qf[(size_t)(l_base + i) * Cout + j]])]++;
+        for (int i = 0; i < kc; ++i) my_pos[slot_bank(sigma[qf[(size_t)(l_base + i) * Cout + j]]) * 8 + (i & 7)]++;
     {
         int run = 0;
-        for (int b = 0; b < 32; ++b) { pos[lane][b] = (unsigned short)run; run += cnt[lane][b]; }
-    }
-    if (live) {
-        unsigned short fill[32];
-#pragma unroll
-        for (int b = 0; b < 32; ++b) fill[b] = 0;
-        for (int i = 0; i < kc; ++i) {
-            const int b = slot_bank(sigma[qf[(size_t)(l_base + i) * Cout + j]]);
-            // position = start of the bank's run + entries already placed (kept in local memory)
-            order[lane][pos[lane][b] + fill[b]] = (unsigned short)i;
-            fill[b]++;
+        for (int key = 0; key < 256; ++key) {
+            const int n = my_pos[key];
+            my_pos[key] = (unsigned short)run;
+            my_end[key] = (unsigned short)run;     // insertion cursor of the second pass
+            run += n;
         }
     }
+    if (live)
+        for (int i = 0; i < kc; ++i) {
+            const int key = slot_bank(sigma[qf[(size_t)(l_base + i) * Cout + j]]) * 8 + (i & 7);
+            my_order[my_end[key]] = (unsigned short)i;
+            my_end[key]++;
+        }
+    for (int b = 0; b < 32; ++b) {
+        unsigned m = 0;
+        for (int r = 0; r < 8; ++r)
+            if (my_pos[b * 8 + r] < my_end[b * 8 + r]) m |= 1u << r;
+        my_rmask[b] = (unsigned char)m;
+    }
     __syncwarp();
+
     int lane_rem = live ? kc : 0;
-    int load = 0;                                  // lane b: remaining items of bank b over all lanes
-    for (int x = 0; x < 32; ++x) load += cnt[x][lane];
+    int load = 0;                                  // lane b: remaining elements of bank b over all lanes
+    for (int x = 0; x < 32; ++x)
+        for (int r = 0; r < 8; ++r) load += int(end[x * 256 + lane * 8 + r]) - int(pos[x * 256 + lane * 8 + r]);
     int total = 0;
     {
         int v = lane_rem;
@@ -259,6 +282,7 @@ __global__ void __launch_bounds__(32) plan_build_kernel(const float *__restrict_
 
     uint4 *prog = reinterpret_cast<uint4 *>(plan + L.prog_off) + (size_t)blockIdx.x * L.sqcap * 32;
     const int step_cap = L.sqcap * 4;
+    const int quarter = lane >> 3;
     uint32_t wq[4] = {0, 0, 0, 0};
     int step = 0;
     bool overflow = false;
@@ -273,45 +297,54 @@ __global__ void __launch_bounds__(32) plan_build_kernel(const float *__restrict_
         bank_at_rank[rank] = lane;
         __syncwarp();
         unsigned used = 0, taken = 0;
+        unsigned used_rho = 0;                     // byte q: row classes taken in quarter q
         int my_bank = -1, my_l = 0;
         for (int r = 0; r < 32; ++r) {
             const int b = bank_at_rank[r];
             if (__shfl_sync(0xffffffffu, load, b) == 0) break;
-            const bool has = cnt[lane][b] > 0 && !((used >> lane) & 1u);
+            const unsigned free_rho = unsigned(my_rmask[b]) & ~((used_rho >> (8 * quarter)) & 0xFFu);
+            const bool has = free_rho != 0u && !((used >> lane) & 1u);
             const unsigned key = has ? ((unsigned(lane_rem) << 5) | unsigned(31 - lane)) : 0u;
             const unsigned best = __reduce_max_sync(0xffffffffu, key);
             if (best == 0u) continue;
             const int chosen = 31 - int(best & 31u);
+            int rho = 0;
             if (lane == chosen) {
-                cnt[lane][b]--;
-                my_l = order[lane][pos[lane][b]];
-                pos[lane][b]++;
+                rho = __ffs(int(free_rho)) - 1;
+                const int key2 = b * 8 + rho;
+                my_l = my_order[my_pos[key2]];
+                if (++my_pos[key2] == my_end[key2]) my_rmask[b] = (unsigned char)(my_rmask[b] & ~(1u << rho));
                 my_bank = b;
                 lane_rem--;
             }
+            rho = __shfl_sync(0xffffffffu, rho, chosen);
             if (lane == b) load--;
             used |= 1u << chosen;
             taken |= 1u << b;
+            used_rho |= 1u << (8 * (chosen >> 3) + rho);
             total--;
         }
         __syncwarp();
         uint32_t w;
         if (my_bank >= 0) {
             const int s = sigma[qf[(size_t)(l_base + my_l) * Cout + j]];
-            const int row = my_l + 1;
-            w = uint32_t(2 * (s & 127)) | (uint32_t(row >> 8) << 8) | (uint32_t(1 + (s >> 7)) << 16) | (uint32_t(row & 255) << 24);
+            const unsigned rowoff = unsigned(my_l + 8) * 16u;
+            w = uint32_t(2 * (s & 127)) | ((rowoff >> 8) << 8) | (uint32_t(1 + (s >> 7)) << 16) | ((rowoff & 255u) << 24);
         } else {
             const unsigned idle = ~used;
             const int k = __popc(idle & ((1u << lane) - 1u));
             const int bank = __fns(~taken, 0, k + 1);   // k-th bank nobody looks up in this step
-            w = uint32_t(4 * bank) | (3u << 16);
+            const unsigned mine = (used_rho >> (8 * quarter)) & 0xFFu;
+            const int rho = __ffs(int(~mine & 0xFFu)) - 1;   // a row class no active lane of the quarter reads
+            const unsigned rowoff = unsigned(rho) * 16u;
+            w = uint32_t(4 * bank) | (3u << 16) | (rowoff << 24);
         }
         wq[step & 3] = w;
         if ((step & 3) == 3) prog[(size_t)(step >> 2) * 32 + lane] = make_uint4(wq[0], wq[1], wq[2], wq[3]);
         ++step;
     }
     if (step & 3) {
-        for (int e = step & 3; e < 4; ++e) wq[e] = uint32_t(4 * lane) | (3u << 16);
+        for (int e = step & 3; e < 4; ++e) wq[e] = uint32_t(4 * lane) | (3u << 16) | (uint32_t((lane & 7) * 16) << 24);
         prog[(size_t)(step >> 2) * 32 + lane] = make_uint4(wq[0], wq[1], wq[2], wq[3]);
     }
     if (lane == 0) {
@@ -334,7 +367,7 @@ struct SchedParams {
     int sh, sw, dh, dw, ph, pw, OH, OW, K;
     long long M;
     int tiles_n;              // channel tiles of 32*GW channels
-    long long tiles_total;
+    long long tiles_total;    // pixel tile groups x channel tiles
     float in_off, in_inv, s1s2, m1, m2, km1m2;
     int vec_ok;
     unsigned long long magic_c, magic_kw;   // ceil(2^40 / C), ceil(2^40 / KW): n / d == (n * magic) >> 40 for n*d < 2^40
@@ -347,21 +380,22 @@ __device__ __forceinline__ int fast_div(int n, unsigned long long magic)
 
 // Named barriers of dense_sched_kernel (barrier 0 is used once, after the table fill).
 #define AXC_BAR(id, count) asm volatile("bar.sync %0, %1;" ::"n"(id), "n"(count) : "memory")
-constexpr int kBarLoad = 1;   // loaders: byte staging complete
-constexpr int kBarIter = 2;   // consumers + loaders: next activation buffer complete, current one released
-constexpr int kBarEpi = 3;    // consumers: reduction scratch released
+constexpr int kBarLoad = 1;   // loaders: pixel geometry of the tile group published
+constexpr int kBarIter = 2;   // consumers + loaders: next activation buffers complete, current ones released
 
-// GW = channel groups per tile (tile = 16 pixels x 32*GW channels).
-// Warps 0..7  "consumers": GW groups x (8/GW) slices of every schedule; nothing but lookups.
-// Warps 8..11 "loaders": prepare the activation rows of the next (tile, chunk) while the consumers work on
-//             the current one: gather + quantise into a byte staging area, then copy every K row 8 times
-//             side by side into the other activation buffer.
+// Tile group = NT pixel tiles of 16 pixels x (32*GW) channels, NT = (8/GW) * NTW.
+// Warps 0..7  "consumers": warp w serves channel group w % GW and the NTW pixel tiles (w / GW)*NTW + i; it walks
+//             the whole schedule of its (group, chunk) and reuses every program word for its NTW tiles.
+// Warps 8..11 "loaders": gather + quantise the activation rows of the next (tile group, chunk) into the other
+//             set of buffers while the consumers work.  An activation buffer is [8 zero rows + KC rows][16 pixel
+//             bytes]; the schedule guarantees that the 8 rows a quarter warp reads in one LDS.128 fall into 8
+//             different 16-byte bank groups.
 // The patch sums come from patch_sum_kernel, which runs before this kernel.
-template <int GW>
+template <int GW, int NTW>
 __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const SchedParams P)
 {
-    constexpr int KS = kComputeWarps / GW;           // schedule slices per group
-    constexpr int PPW = kTilePix / KS;               // pixels a warp finalises
+    constexpr int SLOTS = kComputeWarps / GW;        // pixel-tile slots
+    constexpr int NT = SLOTS * NTW;                  // pixel tiles per tile group
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const PlanHeader *hdr = reinterpret_cast<const PlanHeader *>(P.plan);
     if (hdr->fallback != 0) return;                  // the common-K kernel takes this call
@@ -369,36 +403,36 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
     const unsigned dyn0 = (unsigned)__cvta_generic_to_shared(smem_raw);
     unsigned dyn_size;
     asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
-    // staging below the table: buffer 0 (zero row + KC rows), byte staging, reduction scratch
     const int KC = P.L.KC;
-    unsigned cur = (dyn0 + 127u) & ~127u;
-    const unsigned sBuf0 = cur;              cur += unsigned(KC + 1) * 128u;
-    const unsigned sStage = cur;             cur += unsigned(KC) * 16u;
-    const unsigned sRed = cur;               cur += kComputeWarps * kTilePix * 32u * 4u;
-    // tap table for inputs whose channel count is not a multiple of 4 (scalar gathers): per K element the
-    // element offset of the tap relative to the patch origin and its (dy, dx), so that the gather loops need
-    // no divisions
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // small tables below the table planes, then as many activation buffers as fit; the rest above the planes
+    unsigned cur = (dyn0 + 15u) & ~15u;
+    const unsigned sGeo = cur;               cur += unsigned(NT) * kTilePix * 16u;
     const bool tap_table = !P.vec_ok && P.K <= kTapTableMax;
     const unsigned sTap = cur;               cur += tap_table ? unsigned(P.K) * 8u : 0u;
-    // schedule lengths of every (group, chunk), so that the consumers' look-ahead does not wait on global memory
     const int n_sched = P.L.G * P.L.NCH;
     const bool steps_in_smem = n_sched <= kStepsInSmemMax;
     const unsigned sSteps = cur;             cur += steps_in_smem ? unsigned(n_sched) * 4u : 0u;
-    const unsigned sBuf1 = kBuf1Base;        // its row 0 is the zero-word row
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (cur > kLutBase || sBuf1 + unsigned(KC + 1) * 128u > kWindowEnd || dyn0 + dyn_size < kWindowEnd) {
+    cur = (cur + 127u) & ~127u;
+    const unsigned buf_bytes = unsigned(KC + 8) * 16u;
+    const unsigned sBufA = cur;
+    const int n_a = cur < kLutBase ? int((kLutBase - cur) / buf_bytes) : 0;
+    const unsigned sBufB = kBuf1Base + 128u;         // after the 32 zero words
+    const int n_b = int((kWindowEnd - sBufB) / buf_bytes);
+    if (cur > kLutBase || n_a + n_b < 2 * NT || dyn0 + dyn_size < kWindowEnd) {
         if (tid == 0) atomicExch(const_cast<int *>(&hdr->status), 2);
         return;
     }
+    auto buf_addr = [&](int k) -> unsigned {          // k = parity * NT + tile
+        return k < n_a ? sBufA + unsigned(k) * buf_bytes : sBufB + unsigned(k - n_a) * buf_bytes;
+    };
 
-    // table image (already permuted and in plane layout) and the two zero rows
+    // table image (already permuted and in plane layout), zero words, zero rows, small tables
     {
         const uint4 *src = reinterpret_cast<const uint4 *>(P.plan + P.L.lut_off);
         for (int i = tid; i < 8192; i += kSchedThreads) sts128(kLutBase + unsigned(i) * 16u, __ldg(src + i));
-        if (tid < 8) {
-            sts128(sBuf0 + tid * 16, make_uint4(0, 0, 0, 0));
-            sts128(sBuf1 + tid * 16, make_uint4(0, 0, 0, 0));
-        }
+        if (tid < 8) sts128(kBuf1Base + tid * 16, make_uint4(0, 0, 0, 0));
+        for (int i = tid; i < 2 * NT * 8; i += kSchedThreads) sts128(buf_addr(i >> 3) + unsigned(i & 7) * 16u, make_uint4(0, 0, 0, 0));
         if (steps_in_smem) {
             const int *sq = reinterpret_cast<const int *>(P.plan + P.L.steps_off);
             for (int i = tid; i < n_sched; i += kSchedThreads) sts32(sSteps + unsigned(i) * 4u, unsigned(__ldg(sq + i)));
@@ -418,174 +452,165 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
     }
     __syncthreads();
 
-    // one scalar tap through the table: value of K element l for the patch at (iy0, ix0, base)
-    auto tap_value = [&](int l, int iy0, int ix0, long long base) -> float {
-        unsigned off, dd;
-        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(off), "=r"(dd) : "r"(sTap + unsigned(l) * 8u));
-        const unsigned iy = unsigned(iy0 + int(dd & 0xFFFFu)), ix = unsigned(ix0 + int(dd >> 16));
-        return (iy < unsigned(P.H) && ix < unsigned(P.W)) ? __ldg(P.input + base + int(off)) : 0.0f;
-    };
-
     const int NCH = P.L.NCH;
-    const long long my_tiles = P.tiles_total > blockIdx.x ? (P.tiles_total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const long long my_groups = P.tiles_total > blockIdx.x ? (P.tiles_total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
-    // tile number tl of this CTA -> first pixel and channel tile
-    auto tile_coords = [&](long long tl, long long *m0, int *nt) {
+    // tile group number tl of this CTA -> first pixel and channel tile
+    auto group_coords = [&](long long tl, long long *m0, int *nt) {
         const long long tile = blockIdx.x + tl * gridDim.x;
         const long long mt = tile / P.tiles_n;
         *nt = int(tile - mt * P.tiles_n);
-        *m0 = mt * kTilePix;
-    };
-    auto geometry = [&](long long pix, int *y0, int *x0, long long *b) {
-        *y0 = -(1 << 28); *x0 = -(1 << 28); *b = 0;
-        if (pix < P.M) {
-            const int ow = int(pix % P.OW);
-            const long long t = pix / P.OW;
-            const int oh = int(t % P.OH);
-            const int n = int(t / P.OH);
-            *y0 = oh * P.sh - P.ph;
-            *x0 = ow * P.sw - P.pw;
-            *b = (((long long)n * P.H + *y0) * P.W + *x0) * P.C;
-        }
+        *m0 = mt * (kTilePix * NT);
     };
 
     if (warp >= kComputeWarps) {
         // ======================================== loaders ========================================
         const int ptid = tid - kComputeWarps * 32;          // 0..127
-        const int p = ptid & 15;                            // this thread's pixel of the tile
-        const int LQ = (KC + 3) >> 2;
-        const int quads = LQ * kTilePix;
-        constexpr int kStages = (((kMaxChunk + 3) / 4) * kTilePix + kLoaderThreads - 1) / kLoaderThreads;   // 9
-        constexpr int kRepl = (kMaxChunk * 8 + kLoaderThreads - 1) / kLoaderThreads;                         // 18
-        int iy0 = 0, ix0 = 0;
-        long long base = 0;
+        const int p = ptid & 15;                            // this thread's pixel within every tile
+        constexpr int kBatch = 6;                           // gathers in flight per thread
 
-        auto produce = [&](long long tl, int c, unsigned buf_base) {
+        auto tap_value = [&](int l, int iy0, int ix0, long long base) -> float {
+            unsigned off, dd;
+            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(off), "=r"(dd) : "r"(sTap + unsigned(l) * 8u));
+            const unsigned iy = unsigned(iy0 + int(dd & 0xFFFFu)), ix = unsigned(ix0 + int(dd >> 16));
+            return (iy < unsigned(P.H) && ix < unsigned(P.W)) ? __ldg(P.input + base + int(off)) : 0.0f;
+        };
+
+        auto produce = [&](long long tl, int c, unsigned parity) {
             if (c == 0) {
+                // geometry of the NT*16 pixels of the tile group: {element offset of the patch origin, iy0, ix0}
                 long long m0; int nt;
-                tile_coords(tl, &m0, &nt);
-                geometry(m0 + p, &iy0, &ix0, &base);
+                group_coords(tl, &m0, &nt);
+                for (int x = ptid; x < NT * kTilePix; x += kLoaderThreads) {
+                    const long long pix = m0 + x;
+                    int y0 = -(1 << 28), x0 = -(1 << 28);
+                    long long b = 0;
+                    if (pix < P.M) {
+                        const int ow = int(pix % P.OW);
+                        const long long t = pix / P.OW;
+                        const int oh = int(t % P.OH);
+                        const int n = int(t / P.OH);
+                        y0 = oh * P.sh - P.ph;
+                        x0 = ow * P.sw - P.pw;
+                        b = (((long long)n * P.H + y0) * P.W + x0) * P.C;
+                    }
+                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(sGeo + unsigned(x) * 16u), "r"(unsigned(b)), "r"(unsigned(b >> 32)) : "memory");
+                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(sGeo + unsigned(x) * 16u + 8u), "r"(unsigned(y0)), "r"(unsigned(x0)) : "memory");
+                }
+                AXC_BAR(kBarLoad, kLoaderThreads);
             }
             const int l_base = c * KC;
-            float4 st[kStages];
-            if (P.vec_ok) {
-                // this thread's quads are lq = (ptid >> 4) + 8 * s: walk the tap position incrementally
-                int l0 = l_base + (ptid >> 4) * 4;
+            const int kc = min(KC, P.K - l_base);
+            const int LQ = (kc + 3) >> 2;
+            const int lq_first = ptid >> 4;                 // this thread's quads: lq_first + 8 * s
+            const int stages = lq_first < LQ ? (LQ - lq_first + 7) / 8 : 0;
+            for (int t = 0; t < NT; ++t) {
+                const uint4 gq = lds128(sGeo + unsigned(t * kTilePix + p) * 16u);
+                const long long base = (long long)(((unsigned long long)gq.y << 32) | gq.x);
+                const int iy0 = int(gq.z), ix0 = int(gq.w);
+                const unsigned bb = buf_addr(int(parity) * NT + t) + 8u * 16u + unsigned(p);
+                int l0 = l_base + lq_first * 4;
                 int tap = l0 / P.C;
                 int cc = l0 - tap * P.C;
                 int ky = tap / P.KW;
                 int kx = tap - ky * P.KW;
+                for (int s0 = 0; s0 < stages; s0 += kBatch) {
+                    float4 st[kBatch];
 #pragma unroll
-                for (int s = 0; s < kStages; ++s) {
-                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (s * kLoaderThreads + ptid < quads && l0 < P.K) {
-                        const int iy = iy0 + ky * P.dh, ix = ix0 + kx * P.dw;
-                        if (iy >= 0 && iy < P.H && ix >= 0 && ix < P.W)
-                            v = __ldg(reinterpret_cast<const float4 *>(
-                                P.input + base + ((long long)(ky * P.dh) * P.W + kx * P.dw) * P.C + cc));
-                    }
-                    st[s] = v;
-                    l0 += (kLoaderThreads / kTilePix) * 4;
-                    cc += (kLoaderThreads / kTilePix) * 4;
-                    while (cc >= P.C) { cc -= P.C; if (++kx >= P.KW) { kx = 0; ++ky; } }
-                }
-            } else {
-#pragma unroll
-                for (int s = 0; s < kStages; ++s) {
-                    float e4[4] = {0.f, 0.f, 0.f, 0.f};
-                    const int q = s * kLoaderThreads + ptid;
-                    if (q < quads && tap_table) {
-                        const int lq = q >> 4;
-                        const int l0 = l_base + lq * 4;
-#pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            if (l0 + e < P.K && lq * 4 + e < KC) e4[e] = tap_value(l0 + e, iy0, ix0, base);
-                    } else if (q < quads) {
-                        const int lq = q >> 4;
-                        const int l0 = l_base + lq * 4;
-                        int tap = fast_div(l0, P.magic_c);
-                        int cc = l0 - tap * P.C;
-                        int ky = fast_div(tap, P.magic_kw);
-                        int kx = tap - ky * P.KW;
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            if (l0 + e < P.K && lq * 4 + e < KC) {
+                    for (int u = 0; u < kBatch; ++u) {
+                        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (s0 + u < stages) {
+                            if (P.vec_ok) {
                                 const int iy = iy0 + ky * P.dh, ix = ix0 + kx * P.dw;
                                 if (iy >= 0 && iy < P.H && ix >= 0 && ix < P.W)
-                                    e4[e] = __ldg(P.input + base + ((long long)(ky * P.dh) * P.W + kx * P.dw) * P.C + cc);
+                                    v = __ldg(reinterpret_cast<const float4 *>(
+                                        P.input + base + ((long long)(ky * P.dh) * P.W + kx * P.dw) * P.C + cc));
+                                cc += 32;
+                                while (cc >= P.C) { cc -= P.C; if (++kx >= P.KW) { kx = 0; ++ky; } }
+                            } else {
+                                float e4[4] = {0.f, 0.f, 0.f, 0.f};
+                                if (tap_table) {
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e)
+                                        if (l0 + e < P.K) e4[e] = tap_value(l0 + e, iy0, ix0, base);
+                                } else {
+                                    int tp = fast_div(l0, P.magic_c);
+                                    int c2 = l0 - tp * P.C;
+                                    int y2 = fast_div(tp, P.magic_kw);
+                                    int x2 = tp - y2 * P.KW;
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e) {
+                                        if (l0 + e < P.K) {
+                                            const int iy = iy0 + y2 * P.dh, ix = ix0 + x2 * P.dw;
+                                            if (iy >= 0 && iy < P.H && ix >= 0 && ix < P.W)
+                                                e4[e] = __ldg(P.input + base + ((long long)(y2 * P.dh) * P.W + x2 * P.dw) * P.C + c2);
+                                        }
+                                        if (++c2 >= P.C) { c2 = 0; if (++x2 >= P.KW) { x2 = 0; ++y2; } }
+                                    }
+                                }
+                                v = make_float4(e4[0], e4[1], e4[2], e4[3]);
                             }
-                            if (++cc >= P.C) { cc = 0; if (++kx >= P.KW) { kx = 0; ++ky; } }
+                            l0 += 32;
+                        }
+                        st[u] = v;
+                    }
+                    // quantise -> rows of the activation buffer; lanes = pixels, so the byte stores of a warp fall
+                    // into two groups of four consecutive words
+#pragma unroll
+                    for (int u = 0; u < kBatch; ++u) {
+                        if (s0 + u < stages) {
+                            const int lq = lq_first + 8 * (s0 + u);
+                            const unsigned a = bb + unsigned(lq * 4) * 16u;
+                            const float4 v = st[u];
+                            sts8(a, q_u8(v.x, P.in_off, P.in_inv));
+                            if (lq * 4 + 1 < kc) sts8(a + 16, q_u8(v.y, P.in_off, P.in_inv));
+                            if (lq * 4 + 2 < kc) sts8(a + 32, q_u8(v.z, P.in_off, P.in_inv));
+                            if (lq * 4 + 3 < kc) sts8(a + 48, q_u8(v.w, P.in_off, P.in_inv));
                         }
                     }
-                    st[s] = make_float4(e4[0], e4[1], e4[2], e4[3]);
                 }
-            }
-            // quantise -> byte staging [chunk-local l][pixel]; lanes = pixels, so the byte stores of a warp
-            // fall into two groups of four consecutive words
-#pragma unroll
-            for (int s = 0; s < kStages; ++s) {
-                const int q = s * kLoaderThreads + ptid;
-                if (q < quads) {
-                    const int lq = q >> 4;
-                    const float4 v = st[s];
-                    const unsigned a = sStage + unsigned(lq * 4) * 16u + unsigned(p);
-                    sts8(a, q_u8(v.x, P.in_off, P.in_inv));
-                    if (lq * 4 + 1 < KC) sts8(a + 16, q_u8(v.y, P.in_off, P.in_inv));
-                    if (lq * 4 + 2 < KC) sts8(a + 32, q_u8(v.z, P.in_off, P.in_inv));
-                    if (lq * 4 + 3 < KC) sts8(a + 48, q_u8(v.w, P.in_off, P.in_inv));
-                }
-            }
-            AXC_BAR(kBarLoad, kLoaderThreads);
-            // byte staging -> rows of 8 copies of the 16 pixel bytes (buffer row = chunk-local l + 1); the 8
-            // lanes of a quarter warp write one 128-byte row.  All reads are issued before the writes.
-            uint4 rows[kRepl];
-#pragma unroll
-            for (int i = 0; i < kRepl; ++i) {
-                const int x = ptid + i * kLoaderThreads;
-                if (x < KC * 8) rows[i] = lds128(sStage + unsigned(x >> 3) * 16u);
-            }
-#pragma unroll
-            for (int i = 0; i < kRepl; ++i) {
-                const int x = ptid + i * kLoaderThreads;
-                if (x < KC * 8) sts128(buf_base + unsigned((x >> 3) + 1) * 128u + unsigned(x & 7) * 16u, rows[i]);
             }
         };
 
-        if (my_tiles > 0) produce(0, 0, sBuf0);
+        if (my_groups > 0) produce(0, 0, 0u);
         AXC_BAR(kBarIter, (kComputeWarps + kLoaderWarps) * 32);
         long long tl = 0;
         int c = 0;
         unsigned parity = 0;
-        const long long total_iters = my_tiles * NCH;
+        const long long total_iters = my_groups * NCH;
         for (long long it = 0; it < total_iters; ++it) {
             if (++c == NCH) { c = 0; ++tl; }
             parity ^= 1u;
-            if (it + 1 < total_iters) produce(tl, c, parity ? sBuf1 : sBuf0);
+            if (it + 1 < total_iters) produce(tl, c, parity);
             AXC_BAR(kBarIter, (kComputeWarps + kLoaderWarps) * 32);
         }
         return;
     }
 
     // ========================================= consumers =========================================
-    const int gl = warp % GW, ks = warp / GW;
+    const int gl = warp % GW, slot = warp / GW;
     const int *steps_q = reinterpret_cast<const int *>(P.plan + P.L.steps_off);
     const uint4 *prog = reinterpret_cast<const uint4 *>(P.plan + P.L.prog_off);
     const float *bsum = reinterpret_cast<const float *>(P.plan + P.L.bsum_off);
-    int acc[kTilePix];
+    int acc[NTW][kTilePix];
+    unsigned base0[NTW], base1[NTW];               // this warp's activation buffers, parity 0 / 1
 #pragma unroll
-    for (int i = 0; i < kTilePix; ++i) acc[i] = 0;
+    for (int i = 0; i < NTW; ++i) {
+#pragma unroll
+        for (int x = 0; x < kTilePix; ++x) acc[i][x] = 0;
+        base0[i] = buf_addr(slot * NTW + i);
+        base1[i] = buf_addr(NT + slot * NTW + i);
+    }
 
-    // the slice of the schedule of (channel tile nt, chunk c) that this warp walks
-    auto slice_of = [&](int nt, int c, const uint4 **pp, int *nq) {
+    // the schedule of (channel tile nt, chunk c) that this warp walks
+    auto sched_of = [&](int nt, int c, const uint4 **pp, int *nq) {
         const int g = nt * GW + gl;
         *nq = 0;
         *pp = prog;
         if (g < P.L.G) {
             const int sc = g * NCH + c;
-            const int Q = steps_in_smem ? int(lds32(sSteps + unsigned(sc) * 4u)) : __ldg(steps_q + sc);
-            const int q0 = (ks * Q) / KS, q1 = ((ks + 1) * Q) / KS;
-            *pp = prog + ((size_t)sc * P.L.sqcap + q0) * 32 + lane;
-            *nq = q1 - q0;
+            *nq = steps_in_smem ? int(lds32(sSteps + unsigned(sc) * 4u)) : __ldg(steps_q + sc);
+            *pp = prog + (size_t)sc * P.L.sqcap * 32 + lane;
         }
     };
 
@@ -594,9 +619,9 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
     uint4 w_a = make_uint4(0, 0, 0, 0), w_b = make_uint4(0, 0, 0, 0);   // two quads of look-ahead
     long long m0 = 0;
     int nt = 0;
-    if (my_tiles > 0) {
-        tile_coords(0, &m0, &nt);
-        slice_of(nt, 0, &pp, &nq);
+    if (my_groups > 0) {
+        group_coords(0, &m0, &nt);
+        sched_of(nt, 0, &pp, &nq);
         if (nq > 0) w_a = __ldg(pp);
         if (nq > 1) w_b = __ldg(pp + 32);
     }
@@ -605,27 +630,32 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
     unsigned parity = 0;
     float t2 = 0.0f;          // m1 * bSum[j] of this lane's channel
     int t2_nt = -1;
-    for (long long tl = 0; tl < my_tiles; ++tl) {
+    for (long long tl = 0; tl < my_groups; ++tl) {
         long long m0_next = 0;
         int nt_next = 0;
-        if (tl + 1 < my_tiles) tile_coords(tl + 1, &m0_next, &nt_next);
-        // epilogue operands, requested a whole tile ahead of their use
-        const float asum_lane = (lane < kTilePix && m0 + lane < P.M) ? __ldg(P.asum + m0 + lane) : 0.0f;
+        if (tl + 1 < my_groups) group_coords(tl + 1, &m0_next, &nt_next);
+        // epilogue operands, requested a whole tile group ahead of their use: lane x of the warp holds the
+        // patch sum of pixel x of each of the warp's tiles
+        float asum_lane[NTW];
+#pragma unroll
+        for (int i = 0; i < NTW; ++i) {
+            const long long pix = m0 + (slot * NTW + i) * kTilePix + lane;
+            asum_lane[i] = (lane < kTilePix && pix < P.M) ? __ldg(P.asum + pix) : 0.0f;
+        }
         {
             const int j = (nt * GW + gl) * 32 + lane;
             if (nt != t2_nt) { t2 = j < P.Cout ? __fmul_rn(P.m1, __ldg(bsum + j)) : 0.0f; t2_nt = nt; }
         }
         for (int c = 0; c < NCH; ++c) {
-            // first two quads of the next (tile, chunk): requested now, consumed after the barrier
+            // first two quads of the next (tile group, chunk): requested now, consumed after the barrier
             const uint4 *pp_n = prog;
             int nq_n = 0;
             uint4 n_a = make_uint4(0, 0, 0, 0), n_b = make_uint4(0, 0, 0, 0);
-            if (c + 1 < NCH) slice_of(nt, c + 1, &pp_n, &nq_n);
-            else if (tl + 1 < my_tiles) slice_of(nt_next, 0, &pp_n, &nq_n);
+            if (c + 1 < NCH) sched_of(nt, c + 1, &pp_n, &nq_n);
+            else if (tl + 1 < my_groups) sched_of(nt_next, 0, &pp_n, &nq_n);
             if (nq_n > 0) n_a = __ldg(pp_n);
             if (nq_n > 1) n_b = __ldg(pp_n + 32);
 
-            const unsigned rep = (parity ? sBuf1 : sBuf0) + unsigned(lane & 7) * 16u;
             for (int q = 0; q < nq; ++q) {
                 const uint4 wq = w_a;
                 w_a = w_b;
@@ -634,57 +664,46 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const uint32_t w = ws[e];
-                    const unsigned row = (w >> 24) | (w & 0x300u);
-                    const uint4 av = lds128(rep + row * 128u);
-                    const unsigned aw[4] = {av.x, av.y, av.z, av.w};
+                    const unsigned rowoff = (w >> 24) | (w & 0x3F00u);     // 16 * activation row
 #pragma unroll
-                    for (int i4 = 0; i4 < kTilePix / 4; ++i4) {
-                        // table address = {column byte of w, activation byte, plane byte of w, 0}
-                        acc[i4 * 4 + 0] += int(lds16(prmt<0xA240>(w, aw[i4])));
-                        acc[i4 * 4 + 1] += int(lds16(prmt<0xA250>(w, aw[i4])));
-                        acc[i4 * 4 + 2] += int(lds16(prmt<0xA260>(w, aw[i4])));
-                        acc[i4 * 4 + 3] += int(lds16(prmt<0xA270>(w, aw[i4])));
+                    for (int i = 0; i < NTW; ++i) {
+                        const uint4 av = lds128((parity ? base1[i] : base0[i]) + rowoff);
+                        const unsigned aw[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+                        for (int i4 = 0; i4 < kTilePix / 4; ++i4) {
+                            // table address = {column byte of w, activation byte, plane byte of w, 0}
+                            acc[i][i4 * 4 + 0] += int(lds16(prmt<0xA240>(w, aw[i4])));
+                            acc[i][i4 * 4 + 1] += int(lds16(prmt<0xA250>(w, aw[i4])));
+                            acc[i][i4 * 4 + 2] += int(lds16(prmt<0xA260>(w, aw[i4])));
+                            acc[i][i4 * 4 + 3] += int(lds16(prmt<0xA270>(w, aw[i4])));
+                        }
                     }
                 }
             }
             pp = pp_n; nq = nq_n; w_a = n_a; w_b = n_b;
-            if (c == NCH - 1 && KS > 1) {
-#pragma unroll
-                for (int i = 0; i < kTilePix; ++i)
-                    sts32(sRed + unsigned(((ks * GW + gl) * kTilePix + i) * 32 + lane) * 4u, unsigned(acc[i]));
-            }
             AXC_BAR(kBarIter, (kComputeWarps + kLoaderWarps) * 32);
             parity ^= 1u;
         }
-        // ---- the tile is complete: reduce the slices, dequantise, store --------------------------
+        // ---- the tile group is complete: dequantise and store ------------------------------------
         {
-            const int g = nt * GW + gl;
-            const int j = g * 32 + lane;
-            const bool live = g < P.L.G && j < P.Cout;
+            const int j = (nt * GW + gl) * 32 + lane;
+            const bool live = (nt * GW + gl) < P.L.G && j < P.Cout;
 #pragma unroll
-            for (int ii = 0; ii < PPW; ++ii) {
-                const int i = ks * PPW + ii;
-                int s = 0;
-                if (KS > 1) {
+            for (int i = 0; i < NTW; ++i) {
 #pragma unroll
-                    for (int k2 = 0; k2 < KS; ++k2)
-                        s += int(lds32(sRed + unsigned(((k2 * GW + gl) * kTilePix + i) * 32 + lane) * 4u));
-                } else {
-                    s = acc[i];
-                }
-                const long long pix = m0 + i;
-                const float a_sum = __shfl_sync(0xffffffffu, asum_lane, i);   // lane i holds pixel i's patch sum
-                if (live && pix < P.M) {
-                    const float t0 = __fmul_rn(float(s), P.s1s2);
-                    const float t1 = __fmul_rn(P.m2, a_sum);
-                    P.output[pix * P.Cout + j] = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), P.km1m2);
-                    if (P.acc_out) P.acc_out[pix * P.Cout + j] = s;
+                for (int x = 0; x < kTilePix; ++x) {
+                    const long long pix = m0 + (slot * NTW + i) * kTilePix + x;
+                    const float a_sum = __shfl_sync(0xffffffffu, asum_lane[i], x);
+                    if (live && pix < P.M) {
+                        const float t0 = __fmul_rn(float(acc[i][x]), P.s1s2);
+                        const float t1 = __fmul_rn(P.m2, a_sum);
+                        P.output[pix * P.Cout + j] = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), P.km1m2);
+                        if (P.acc_out) P.acc_out[pix * P.Cout + j] = acc[i][x];
+                    }
+                    acc[i][x] = 0;
                 }
             }
-#pragma unroll
-            for (int i = 0; i < kTilePix; ++i) acc[i] = 0;
         }
-        if (KS > 1) AXC_BAR(kBarEpi, kComputeWarps * 32);
         m0 = m0_next;
         nt = nt_next;
     }
@@ -775,17 +794,32 @@ __global__ void __launch_bounds__(kPsThreads) patch_sum_kernel(const PatchSumPar
     if (tid < tp) P.asum[((long long)n * P.OH + oh) * P.OW + ow0 + tid] = sum;
 }
 
-template <int GW>
+template <int GW, int NTW>
 int launch_sched_variant(SchedParams P, const DeviceInfo &di, cudaStream_t stream)
 {
+    constexpr int NT = (kComputeWarps / GW) * NTW;
     P.tiles_n = (P.L.G + GW - 1) / GW;
-    P.tiles_total = ((P.M + kTilePix - 1) / kTilePix) * P.tiles_n;
-    AXC_CUDA(cudaFuncSetAttribute(dense_sched_kernel<GW>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
+    P.tiles_total = ((P.M + kTilePix * NT - 1) / (kTilePix * NT)) * P.tiles_n;
+    AXC_CUDA(cudaFuncSetAttribute(dense_sched_kernel<GW, NTW>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
     const long long grid = P.tiles_total < di.sm_count ? P.tiles_total : di.sm_count;
-    dense_sched_kernel<GW><<<unsigned(grid), kSchedThreads, size_t(di.max_smem_optin), stream>>>(P);
+    dense_sched_kernel<GW, NTW><<<unsigned(grid), kSchedThreads, size_t(di.max_smem_optin), stream>>>(P);
     AXC_CUDA(cudaGetLastError());
     count_launch();
     return AXC_OK;
+}
+
+// Activation buffers that fit beside the table (the kernel repeats this computation with the real window base).
+int buffers_that_fit(const SchedParams &P, int NT)
+{
+    unsigned cur = 1024u;                                     // first byte after the driver's reserved kilobyte
+    cur += unsigned(NT) * kTilePix * 16u;
+    if (!P.vec_ok && P.K <= kTapTableMax) cur += unsigned(P.K) * 8u;
+    if (P.L.G * P.L.NCH <= kStepsInSmemMax) cur += unsigned(P.L.G * P.L.NCH) * 4u;
+    cur = (cur + 127u) & ~127u;
+    const unsigned buf_bytes = unsigned(P.L.KC + 8) * 16u;
+    const int n_a = cur < kLutBase ? int((kLutBase - cur) / buf_bytes) : 0;
+    const int n_b = int((kWindowEnd - (kBuf1Base + 128u)) / buf_bytes);
+    return n_a + n_b;
 }
 
 }  // namespace
@@ -794,9 +828,12 @@ PlanLayout plan_layout(int K, int Cout)
 {
     PlanLayout L;
     L.G = (Cout + 31) / 32;
-    L.NCH = (K + kMaxChunk - 1) / kMaxChunk;
+    // Chunk length: two sets of activation buffers of (KC + 8) * 16 bytes must fit beside the table for every
+    // pixel-tile slot of the kernel (8 slots for one channel group, 4 for two, 2 for up to four, else 1).
+    const int kc_max = L.G <= 1 ? 320 : L.G <= 2 ? 608 : kMaxChunk;
+    L.NCH = (K + kc_max - 1) / kc_max;
     L.KC = (((K + L.NCH - 1) / L.NCH) + 3) & ~3;
-    if (L.KC > kMaxChunk) L.KC = kMaxChunk;
+    if (L.KC > kc_max) L.KC = kc_max;
     L.sqcap = (2 * L.KC + 3) / 4 + 1;               // room for twice the ideal number of steps
     auto r256 = [](size_t v) { return (v + 255) & ~size_t(255); };
     size_t off = 256;
@@ -814,7 +851,7 @@ int launch_plan(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, cons
                 unsigned char *plan, const PlanLayout &L, uint8_t *qf_debug, cudaStream_t stream)
 {
     PlanHeader want = {};
-    want.magic = 0x41584332u;  // "AXC2"
+    want.magic = 0x41584333u;  // "AXC3"
     want.K = g.K; want.Cout = g.Cout; want.G = L.G; want.NCH = L.NCH; want.KC = L.KC; want.sqcap = L.sqcap;
     want.table_uid = table_uid;
     memcpy(&want.f_off_bits, &q.f_off, 4);
@@ -828,7 +865,9 @@ int launch_plan(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, cons
     plan_sigma_kernel<<<1, 256, 0, stream>>>(plan + L.qf_off, count, plan + L.sigma_off, hdr, want);
     AXC_CUDA(cudaGetLastError());
     const unsigned blocks = unsigned(L.G * L.NCH + 256 + (g.Cout + 31) / 32);
-    plan_build_kernel<<<blocks, 32, 0, stream>>>(filter, lut_dev, plan, L, g.K, g.Cout);
+    const size_t sched_smem = size_t(32) * L.KC * 2 + 2 * size_t(32) * 256 * 2 + 32 * 32;
+    AXC_CUDA(cudaFuncSetAttribute(plan_build_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sched_smem)));
+    plan_build_kernel<<<blocks, 32, sched_smem, stream>>>(filter, lut_dev, plan, L, g.K, g.Cout);
     AXC_CUDA(cudaGetLastError());
     count_launch(3);
     return AXC_OK;
@@ -883,10 +922,26 @@ int launch_dense_sched(const Geom &g, const Quant &q, const float *input, const 
     // n / d == (n * magic) >> 40 holds while n * d < 2^40; launch_dense keeps shapes beyond that on the common-K kernel
     P.magic_c = ((1ull << 40) + unsigned(g.C) - 1) / unsigned(g.C);
     P.magic_kw = ((1ull << 40) + unsigned(g.KW) - 1) / unsigned(g.KW);
-    if (L.G <= 1) return launch_sched_variant<1>(P, di, stream);
-    if (L.G <= 2) return launch_sched_variant<2>(P, di, stream);
-    if (L.G <= 4) return launch_sched_variant<4>(P, di, stream);
-    return launch_sched_variant<8>(P, di, stream);
+    // pixel tiles per consumer warp: as many as the shared-memory budget allows (two sets of buffers)
+    const int gw = L.G <= 1 ? 1 : L.G <= 2 ? 2 : L.G <= 4 ? 4 : 8;
+    const int slots = kComputeWarps / gw;
+    int ntw = 4;
+    while (ntw > 1 && buffers_that_fit(P, slots * ntw) < 2 * slots * ntw) ntw >>= 1;
+    if (buffers_that_fit(P, slots * ntw) < 2 * slots * ntw) return AXC_INTERNAL;
+    // few pixels: do not make tile groups larger than the work available per SM
+    while (ntw > 1 && (P.M + kTilePix * slots * ntw - 1) / (kTilePix * slots * ntw) * ((L.G + gw - 1) / gw) < 2LL * di.sm_count) ntw >>= 1;
+#define AXC_DISPATCH(GWV)                                                     \
+    if (gw == GWV) {                                                          \
+        if (ntw == 4) return launch_sched_variant<GWV, 4>(P, di, stream);     \
+        if (ntw == 2) return launch_sched_variant<GWV, 2>(P, di, stream);     \
+        return launch_sched_variant<GWV, 1>(P, di, stream);                   \
+    }
+    AXC_DISPATCH(1)
+    AXC_DISPATCH(2)
+    AXC_DISPATCH(4)
+    AXC_DISPATCH(8)
+#undef AXC_DISPATCH
+    return AXC_INTERNAL;
 }
 
 }  // namespace axc

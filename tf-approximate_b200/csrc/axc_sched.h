@@ -11,9 +11,8 @@ struct Geom;
 struct Quant;
 struct DeviceInfo;
 
-// K elements per schedule chunk: row index + 1 must fit the activation buffer above the table
-// ((kMaxChunk + 1) * 128 bytes in the 36 KiB between the table and the end of the shared window).
-constexpr int kMaxChunk = 284;
+// K elements per schedule chunk: a program word addresses activation rows 0..1023 (8 zero rows + the chunk).
+constexpr int kMaxChunk = 1016;
 
 struct PlanHeader {
     uint32_t magic;
@@ -23,6 +22,7 @@ struct PlanHeader {
     int dirty;      // set by plan_check when the stored plan does not belong to this filter / table
     int fallback;   // set when a schedule did not fit: the common-K kernel serves the call
     int status;     // 0 fine; 2 shared-memory layout check failed
+    int pad[3];
 };
 
 struct PlanLayout {
