@@ -280,6 +280,11 @@ def run_gpu(args):
                 "peak_source": "measured" if "hbm_gbs" in peaks else "fallback"},
         "slowest_layers_ms": [[net.convs[i][0].name, v / args.steps] for i, v in slowest],
     }
+    if args.per_layer:
+        roofline["layers"] = [[net.convs[i][0].name, net.convs[i][1], net.convs[i][0].cin, net.convs[i][0].cout,
+                               net.convs[i][0].k, net.convs[i][0].stride, per_layer[i] / args.steps,
+                               W.conv_macs(net.convs[i][0], net.convs[i][1], batch) / (per_layer[i] / args.steps * 1e-3)
+                               / (SM_COUNT * sm_mhz * 1e6)] for i in sorted(per_layer)]
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
@@ -376,6 +381,7 @@ def main():
     ap.add_argument("--batch", type=int, default=256, help="images per GPU")
     ap.add_argument("--workload", default="resnet50", choices=["resnet50", "resnet20", "mobilenet_stack"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--per-layer", action="store_true", help="add per-layer times and lookups/clk/SM to the JSON line")
     ap.add_argument("--layer", default=None, help="time one layer instead: N,H,W,C,K,Cout,stride[,dw]")
     ap.add_argument("--table", default="truncated", choices=["truncated", "noisy", "exact"])
     args = ap.parse_args()
