@@ -8,7 +8,7 @@
 // Lane = output channel (consecutive channels are contiguous in NHWC, so every global
 // access of a warp is one 128-byte line), one warp walks a run of output pixels of one
 // image row and keeps the 3x3 input window in registers, so an input element is read once
-// per output row it touches.  The table lives in shared memory in the two-plane layout of
+// per output row it touches; the new window columns of four outputs are requested together.  The table lives in shared memory in the two-plane layout of
 // the dense kernel (plane p at 65536*(1+p), byte a*256 + 2*(b&127)).
 #include <mutex>
 
@@ -18,7 +18,7 @@ namespace axc {
 
 namespace {
 
-constexpr int kDwThreads = 512;
+constexpr int kDwThreads = 1024;
 constexpr int kDwWarps = kDwThreads / 32;
 constexpr unsigned kLutBase = 65536u;
 constexpr unsigned kSmemEnd = 196608u;
@@ -205,34 +205,50 @@ __global__ void __launch_bounds__(kDwThreads, 1) depthwise_3x3_kernel(const DwPa
                 xf[ky][kx] = fetch(ky, ix_first + kx - S);
                 xq[ky][kx] = dw_quantize_u8(xf[ky][kx], P.in_off, P.in_inv);
             }
-        for (int ow = ow0; ow < ow_end; ++ow) {
-            const int ix0 = ow * S - P.pw;
-            // shift the window left by S columns, fetch S new columns
+        // Outputs are produced in batches: the new input columns of a whole batch are requested first, so that
+        // kBatch * S * 3 loads per lane are in flight while the previous values are consumed.
+        constexpr int kBatch = 4;
+        for (int owb = ow0; owb < ow_end; owb += kBatch) {
+            float nf[kBatch][3][S];
 #pragma unroll
-            for (int ky = 0; ky < 3; ++ky) {
+            for (int u = 0; u < kBatch; ++u)
 #pragma unroll
-                for (int kx = 0; kx < 3 - S; ++kx) {
-                    xf[ky][kx] = xf[ky][kx + S];
-                    xq[ky][kx] = xq[ky][kx + S];
-                }
+                for (int ky = 0; ky < 3; ++ky)
 #pragma unroll
-                for (int kx = 3 - S; kx < 3; ++kx) {
-                    xf[ky][kx] = fetch(ky, ix0 + kx);
-                    xq[ky][kx] = dw_quantize_u8(xf[ky][kx], P.in_off, P.in_inv);
+                    for (int k2 = 0; k2 < S; ++k2)
+                        nf[u][ky][k2] = (owb + u < ow_end) ? fetch(ky, (owb + u) * S - P.pw + (3 - S) + k2) : 0.0f;
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int ow = owb + u;
+                if (ow < ow_end) {
+                    // shift the window left by S columns, append the S new columns
+#pragma unroll
+                    for (int ky = 0; ky < 3; ++ky) {
+#pragma unroll
+                        for (int kx = 0; kx < 3 - S; ++kx) {
+                            xf[ky][kx] = xf[ky][kx + S];
+                            xq[ky][kx] = xq[ky][kx + S];
+                        }
+#pragma unroll
+                        for (int k2 = 0; k2 < S; ++k2) {
+                            xf[ky][3 - S + k2] = nf[u][ky][k2];
+                            xq[ky][3 - S + k2] = dw_quantize_u8(nf[u][ky][k2], P.in_off, P.in_inv);
+                        }
+                    }
+                    int acc = 0;
+                    float a_sum = 0.0f;
+#pragma unroll
+                    for (int ky = 0; ky < 3; ++ky)
+#pragma unroll
+                        for (int kx = 0; kx < 3; ++kx) {
+                            a_sum = __fadd_rn(a_sum, xf[ky][kx]);
+                            acc += int(dw_lds_u16(__byte_perm(w[ky * 3 + kx], xq[ky][kx], 0x3240)));
+                        }
+                    const long long o = (((long long)n * P.OH + oh) * P.OW + ow) * P.OC + oc;
+                    P.output[o] = dw_epilogue(acc, a_sum, t2, P);
+                    if (P.acc_out) P.acc_out[o] = acc;
                 }
             }
-            int acc = 0;
-            float a_sum = 0.0f;
-#pragma unroll
-            for (int ky = 0; ky < 3; ++ky)
-#pragma unroll
-                for (int kx = 0; kx < 3; ++kx) {
-                    a_sum = __fadd_rn(a_sum, xf[ky][kx]);
-                    acc += int(dw_lds_u16(__byte_perm(w[ky * 3 + kx], xq[ky][kx], 0x3240)));
-                }
-            const long long o = (((long long)n * P.OH + oh) * P.OW + ow) * P.OC + oc;
-            P.output[o] = dw_epilogue(acc, a_sum, t2, P);
-            if (P.acc_out) P.acc_out[o] = acc;
         }
     }
 }
@@ -286,7 +302,7 @@ int launch_depthwise(const uint16_t *lut_dev, const Geom &g, const Quant &q, con
     P.status = status;
     P.N = g.N; P.H = g.H; P.W = g.W; P.C = g.C; P.KH = g.KH; P.KW = g.KW; P.mult = g.Cout; P.OC = OC;
     P.sh = g.sh; P.sw = g.sw; P.dh = g.dh; P.dw = g.dw; P.ph = g.ph; P.pw = g.pw; P.OH = g.OH; P.OW = g.OW;
-    P.run = g.OW < 14 ? g.OW : 14;
+    P.run = g.OW < 16 ? g.OW : 16;   // a multiple of the 3x3 kernels' batch of four outputs
     P.runs_per_row = (g.OW + P.run - 1) / P.run;
     P.groups = (OC + 31) / 32;
     P.items = (long long)g.N * g.OH * P.runs_per_row * P.groups;
