@@ -89,11 +89,19 @@ int axc_table_ensure_device(axc_table *table, int device);
 int axc_conv2d_output_dims(const axc_conv_desc *desc, int64_t out4[4]);
 int axc_depthwise_conv2d_output_dims(const axc_conv_desc *desc, int64_t out4[4]);
 
-/* Device scratch a forward call needs (the quantised filter in kernel layout and the
- * per-channel filter sums; stands in for the reference's allocate_temp buffers,
- * tf2/src/approx_nn_conv_ops.cpp:590-617).  The caller allocates it, 256-byte aligned. */
+/* Device scratch a forward call needs; stands in for the reference's allocate_temp buffers
+ * (tf2/src/approx_nn_conv_ops.cpp:590-617).  The caller allocates it, 256-byte aligned.
+ * For the dense op it holds the filter's lookup plan (quantised filter copy, table image, per-lane lookup
+ * schedule, filter sums) and the per-pixel patch sums.  The plan is rebuilt only when the buffer does not
+ * already hold the plan of this very filter (values, ranges, table): keep one buffer per layer between
+ * calls, leave it untouched, and the preparation is paid once; a fresh or recycled buffer is always safe
+ * (its first 256 bytes decide), only slower.  One buffer serves one stream at a time. */
 int axc_conv2d_workspace_bytes(const axc_conv_desc *desc, size_t *bytes);
 int axc_depthwise_conv2d_workspace_bytes(const axc_conv_desc *desc, size_t *bytes);
+/* Reads back {rebuilt in the last call, fallback kernel in use, kernel status (0 = fine), schedule steps per
+ * ideal step in per-mille} of the plan in a dense workspace.  Blocks until `stream` is idle.  Diagnostics only;
+ * no counterpart in the reference. */
+int axc_conv2d_plan_info(const void *workspace, int32_t out4[4], int device, void *stream);
 
 /* ---- forward: ApproxConv2DOp::Compute + LaunchApproxConv2DOp<GPUDevice>
  *      (tf2/src/approx_nn_conv_ops.cpp:420-460, 510-664) with the quantisation state of

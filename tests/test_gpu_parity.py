@@ -40,7 +40,8 @@ def run_dense(ax, lut, x, f, mm, stride, dil, pad):
                                                 strides=[1, stride[0], stride[1], 1], num_bits=8, mul_map_file=t,
                                                 padding=pad, dilations=[1, dil[0], dil[1], 1], debug=True)
     torch.cuda.synchronize()
-    return y.cpu().numpy(), {k: v.cpu().numpy() for k, v in dbg.items()}
+    assert dbg["plan"]["status"] == 0
+    return y.cpu().numpy(), {k: (v if k == "plan" else v.cpu().numpy()) for k, v in dbg.items()}
 
 
 def check_dense(ax, lut, x, f, mm, stride=(1, 1), dil=(1, 1), pad="SAME"):
@@ -140,6 +141,41 @@ def test_zero_ranges(ax):
     f = rng.normal(0, 0.1, (3, 3, 4, 8)).astype(np.float32)
     check_dense(ax, cases.make_table(("noisy", 33)), x, f, (0.0, 0.0, float(f.min()), float(f.max())))
     check_dense(ax, cases.make_table(("noisy", 33)), x, f, (-1.0, 1.0, 0.0, 0.0))
+
+
+def test_plan_reuse_and_fallback(ax):
+    """The lookup plan lives in the per-filter workspace: built on the first call, reused while the filter is
+    unchanged, rebuilt when a filter value changes; a filter whose weights all fall into one table column cannot
+    be scheduled and is served by the common-K kernel - every case with the same bits as the checker."""
+    import torch
+    rng = np.random.Generator(np.random.PCG64(21))
+    lut = cases.make_table(("noisy", 35))
+    t = ax.Table(array=lut)
+    x = rng.uniform(-1, 1, (2, 10, 10, 16)).astype(np.float32)
+    f = rng.normal(0, 0.1, (3, 3, 16, 40)).astype(np.float32)
+    xd, fd = torch.from_numpy(x).cuda(), torch.from_numpy(f).cuda()
+    mm = (-1.0, 1.0, -0.45, 0.45)
+    d = O.desc(2, 10, 10, 16, 3, 3, 40)
+
+    def run():
+        y, dbg = ax.approx_conv2d_with_min_max_vars(xd, fd, *mm, [1, 1, 1, 1], 8, t, "SAME", debug=True)
+        ref = O.conv2d(d, lut, x, fd.cpu().numpy(), *mm, want=("out_exact", "acc"))
+        assert np.array_equal(dbg["acc"].cpu().numpy(), ref["acc"])
+        assert np.array_equal(y.cpu().numpy().view(np.uint32), ref["out_exact"].view(np.uint32))
+        return dbg["plan"]
+
+    p1 = run()
+    assert p1["rebuilt"] == 1 and p1["fallback"] == 0 and 1000 <= p1["steps_per_mille"] < 1500
+    p2 = run()
+    assert p2["rebuilt"] == 0 and p2["fallback"] == 0
+    fd[1, 1, 3, 7] += 0.2                      # same storage, one weight changed
+    p3 = run()
+    assert p3["rebuilt"] == 1
+    fd.fill_(0.1)                              # every weight in one column: no conflict-free schedule
+    p4 = run()
+    assert p4["rebuilt"] == 1 and p4["fallback"] == 1
+    p5 = run()
+    assert p5["rebuilt"] == 0 and p5["fallback"] == 1
 
 
 def test_empty_batch(ax):

@@ -10,7 +10,7 @@ SYMBOLS = [
     "axc_table_create_from_file", "axc_table_create_from_memory", "axc_table_create_exact",
     "axc_table_destroy", "axc_table_host_data", "axc_table_ensure_device",
     "axc_conv2d_output_dims", "axc_depthwise_conv2d_output_dims",
-    "axc_conv2d_workspace_bytes", "axc_depthwise_conv2d_workspace_bytes",
+    "axc_conv2d_workspace_bytes", "axc_depthwise_conv2d_workspace_bytes", "axc_conv2d_plan_info",
     "axc_conv2d_forward", "axc_depthwise_conv2d_forward", "axc_depthwise_conv2d_forward_noalloc",
     "axc_quant_props", "axc_status_string", "axc_last_cuda_error", "axc_launch_count",
 ]
@@ -51,6 +51,7 @@ def load():
     L.axc_depthwise_conv2d_output_dims.argtypes = [C.POINTER(ConvDesc), C.POINTER(C.c_int64)]
     L.axc_conv2d_workspace_bytes.argtypes = [C.POINTER(ConvDesc), C.POINTER(C.c_size_t)]
     L.axc_depthwise_conv2d_workspace_bytes.argtypes = [C.POINTER(ConvDesc), C.POINTER(C.c_size_t)]
+    L.axc_conv2d_plan_info.argtypes = [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_void_p]
     L.axc_conv2d_forward.argtypes = fwd
     L.axc_depthwise_conv2d_forward.argtypes = fwd
     L.axc_depthwise_conv2d_forward_noalloc.argtypes = [C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.c_float,

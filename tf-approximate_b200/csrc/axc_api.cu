@@ -396,6 +396,17 @@ int axc_depthwise_conv2d_forward(axc_table *table, const axc_conv_desc *desc, co
                         workspace_bytes, debug, device, stream);
 }
 
+int axc_conv2d_plan_info(const void *workspace, int32_t out4[4], int device, void *stream)
+{
+    if (!workspace || !out4) return AXC_INVALID_ARGUMENT;
+    int prev = 0;
+    AXC_CUDA(cudaGetDevice(&prev));
+    if (prev != device) AXC_CUDA(cudaSetDevice(device));
+    const int rc = axc::plan_info(workspace, out4, cudaStream_t(stream));
+    if (prev != device) cudaSetDevice(prev);
+    return rc;
+}
+
 int axc_quant_props(float min_value, float max_value, float out3[3])
 {
     if (!out3) return AXC_INVALID_ARGUMENT;

@@ -20,6 +20,7 @@
 // tf2/src/approx_nn_conv_kernels.cpp:167-296; results are bit-identical to the common-K kernel.
 #include "axc_internal.h"
 #include "axc_sched.h"
+#include <vector>
 
 namespace axc {
 
@@ -758,13 +759,28 @@ __global__ void __launch_bounds__(kPsThreads) patch_sum_kernel(const PatchSumPar
                 __syncthreads();
                 if (P.vec) {
                     const int q4 = ccn >> 2;
-                    for (int i = tid; i < span * q4; i += kPsThreads) {
-                        const int x = i / q4, c4 = (i - x * q4) * 4;
-                        const int ix = ix_lo + x;
-                        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (ix >= 0 && ix < P.W) v = __ldg(reinterpret_cast<const float4 *>(row + (long long)ix * P.C + c0 + c4));
-                        float *d = tile + x * P.ccp + c4;
-                        d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+                    const int total = span * q4;
+                    for (int i0 = tid; i0 < total; i0 += 4 * kPsThreads) {
+                        float4 v[4];
+                        int dst[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {      // four independent loads in flight per thread
+                            const int i = i0 + u * kPsThreads;
+                            v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            dst[u] = -1;
+                            if (i < total) {
+                                const int x = i / q4, c4 = (i - x * q4) * 4;
+                                const int ix = ix_lo + x;
+                                if (ix >= 0 && ix < P.W) v[u] = __ldg(reinterpret_cast<const float4 *>(row + (long long)ix * P.C + c0 + c4));
+                                dst[u] = x * P.ccp + c4;
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            if (dst[u] >= 0) {
+                                float *d = tile + dst[u];
+                                d[0] = v[u].x; d[1] = v[u].y; d[2] = v[u].z; d[3] = v[u].w;
+                            }
                     }
                 } else {
                     for (int i = tid; i < span * ccn; i += kPsThreads) {
@@ -942,6 +958,25 @@ int launch_dense_sched(const Geom &g, const Quant &q, const float *input, const 
     AXC_DISPATCH(8)
 #undef AXC_DISPATCH
     return AXC_INTERNAL;
+}
+
+int plan_info(const void *workspace, int32_t out4[4], cudaStream_t stream)
+{
+    AXC_CUDA(cudaStreamSynchronize(stream));
+    PlanHeader h;
+    AXC_CUDA(cudaMemcpy(&h, workspace, sizeof(h), cudaMemcpyDeviceToHost));
+    out4[0] = h.dirty; out4[1] = h.fallback; out4[2] = h.status; out4[3] = 0;
+    if (h.magic == 0x41584333u && h.G > 0 && h.NCH > 0 && h.G * h.NCH <= 65536) {
+        const PlanLayout L = plan_layout(h.K, h.Cout);
+        std::vector<int> steps(size_t(h.G) * h.NCH);
+        AXC_CUDA(cudaMemcpy(steps.data(), static_cast<const unsigned char *>(workspace) + L.steps_off,
+                            steps.size() * sizeof(int), cudaMemcpyDeviceToHost));
+        long long quads = 0;
+        for (int v : steps) quads += v;
+        const long long ideal = (long long)h.G * ((h.K + 3) / 4);
+        out4[3] = ideal > 0 ? int(quads * 1000 / ideal) : 0;
+    }
+    return AXC_OK;
 }
 
 }  // namespace axc

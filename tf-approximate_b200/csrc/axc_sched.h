@@ -42,4 +42,7 @@ int launch_dense_sched(const Geom &g, const Quant &q, const float *input, const 
                        const unsigned char *plan, const PlanLayout &L, int32_t *acc_out, const DeviceInfo &di,
                        cudaStream_t stream);
 
+// Header fields of the plan in `workspace` (diagnostics; synchronises the stream).
+int plan_info(const void *workspace, int32_t out4[4], cudaStream_t stream);
+
 }  // namespace axc

@@ -190,6 +190,11 @@ def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_
              dev.index if dev.index is not None else torch.cuda.current_device(), C.c_void_p(stream))
     raise_for_status(st, "ApproxConv2D", _cuda_detail() if st == 100 else "")
     if debug:
+        if not depthwise:
+            info = (C.c_int32 * 4)()
+            raise_for_status(L.axc_conv2d_plan_info(ws.data_ptr(), info, dev.index or 0, C.c_void_p(stream)), "plan info")
+            dbg_t["plan"] = {"rebuilt": int(info[0]), "fallback": int(info[1]), "status": int(info[2]),
+                             "steps_per_mille": int(info[3])}
         return out, dbg_t
     return out
 
