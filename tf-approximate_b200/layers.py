@@ -88,9 +88,9 @@ class FakeApproxConv2D(torch.nn.Module):
         self.bias = torch.nn.Parameter(torch.zeros(filters)) if use_bias else None
 
     def forward(self, inputs):
-        input_min, input_max = float(inputs.min()), float(inputs.max())
+        input_min, input_max = float(inputs.detach().min()), float(inputs.detach().max())
         q_in = fake_quant_with_min_max_vars(inputs, input_min, input_max, self.num_bits)
-        k_min, k_max = float(self.kernel.min()), float(self.kernel.max())
+        k_min, k_max = float(self.kernel.detach().min()), float(self.kernel.detach().max())
         q_k = fake_quant_with_min_max_vars(self.kernel, k_min, k_max, self.num_bits)
         # straight-through estimator for the fake-quant steps, as TF's fake-quant gradient inside the range
         q_in = inputs + (q_in - inputs).detach()
