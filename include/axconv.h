@@ -130,9 +130,9 @@ int axc_depthwise_conv2d_forward(axc_table *table, const axc_conv_desc *desc,
  * no counterpart in the reference.  Same arithmetic and results as axc_depthwise_conv2d_forward, but no
  * workspace argument: the scratch is a 1 MiB array that every GPU using this library carries until the
  * process exits.  Limits and rules:
- *   - the scratch a call needs - what axc_depthwise_conv2d_workspace_bytes() reports: 4 bytes per filter
+ *   - the scratch a call needs - what axc_depthwise_conv2d_workspace_bytes() reports: about 6 bytes per filter
  *     element, 4 bytes per output channel and under 1 KiB of padding - must fit in 1 MiB (3x3 filters: up to
- *     about 26 000 channels), else AXC_INVALID_ARGUMENT; nothing is launched;
+ *     about 17 000 channels), else AXC_INVALID_ARGUMENT; nothing is launched;
  *   - the table replica must already be on `device`: call axc_table_ensure_device() beforehand (that call
  *     allocates 128 KiB); otherwise AXC_INTERNAL;
  *   - the first call on a device looks up the array's device address; make that call before any stream

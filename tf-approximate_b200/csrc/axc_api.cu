@@ -156,7 +156,7 @@ Workspace depthwise_workspace(int KHW, int C, int mult)
 {
     Workspace w;
     const size_t oc = size_t(C) * size_t(mult);
-    w.prog_bytes = round256(size_t(KHW) * oc * 4);
+    w.prog_bytes = round256((size_t(KHW) + size_t(KHW + 1) / 2) * oc * 4);   // program words + two-tap packed words
     w.sums_off = w.prog_bytes;
     w.status_off = w.sums_off + round256(oc * 4);
     w.total = w.status_off + 256;

@@ -28,6 +28,7 @@ struct DwParams {
     const float *input;
     float *output;
     const uint32_t *prog;  // [KH*KW][OC] program words {2*(b&127), 0, 1+(b>>7), 0}
+    const uint32_t *prog_packed;  // [(KH*KW+1)/2][OC]: bytes {column, plane} of tap 2i, then of tap 2i+1
     const float *bsum;     // [OC]
     int32_t *acc_out;
     int *status;
@@ -56,18 +57,22 @@ __device__ __forceinline__ unsigned dw_lds_u16(unsigned addr)
 // Quantise the depthwise filter [KHW][OC] into program words, the plain uint8 copy
 // (optional) and the per-channel fp32 filter sums (tap order).
 __global__ void dw_filter_prep_kernel(const float *__restrict__ filter, int KHW, int OC, float f_off, float f_inv,
-                                      uint32_t *__restrict__ prog, float *__restrict__ bsum,
-                                      uint8_t *__restrict__ qfilter, int *status)
+                                      uint32_t *__restrict__ prog, uint32_t *__restrict__ prog_packed,
+                                      float *__restrict__ bsum, uint8_t *__restrict__ qfilter, int *status)
 {
     const int oc = blockIdx.x * blockDim.x + threadIdx.x;
     if (oc == 0) *status = 0;
     if (oc >= OC) return;
     float s = 0.0f;
+    unsigned packed = 0;
     for (int t = 0; t < KHW; ++t) {
         const float f = filter[(size_t)t * OC + oc];
         s = __fadd_rn(s, f);
         const unsigned b = dw_quantize_u8(f, f_off, f_inv);
         prog[(size_t)t * OC + oc] = ((b & 127u) << 1) | ((1u + (b >> 7)) << 16);
+        const unsigned half = ((b & 127u) << 1) | ((1u + (b >> 7)) << 8);
+        packed = (t & 1) ? (packed | (half << 16)) : half;
+        if ((t & 1) || t == KHW - 1) prog_packed[(size_t)(t >> 1) * OC + oc] = (t & 1) ? packed : (packed | (1u << 24));
         if (qfilter) qfilter[(size_t)t * OC + oc] = uint8_t(b);
     }
     bsum[oc] = s;
@@ -148,7 +153,53 @@ __global__ void __launch_bounds__(kDwThreads, 1) depthwise_generic_kernel(const 
     }
 }
 
-// 3x3, dilation 1, stride S in {1, 2}: sliding window of raw and quantised taps in registers.
+// prmt.b32 with an immediate selector (a selector nibble with bit 3 set replicates the sign of the byte)
+template <unsigned SEL>
+__device__ __forceinline__ unsigned dw_prmt(unsigned a, unsigned b)
+{
+    unsigned d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "n"(SEL));
+    return d;
+}
+
+// Table address of tap TAP (0..8) for the activation in byte SLOT of `q`.  `wp` packs the program bytes of two
+// taps: {column byte, plane byte} of tap 2i in bytes 0-1 and of tap 2i+1 in bytes 2-3.  Result bytes:
+// {column, activation, plane, 0}; the zero is the replicated sign bit of the plane byte (1 or 2).
+template <int TAP, int SLOT>
+__device__ __forceinline__ unsigned dw_addr(const unsigned *wp, unsigned q)
+{
+    constexpr unsigned lo = (TAP & 1) ? 2u : 0u;                 // column byte of this tap inside wp[TAP/2]
+    constexpr unsigned sel = lo | ((4u + SLOT) << 4) | ((lo + 1u) << 8) | ((8u | (lo + 1u)) << 12);
+    return dw_prmt<sel>(wp[TAP >> 1], q);
+}
+
+// Nine table MACs and the raw-tap sum of one output, taps in (ky, kx) order; U = position of the output in
+// its batch of three, which fixes the ring slot of every logical column at compile time.
+template <int S, int U>
+__device__ __forceinline__ float dw_window(const float (&xf)[3][3], const unsigned (&xq)[3], const unsigned *wp, int *acc_out)
+{
+    constexpr int c0 = (S * U + 0) % 3, c1 = (S * U + 1) % 3, c2 = (S * U + 2) % 3;
+    float a = 0.0f;
+    int acc = 0;
+    a = __fadd_rn(a, xf[0][c0]); acc += int(dw_lds_u16(dw_addr<0, c0>(wp, xq[0])));
+    a = __fadd_rn(a, xf[0][c1]); acc += int(dw_lds_u16(dw_addr<1, c1>(wp, xq[0])));
+    a = __fadd_rn(a, xf[0][c2]); acc += int(dw_lds_u16(dw_addr<2, c2>(wp, xq[0])));
+    a = __fadd_rn(a, xf[1][c0]); acc += int(dw_lds_u16(dw_addr<3, c0>(wp, xq[1])));
+    a = __fadd_rn(a, xf[1][c1]); acc += int(dw_lds_u16(dw_addr<4, c1>(wp, xq[1])));
+    a = __fadd_rn(a, xf[1][c2]); acc += int(dw_lds_u16(dw_addr<5, c2>(wp, xq[1])));
+    a = __fadd_rn(a, xf[2][c0]); acc += int(dw_lds_u16(dw_addr<6, c0>(wp, xq[2])));
+    a = __fadd_rn(a, xf[2][c1]); acc += int(dw_lds_u16(dw_addr<7, c1>(wp, xq[2])));
+    a = __fadd_rn(a, xf[2][c2]); acc += int(dw_lds_u16(dw_addr<8, c2>(wp, xq[2])));
+    *acc_out = acc;
+    return a;
+}
+
+// 3x3, dilation 1, stride S in {1, 2}.  Lane = output channel; a warp walks a run of output pixels of one row.
+// The 3x3 window lives in registers: raw fp32 taps in three ring slots per filter row (output u of a batch of
+// three reads logical column kx from slot (S*u + kx) % 3, so sliding costs no moves) and the quantised taps
+// packed as one byte per slot in one register per filter row.  The new columns of a whole batch are requested
+// before its first output is computed.  Offsets are 32-bit: the launcher sends tensors of 2^31 elements or more
+// to the generic kernel.
 template <int S>
 __global__ void __launch_bounds__(kDwThreads, 1) depthwise_3x3_kernel(const DwParams P)
 {
@@ -164,89 +215,88 @@ __global__ void __launch_bounds__(kDwThreads, 1) depthwise_3x3_kernel(const DwPa
     __syncthreads();
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (long long item = (long long)blockIdx.x * kDwWarps + warp; item < P.items; item += (long long)gridDim.x * kDwWarps) {
-        const int grp = int(item % P.groups);
-        long long t = item / P.groups;
-        const int r = int(t % P.runs_per_row);
+    const int items = int(P.items);
+    for (int item = blockIdx.x * kDwWarps + warp; item < items; item += gridDim.x * kDwWarps) {
+        const int grp = item % P.groups;
+        int t = item / P.groups;
+        const int r = t % P.runs_per_row;
         t /= P.runs_per_row;
-        const int oh = int(t % P.OH);
-        const int n = int(t / P.OH);
+        const int oh = t % P.OH;
+        const int n = t / P.OH;
         const int oc = grp * 32 + lane;
         if (oc >= P.OC) continue;
         const int c = oc / P.mult;
         const float t2 = __fmul_rn(P.m1, __ldg(P.bsum + oc));
-        unsigned w[9];
+        unsigned wp[5];
 #pragma unroll
-        for (int tap = 0; tap < 9; ++tap) w[tap] = __ldg(P.prog + (size_t)tap * P.OC + oc);
+        for (int i = 0; i < 5; ++i) wp[i] = __ldg(P.prog_packed + i * P.OC + oc);
 
+        const int ow0 = r * P.run;
+        const int ow_end = min(P.OW, ow0 + P.run);
         const int iy0 = oh * P.sh - P.ph;
-        const float *rowp[3];
+        const int ix_first = ow0 * S - P.pw;              // leftmost input column of the first window
+        int rowoff[3];                                    // element offset of (row, column ix_first, channel c)
         bool rowok[3];
 #pragma unroll
         for (int ky = 0; ky < 3; ++ky) {
             const int iy = iy0 + ky;
-            rowok[ky] = iy >= 0 && iy < P.H;
-            rowp[ky] = P.input + (((long long)n * P.H + (rowok[ky] ? iy : 0)) * P.W) * P.C + c;
+            rowok[ky] = unsigned(iy) < unsigned(P.H);
+            rowoff[ky] = (((n * P.H + (rowok[ky] ? iy : 0)) * P.W) + ix_first) * P.C + c;
         }
-        auto fetch = [&](int ky, int ix) -> float {
-            return (rowok[ky] && ix >= 0 && ix < P.W) ? __ldg(rowp[ky] + (long long)ix * P.C) : 0.0f;
-        };
+        int outoff = ((n * P.OH + oh) * P.OW + ow0) * P.OC + oc;
 
-        const int ow0 = r * P.run;
-        const int ow_end = min(P.OW, ow0 + P.run);
-        float xf[3][3];
-        unsigned xq[3][3];
-        // columns 0 .. 2-S of the first window come from the "previous" position
-        const int ix_first = ow0 * S - P.pw;
+        float xf[3][3];       // [ky][slot]
+        unsigned xq[3] = {0u, 0u, 0u};   // [ky], byte = slot
+        // columns 0 .. 2-S of the first window
 #pragma unroll
         for (int ky = 0; ky < 3; ++ky)
 #pragma unroll
-            for (int kx = S; kx < 3; ++kx) {
-                xf[ky][kx] = fetch(ky, ix_first + kx - S);
-                xq[ky][kx] = dw_quantize_u8(xf[ky][kx], P.in_off, P.in_inv);
+            for (int kx = 0; kx < 3 - S; ++kx) {
+                const bool ok = rowok[ky] && unsigned(ix_first + kx) < unsigned(P.W);
+                xf[ky][kx] = ok ? __ldg(P.input + (rowoff[ky] + kx * P.C)) : 0.0f;
+                xq[ky] |= dw_quantize_u8(xf[ky][kx], P.in_off, P.in_inv) << (8 * kx);
             }
-        // Outputs are produced in batches: the new input columns of a whole batch are requested first, so that
-        // kBatch * S * 3 loads per lane are in flight while the previous values are consumed.
-        constexpr int kBatch = 4;
-        for (int owb = ow0; owb < ow_end; owb += kBatch) {
-            float nf[kBatch][3][S];
+        int col = 3 - S;                                  // next new column, relative to ix_first
+        for (int owb = ow0; owb < ow_end; owb += 3) {
+            float nf[3][S][3];                            // [output of the batch][new column][ky]
 #pragma unroll
-            for (int u = 0; u < kBatch; ++u)
+            for (int u = 0; u < 3; ++u)
 #pragma unroll
-                for (int ky = 0; ky < 3; ++ky)
-#pragma unroll
-                    for (int k2 = 0; k2 < S; ++k2)
-                        nf[u][ky][k2] = (owb + u < ow_end) ? fetch(ky, (owb + u) * S - P.pw + (3 - S) + k2) : 0.0f;
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                const int ow = owb + u;
-                if (ow < ow_end) {
-                    // shift the window left by S columns, append the S new columns
-#pragma unroll
-                    for (int ky = 0; ky < 3; ++ky) {
-#pragma unroll
-                        for (int kx = 0; kx < 3 - S; ++kx) {
-                            xf[ky][kx] = xf[ky][kx + S];
-                            xq[ky][kx] = xq[ky][kx + S];
-                        }
-#pragma unroll
-                        for (int k2 = 0; k2 < S; ++k2) {
-                            xf[ky][3 - S + k2] = nf[u][ky][k2];
-                            xq[ky][3 - S + k2] = dw_quantize_u8(nf[u][ky][k2], P.in_off, P.in_inv);
-                        }
-                    }
-                    int acc = 0;
-                    float a_sum = 0.0f;
+                for (int k2 = 0; k2 < S; ++k2) {
+                    const int rel = col + u * S + k2;
+                    const bool colok = owb + u < ow_end && unsigned(ix_first + rel) < unsigned(P.W);
+                    const int o = rel * P.C;
 #pragma unroll
                     for (int ky = 0; ky < 3; ++ky)
+                        nf[u][k2][ky] = (colok && rowok[ky]) ? __ldg(P.input + (rowoff[ky] + o)) : 0.0f;
+                }
+            col += 3 * S;
 #pragma unroll
-                        for (int kx = 0; kx < 3; ++kx) {
-                            a_sum = __fadd_rn(a_sum, xf[ky][kx]);
-                            acc += int(dw_lds_u16(__byte_perm(w[ky * 3 + kx], xq[ky][kx], 0x3240)));
+            for (int u = 0; u < 3; ++u) {
+                if (owb + u < ow_end) {
+#pragma unroll
+                    for (int k2 = 0; k2 < S; ++k2) {
+                        const int slot = (S * u + (3 - S) + k2) % 3;
+#pragma unroll
+                        for (int ky = 0; ky < 3; ++ky) {
+                            xf[ky][slot] = nf[u][k2][ky];
+                            const unsigned q = dw_quantize_u8(nf[u][k2][ky], P.in_off, P.in_inv);
+                            xq[ky] = (xq[ky] & ~(0xFFu << (8 * slot))) | (q << (8 * slot));
                         }
-                    const long long o = (((long long)n * P.OH + oh) * P.OW + ow) * P.OC + oc;
-                    P.output[o] = dw_epilogue(acc, a_sum, t2, P);
-                    if (P.acc_out) P.acc_out[o] = acc;
+                    }
+                    // taps in the reference's order (ky, kx); logical column kx sits in slot (S*u + kx) % 3
+                    float a_sum = 0.0f;
+                    int acc = 0;
+                    if (u == 0) {
+                        a_sum = dw_window<S, 0>(xf, xq, wp, &acc);
+                    } else if (u == 1) {
+                        a_sum = dw_window<S, 1>(xf, xq, wp, &acc);
+                    } else {
+                        a_sum = dw_window<S, 2>(xf, xq, wp, &acc);
+                    }
+                    P.output[outoff] = dw_epilogue(acc, a_sum, t2, P);
+                    if (P.acc_out) P.acc_out[outoff] = acc;
+                    outoff += P.OC;
                 }
             }
         }
@@ -279,11 +329,12 @@ int launch_depthwise(const uint16_t *lut_dev, const Geom &g, const Quant &q, con
     const Workspace ws = depthwise_workspace(g.K, g.C, g.Cout);
     unsigned char *wsb = static_cast<unsigned char *>(workspace);
     uint32_t *prog = reinterpret_cast<uint32_t *>(wsb);
+    uint32_t *prog_packed = prog + size_t(g.K) * OC;
     float *bsum = reinterpret_cast<float *>(wsb + ws.sums_off);
     int *status = reinterpret_cast<int *>(wsb + ws.status_off);
 
-    dw_filter_prep_kernel<<<unsigned((OC + 127) / 128), 128, 0, stream>>>(filter, g.K, OC, q.f_off, q.f_inv, prog, bsum,
-                                                                         dbg ? dbg->qfilter : nullptr, status);
+    dw_filter_prep_kernel<<<unsigned((OC + 127) / 128), 128, 0, stream>>>(filter, g.K, OC, q.f_off, q.f_inv, prog, prog_packed,
+                                                                         bsum, dbg ? dbg->qfilter : nullptr, status);
     AXC_CUDA(cudaGetLastError());
     count_launch();
     if (dbg && dbg->qinput) {
@@ -297,12 +348,12 @@ int launch_depthwise(const uint16_t *lut_dev, const Geom &g, const Quant &q, con
     }
 
     DwParams P;
-    P.lut = lut_dev; P.input = input; P.output = output; P.prog = prog; P.bsum = bsum;
+    P.lut = lut_dev; P.input = input; P.output = output; P.prog = prog; P.prog_packed = prog_packed; P.bsum = bsum;
     P.acc_out = dbg ? dbg->acc : nullptr;
     P.status = status;
     P.N = g.N; P.H = g.H; P.W = g.W; P.C = g.C; P.KH = g.KH; P.KW = g.KW; P.mult = g.Cout; P.OC = OC;
     P.sh = g.sh; P.sw = g.sw; P.dh = g.dh; P.dw = g.dw; P.ph = g.ph; P.pw = g.pw; P.OH = g.OH; P.OW = g.OW;
-    P.run = g.OW < 16 ? g.OW : 16;   // a multiple of the 3x3 kernels' batch of four outputs
+    P.run = g.OW < 15 ? g.OW : 15;   // a multiple of the 3x3 kernels' batch of three outputs
     P.runs_per_row = (g.OW + P.run - 1) / P.run;
     P.groups = (OC + 31) / 32;
     P.items = (long long)g.N * g.OH * P.runs_per_row * P.groups;
@@ -312,7 +363,8 @@ int launch_depthwise(const uint16_t *lut_dev, const Geom &g, const Quant &q, con
         volatile float t3 = kf * q.m1m2;
         P.km1m2 = t3;
     }
-    const bool k3 = g.KH == 3 && g.KW == 3 && g.dh == 1 && g.dw == 1 && g.sh == g.sw;
+    const bool small = (long long)g.N * g.H * g.W * g.C < (1ll << 31) && g.M * OC < (1ll << 31) && P.items < (1ll << 31);
+    const bool k3 = small && g.KH == 3 && g.KW == 3 && g.dh == 1 && g.dw == 1 && g.sh == g.sw;
     if (k3 && g.sw == 1) return launch_dw(depthwise_3x3_kernel<1>, P, di, stream);
     if (k3 && g.sw == 2) return launch_dw(depthwise_3x3_kernel<2>, P, di, stream);
     return launch_dw(depthwise_generic_kernel, P, di, stream);
