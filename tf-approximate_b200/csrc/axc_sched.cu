@@ -367,6 +367,7 @@ struct SchedParams {
     int N, H, W, C, KH, KW, Cout;
     int sh, sw, dh, dw, ph, pw, OH, OW, K;
     long long M;
+    int g_base, g_count;      // channel groups [g_base, g_base + g_count) are served by this launch
     int tiles_n;              // channel tiles of 32*GW channels
     long long tiles_total;    // pixel tile groups x channel tiles
     float in_off, in_inv, s1s2, m1, m2, km1m2;
@@ -605,11 +606,11 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
 
     // the schedule of (channel tile nt, chunk c) that this warp walks
     auto sched_of = [&](int nt, int c, const uint4 **pp, int *nq) {
-        const int g = nt * GW + gl;
+        const int gi = nt * GW + gl;
         *nq = 0;
         *pp = prog;
-        if (g < P.L.G) {
-            const int sc = g * NCH + c;
+        if (gi < P.g_count) {
+            const int sc = (P.g_base + gi) * NCH + c;
             *nq = steps_in_smem ? int(lds32(sSteps + unsigned(sc) * 4u)) : __ldg(steps_q + sc);
             *pp = prog + (size_t)sc * P.L.sqcap * 32 + lane;
         }
@@ -644,7 +645,7 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
             asum_lane[i] = (lane < kTilePix && pix < P.M) ? __ldg(P.asum + pix) : 0.0f;
         }
         {
-            const int j = (nt * GW + gl) * 32 + lane;
+            const int j = (P.g_base + nt * GW + gl) * 32 + lane;
             if (nt != t2_nt) { t2 = j < P.Cout ? __fmul_rn(P.m1, __ldg(bsum + j)) : 0.0f; t2_nt = nt; }
         }
         for (int c = 0; c < NCH; ++c) {
@@ -687,8 +688,8 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
         }
         // ---- the tile group is complete: dequantise and store ------------------------------------
         {
-            const int j = (nt * GW + gl) * 32 + lane;
-            const bool live = (nt * GW + gl) < P.L.G && j < P.Cout;
+            const int j = (P.g_base + nt * GW + gl) * 32 + lane;
+            const bool live = (nt * GW + gl) < P.g_count && j < P.Cout;
 #pragma unroll
             for (int i = 0; i < NTW; ++i) {
 #pragma unroll
@@ -814,7 +815,7 @@ template <int GW, int NTW>
 int launch_sched_variant(SchedParams P, const DeviceInfo &di, cudaStream_t stream)
 {
     constexpr int NT = (kComputeWarps / GW) * NTW;
-    P.tiles_n = (P.L.G + GW - 1) / GW;
+    P.tiles_n = (P.g_count + GW - 1) / GW;
     P.tiles_total = ((P.M + kTilePix * NT - 1) / (kTilePix * NT)) * P.tiles_n;
     AXC_CUDA(cudaFuncSetAttribute(dense_sched_kernel<GW, NTW>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
     const long long grid = P.tiles_total < di.sm_count ? P.tiles_total : di.sm_count;
@@ -840,13 +841,33 @@ int buffers_that_fit(const SchedParams &P, int NT)
 
 }  // namespace
 
+// Next run of channel groups for a launch: `rem` groups are left; returns the GW of the launch and how many
+// groups it covers.  Whole multiples of 8 go together; 5 and 6 are cut into 4 + 1 and 4 + 2; 3 and 7 are rounded
+// up to a launch of 4 resp. 8 with one idle consumer-warp column (cheaper than a second launch).
+static void next_group_run(int rem, int *gw, int *count)
+{
+    if (rem >= 8) { *gw = 8; *count = (rem / 8) * 8; return; }
+    if (rem == 7) { *gw = 8; *count = 7; return; }
+    if (rem >= 4) { *gw = 4; *count = 4; return; }
+    if (rem == 3) { *gw = 4; *count = 3; return; }
+    *gw = rem; *count = rem;
+}
+
 PlanLayout plan_layout(int K, int Cout)
 {
     PlanLayout L;
     L.G = (Cout + 31) / 32;
     // Chunk length: two sets of activation buffers of (KC + 8) * 16 bytes must fit beside the table for every
-    // pixel-tile slot of the kernel (8 slots for one channel group, 4 for two, 2 for up to four, else 1).
-    const int kc_max = L.G <= 1 ? 320 : L.G <= 2 ? 608 : kMaxChunk;
+    // pixel-tile slot of the kernel.  The groups are served in runs of 8, 4, 2 and 1 (launch_dense_sched); the
+    // smallest run decides: 8 slots for a run of one group, 4 for two, 2 for four, 1 for eight.
+    int smallest = 8;
+    for (int rem = L.G; rem > 0;) {
+        int gw, count;
+        next_group_run(rem, &gw, &count);
+        if (gw < smallest) smallest = gw;
+        rem -= count;
+    }
+    const int kc_max = smallest == 1 ? 320 : smallest == 2 ? 608 : kMaxChunk;
     L.NCH = (K + kc_max - 1) / kc_max;
     L.KC = (((K + L.NCH - 1) / L.NCH) + 3) & ~3;
     if (L.KC > kc_max) L.KC = kc_max;
@@ -938,26 +959,38 @@ int launch_dense_sched(const Geom &g, const Quant &q, const float *input, const 
     // n / d == (n * magic) >> 40 holds while n * d < 2^40; launch_dense keeps shapes beyond that on the common-K kernel
     P.magic_c = ((1ull << 40) + unsigned(g.C) - 1) / unsigned(g.C);
     P.magic_kw = ((1ull << 40) + unsigned(g.KW) - 1) / unsigned(g.KW);
-    // pixel tiles per consumer warp: as many as the shared-memory budget allows (two sets of buffers)
-    const int gw = L.G <= 1 ? 1 : L.G <= 2 ? 2 : L.G <= 4 ? 4 : 8;
-    const int slots = kComputeWarps / gw;
-    int ntw = 4;
-    while (ntw > 1 && buffers_that_fit(P, slots * ntw) < 2 * slots * ntw) ntw >>= 1;
-    if (buffers_that_fit(P, slots * ntw) < 2 * slots * ntw) return AXC_INTERNAL;
-    // few pixels: do not make tile groups larger than the work available per SM
-    while (ntw > 1 && (P.M + kTilePix * slots * ntw - 1) / (kTilePix * slots * ntw) * ((L.G + gw - 1) / gw) < 2LL * di.sm_count) ntw >>= 1;
-#define AXC_DISPATCH(GWV)                                                     \
-    if (gw == GWV) {                                                          \
-        if (ntw == 4) return launch_sched_variant<GWV, 4>(P, di, stream);     \
-        if (ntw == 2) return launch_sched_variant<GWV, 2>(P, di, stream);     \
-        return launch_sched_variant<GWV, 1>(P, di, stream);                   \
-    }
-    AXC_DISPATCH(1)
-    AXC_DISPATCH(2)
-    AXC_DISPATCH(4)
-    AXC_DISPATCH(8)
+    // The 8 consumer warps of a CTA serve GW channel groups x 8/GW pixel-tile slots, GW a power of two.  A
+    // group count that is not one is cut into runs (next_group_run), one launch each, so that few consumer warps
+    // are left without a group.
+    int g_done = 0;
+    while (g_done < L.G) {
+        int gw, count;
+        next_group_run(L.G - g_done, &gw, &count);
+        P.g_base = g_done;
+        P.g_count = count;
+        // pixel tiles per consumer warp: as many as the shared-memory budget allows (two sets of buffers)
+        const int slots = kComputeWarps / gw;
+        int ntw = 4;
+        while (ntw > 1 && buffers_that_fit(P, slots * ntw) < 2 * slots * ntw) ntw >>= 1;
+        if (buffers_that_fit(P, slots * ntw) < 2 * slots * ntw) return AXC_INTERNAL;
+        // few pixels: do not make tile groups larger than the work available per SM
+        while (ntw > 1 && (P.M + kTilePix * slots * ntw - 1) / (kTilePix * slots * ntw) * ((count + gw - 1) / gw) < 2LL * di.sm_count) ntw >>= 1;
+        int rc = AXC_INTERNAL;
+#define AXC_DISPATCH(GWV)                                                          \
+        if (gw == GWV) {                                                           \
+            if (ntw == 4) rc = launch_sched_variant<GWV, 4>(P, di, stream);        \
+            else if (ntw == 2) rc = launch_sched_variant<GWV, 2>(P, di, stream);   \
+            else rc = launch_sched_variant<GWV, 1>(P, di, stream);                 \
+        }
+        AXC_DISPATCH(1)
+        AXC_DISPATCH(2)
+        AXC_DISPATCH(4)
+        AXC_DISPATCH(8)
 #undef AXC_DISPATCH
-    return AXC_INTERNAL;
+        if (rc) return rc;
+        g_done += count;
+    }
+    return AXC_OK;
 }
 
 int plan_info(const void *workspace, int32_t out4[4], cudaStream_t stream)
