@@ -722,7 +722,7 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
 // ------------------------------------------------------------------------------------------------
 constexpr int kPsPixels = 64;
 constexpr int kPsThreads = 128;
-constexpr int kPsFloats = 11 * 1024;   // 44 KiB of staging
+constexpr int kPsFloats = 11 * 1024;   // at most 44 KiB of staging per block
 
 struct PatchSumParams {
     const float *input;
@@ -737,7 +737,7 @@ struct PatchSumParams {
 
 __global__ void __launch_bounds__(kPsThreads) patch_sum_kernel(const PatchSumParams P)
 {
-    __shared__ float tile[kPsFloats];
+    extern __shared__ __align__(16) float tile[];   // span * ccp floats, sized by the launcher
     const int tid = threadIdx.x;
     long long b = blockIdx.x;
     const int tr = int(b % P.tiles_per_row); b /= P.tiles_per_row;
@@ -934,7 +934,10 @@ int launch_patch_sums(const Geom &g, const float *input, float *asum, cudaStream
     S.ccp = odd(S.cc);
     S.vec = (g.C % 4 == 0) && (S.cc % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
     const long long blocks = (long long)g.N * g.OH * S.tiles_per_row;
-    patch_sum_kernel<<<unsigned(blocks), kPsThreads, 0, stream>>>(S);
+    // only what one staging step needs, so that many blocks share an SM and hide each other's load latency
+    const long long span = (long long)(tp - 1) * g.sw + (long long)(S.kx_group - 1) * g.dw + 1;
+    const size_t smem = size_t(span) * S.ccp * sizeof(float);
+    patch_sum_kernel<<<unsigned(blocks), kPsThreads, smem, stream>>>(S);
     AXC_CUDA(cudaGetLastError());
     count_launch();
     return AXC_OK;
