@@ -114,6 +114,17 @@ int axc_conv2d_forward(axc_table *table, const axc_conv_desc *desc,
                        float *output, void *workspace, size_t workspace_bytes,
                        const axc_debug_out *debug, int device, void *stream);
 
+/* Same op with the four range scalars read from DEVICE memory: `ranges` = {input_min, input_max, filter_min,
+ * filter_max}, four floats on `device`, typically written by the reductions that precede the op in the
+ * reference's Keras wrapper (tf2/python/keras/layers/fake_approx_convolutional.py:233-242).  The quantisation
+ * parameters are derived on the device with the host's arithmetic, so nothing waits for the host; the reference
+ * pins these inputs to host memory (tf2/src/approx_nn_conv_ops.cpp:691-694), which costs a device-to-host
+ * synchronisation per layer.  Results are bit-identical to axc_conv2d_forward with the same four values. */
+int axc_conv2d_forward_device_ranges(axc_table *table, const axc_conv_desc *desc,
+                                     const float *input, const float *filter, const float *ranges,
+                                     float *output, void *workspace, size_t workspace_bytes,
+                                     const axc_debug_out *debug, int device, void *stream);
+
 /* Depthwise variant (new: the reference rejects grouped shapes,
  * tf2/src/approx_nn_conv_ops.cpp:229-232).  filter [kh,kw,c,mult] in TensorFlow's
  * DepthwiseConv2dNative layout, output channel c*mult + m, same quantiser, table

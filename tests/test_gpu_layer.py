@@ -18,9 +18,9 @@ def test_layer_forward_matches_op_and_float_conv(built):
     y = layer(x)
     # the same thing spelled out with the op
     xq = ax.fake_quant_with_min_max_vars(x, float(x.min()), float(x.max()))
-    wq = ax.fake_quant_with_min_max_vars(layer.kernel.detach(), float(layer.kernel.min()), float(layer.kernel.max()))
-    y_op = ax.approx_conv2d_with_min_max_vars(xq, wq, float(x.min()), float(x.max()), float(layer.kernel.min()),
-                                              float(layer.kernel.max()), [1, 1, 1, 1], 8, "", "SAME") + layer.bias
+    wq = ax.fake_quant_with_min_max_vars(layer.kernel.detach(), float(layer.kernel.detach().min()), float(layer.kernel.detach().max()))
+    y_op = ax.approx_conv2d_with_min_max_vars(xq, wq, float(x.min()), float(x.max()), float(layer.kernel.detach().min()),
+                                              float(layer.kernel.detach().max()), [1, 1, 1, 1], 8, "", "SAME") + layer.bias
     assert torch.equal(y.detach(), y_op)
     # exact table + fake-quantised operands = the float convolution of those operands (the reference's own test)
     ref = torch.nn.functional.conv2d(xq.permute(0, 3, 1, 2).double(), wq.permute(3, 2, 0, 1).double(), padding=1)

@@ -178,6 +178,22 @@ def test_plan_reuse_and_fallback(ax):
     assert p5["rebuilt"] == 0 and p5["fallback"] == 1
 
 
+def test_device_resident_ranges_match_host_ranges(ax):
+    """Ranges handed over in device memory: the quantisation parameters are derived on the GPU; the result has
+    the bits of the call with the same four values passed from the host."""
+    import torch
+    rng = np.random.Generator(np.random.PCG64(31))
+    t = ax.Table(array=cases.make_table(("noisy", 36)))
+    for mm in [(-1.0, 1.0, -0.37, 0.41), (0.0, 2.5, -0.2, 0.3), (0.0, 0.0, -0.3, 0.3), (0.3, 1.7, -0.9, -0.1)]:
+        x = torch.from_numpy(rng.uniform(mm[0], mm[1] if mm[1] > mm[0] else 1.0, (2, 11, 9, 12)).astype(np.float32)).cuda()
+        f = torch.from_numpy(rng.uniform(mm[2], mm[3], (3, 3, 12, 20)).astype(np.float32)).cuda()
+        y_host, d_host = ax.approx_conv2d_with_min_max_vars(x, f, *mm, [1, 1, 1, 1], 8, t, "SAME", debug=True)
+        dev_mm = [torch.tensor(v, dtype=torch.float32, device="cuda") for v in mm]
+        y_dev, d_dev = ax.approx_conv2d_with_min_max_vars(x, f, *dev_mm, [1, 1, 1, 1], 8, t, "SAME", debug=True)
+        assert torch.equal(d_host["acc"], d_dev["acc"]) and torch.equal(d_host["qinput"], d_dev["qinput"])
+        assert torch.equal(y_host.view(torch.int32), y_dev.view(torch.int32)), mm
+
+
 def test_empty_batch(ax):
     import torch
     y = ax.approx_conv2d_with_min_max_vars(torch.zeros(0, 8, 8, 4).cuda(), torch.zeros(3, 3, 4, 8).cuda(),

@@ -11,7 +11,8 @@ SYMBOLS = [
     "axc_table_destroy", "axc_table_host_data", "axc_table_ensure_device",
     "axc_conv2d_output_dims", "axc_depthwise_conv2d_output_dims",
     "axc_conv2d_workspace_bytes", "axc_depthwise_conv2d_workspace_bytes", "axc_conv2d_plan_info",
-    "axc_conv2d_forward", "axc_depthwise_conv2d_forward", "axc_depthwise_conv2d_forward_noalloc",
+    "axc_conv2d_forward", "axc_conv2d_forward_device_ranges", "axc_depthwise_conv2d_forward",
+    "axc_depthwise_conv2d_forward_noalloc",
     "axc_quant_props", "axc_status_string", "axc_last_cuda_error", "axc_launch_count",
 ]
 
@@ -54,6 +55,9 @@ def load():
     L.axc_conv2d_plan_info.argtypes = [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_void_p]
     L.axc_conv2d_forward.argtypes = fwd
     L.axc_depthwise_conv2d_forward.argtypes = fwd
+    L.axc_conv2d_forward_device_ranges.argtypes = [C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.c_void_p,
+                                                   C.c_void_p, C.c_void_p, C.c_size_t, C.POINTER(DebugOut), C.c_int,
+                                                   C.c_void_p]
     L.axc_depthwise_conv2d_forward_noalloc.argtypes = [C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.c_float,
                                                        C.c_float, C.c_float, C.c_float, C.c_void_p, C.c_int, C.c_void_p]
     L.axc_quant_props.argtypes = [C.c_float, C.c_float, C.POINTER(C.c_float)]

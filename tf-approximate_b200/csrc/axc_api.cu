@@ -227,7 +227,7 @@ int device_info(int device, DeviceInfo *out)
 
 // Shared body of the two forward entry points.
 static int forward(bool depthwise, axc_table *table, const axc_conv_desc *desc, const float *input,
-                   const float *filter, float in_min, float in_max, float f_min, float f_max,
+                   const float *filter, const float *ranges_dev, float in_min, float in_max, float f_min, float f_max,
                    float *output, void *workspace, size_t workspace_bytes, const axc_debug_out *dbg,
                    int device, void *stream)
 {
@@ -251,7 +251,8 @@ static int forward(bool depthwise, axc_table *table, const axc_conv_desc *desc, 
     if (prev != device) AXC_CUDA(cudaSetDevice(device));
     const Quant q = make_quant(in_min, in_max, f_min, f_max);
     rc = depthwise ? launch_depthwise(lut, g, q, input, filter, output, workspace, dbg, device, cudaStream_t(stream))
-                   : launch_dense(lut, table_uid(table), g, q, input, filter, output, workspace, dbg, device, cudaStream_t(stream));
+                   : launch_dense(lut, table_uid(table), g, q, ranges_dev, input, filter, output, workspace, dbg, device,
+                                  cudaStream_t(stream));
     if (prev != device) cudaSetDevice(prev);
     return rc;
 }
@@ -383,7 +384,16 @@ int axc_conv2d_forward(axc_table *table, const axc_conv_desc *desc, const float 
                        void *workspace, size_t workspace_bytes, const axc_debug_out *debug, int device,
                        void *stream)
 {
-    return axc::forward(false, table, desc, input, filter, in_min, in_max, f_min, f_max, output, workspace,
+    return axc::forward(false, table, desc, input, filter, nullptr, in_min, in_max, f_min, f_max, output, workspace,
+                        workspace_bytes, debug, device, stream);
+}
+
+int axc_conv2d_forward_device_ranges(axc_table *table, const axc_conv_desc *desc, const float *input,
+                                     const float *filter, const float *ranges, float *output, void *workspace,
+                                     size_t workspace_bytes, const axc_debug_out *debug, int device, void *stream)
+{
+    if (!ranges) return AXC_INVALID_ARGUMENT;
+    return axc::forward(false, table, desc, input, filter, ranges, 0.f, 0.f, 0.f, 0.f, output, workspace,
                         workspace_bytes, debug, device, stream);
 }
 
@@ -392,7 +402,7 @@ int axc_depthwise_conv2d_forward(axc_table *table, const axc_conv_desc *desc, co
                                  float *output, void *workspace, size_t workspace_bytes,
                                  const axc_debug_out *debug, int device, void *stream)
 {
-    return axc::forward(true, table, desc, input, filter, in_min, in_max, f_min, f_max, output, workspace,
+    return axc::forward(true, table, desc, input, filter, nullptr, in_min, in_max, f_min, f_max, output, workspace,
                         workspace_bytes, debug, device, stream);
 }
 

@@ -50,7 +50,7 @@ struct DenseParams {
     long long M;
     int tiles_n;
     long long tiles_total;
-    float in_off, in_inv, s1s2, m1, m2, km1m2;
+    const DevQuant *dq;    // quantisation parameters of the call (workspace header)
     int vec_ok;            // C % 4 == 0 and 16-byte aligned input
     const int *gate;       // when set: run only if *gate != 0 (the scheduled kernel handed the call over)
 };
@@ -103,11 +103,12 @@ __device__ __forceinline__ float lds_f32(unsigned addr)
 // Filter preparation: quantise the fp32 filter [K][Cout] into kernel-layout program words
 // (one uint4 per (l/4, j): the four words of l = 4*lq .. 4*lq+3) and, optionally, the plain
 // uint8 matrix.  Weight quantiser as tf2/src/approx_nn_conv_kernels.cpp:243.
-__global__ void filter_prep_kernel(const float *__restrict__ filter, int K, int Cout, float f_off, float f_inv,
+__global__ void filter_prep_kernel(const float *__restrict__ filter, int K, int Cout, const DevQuant *__restrict__ dq,
                                    uint4 *__restrict__ prog, uint8_t *__restrict__ qfilter, int *status,
                                    const int *gate)
 {
     if (gate && *gate == 0) return;
+    const float f_off = dq->f_off, f_inv = dq->f_inv;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx == 0) *status = 0;
     const int kq = (K + 3) / 4;
@@ -151,9 +152,10 @@ __global__ void filter_sum_kernel(const float *__restrict__ filter, int K, int C
 }
 
 // Element-wise quantised copy of the input, for the parity taps only.
-__global__ void quantize_tensor_kernel(const float *__restrict__ x, long long n, float off, float inv,
+__global__ void quantize_tensor_kernel(const float *__restrict__ x, long long n, const DevQuant *__restrict__ dq,
                                        uint8_t *__restrict__ q)
 {
+    const float off = dq->in_off, inv = dq->in_inv;
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (; i < n; i += stride) q[i] = uint8_t(quantize_u8(x[i], off, inv));
@@ -178,6 +180,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     if (P.gate && *P.gate == 0) return;
+    const DevQuant Q = *P.dq;
     const unsigned dyn0 = (unsigned)__cvta_generic_to_shared(smem_raw);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
@@ -331,10 +334,10 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
                     const int p = (s * kWarps + warp) * 4 + p_lo;
                     const float4 v = a_stage[h * PIX_SLOTS + s];
                     uint32_t packed = 0;
-                    if (l0 + 0 < P.K) packed |= quantize_u8(v.x, P.in_off, P.in_inv);
-                    if (l0 + 1 < P.K) packed |= quantize_u8(v.y, P.in_off, P.in_inv) << 8;
-                    if (l0 + 2 < P.K) packed |= quantize_u8(v.z, P.in_off, P.in_inv) << 16;
-                    if (l0 + 3 < P.K) packed |= quantize_u8(v.w, P.in_off, P.in_inv) << 24;
+                    if (l0 + 0 < P.K) packed |= quantize_u8(v.x, Q.in_off, Q.in_inv);
+                    if (l0 + 1 < P.K) packed |= quantize_u8(v.y, Q.in_off, Q.in_inv) << 8;
+                    if (l0 + 2 < P.K) packed |= quantize_u8(v.z, Q.in_off, Q.in_inv) << 16;
+                    if (l0 + 3 < P.K) packed |= quantize_u8(v.w, Q.in_off, Q.in_inv) << 24;
                     sts_u32(sA + buf * A_BYTES + (lq * AROW + p) * 4, packed);
                 }
 #pragma unroll
@@ -443,15 +446,15 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
         // ---- dequantisation: ((S*s1s2 + m2*aSum) + m1*bSum) - K*m1m2 -----------------
         const int j = j0 + wn * 32 + lane;
         if (j < P.Cout) {
-            const float t2 = __fmul_rn(P.m1, __ldg(P.bsum + j));
+            const float t2 = __fmul_rn(Q.m1, __ldg(P.bsum + j));
 #pragma unroll
             for (int i = 0; i < kPixPerLane; ++i) {
                 const long long p = m0 + wm * kPixPerLane + i;
                 if (p < P.M) {
                     const float a_sum = lds_f32(sAsum + (wm * kPixPerLane + i) * 4);
-                    const float t0 = __fmul_rn(float(acc[i]), P.s1s2);
-                    const float t1 = __fmul_rn(P.m2, a_sum);
-                    const float o = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), P.km1m2);
+                    const float t0 = __fmul_rn(float(acc[i]), Q.s1s2);
+                    const float t1 = __fmul_rn(Q.m2, a_sum);
+                    const float o = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), Q.km1m2);
                     P.output[p * P.Cout + j] = o;
                     if (P.acc_out) P.acc_out[p * P.Cout + j] = acc[i];
                 }
@@ -498,9 +501,9 @@ static int dense_variant()
     return v;
 }
 
-int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const Quant &q, const float *input,
-                 const float *filter, float *output, void *workspace, const axc_debug_out *dbg, int device,
-                 cudaStream_t stream)
+int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const Quant &q, const float *ranges_dev,
+                 const float *input, const float *filter, float *output, void *workspace, const axc_debug_out *dbg,
+                 int device, cudaStream_t stream)
 {
     DeviceInfo di;
     int rc = device_info(device, &di);
@@ -516,30 +519,33 @@ int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, con
     float *bsum = reinterpret_cast<float *>(wsb + ws.sums_off);
     int *status = reinterpret_cast<int *>(wsb + ws.status_off);
     const int *gate = nullptr;
+    const DevQuant *dq = reinterpret_cast<const DevQuant *>(plan + kDevQuantOffset);
 
+    rc = launch_quant(q, ranges_dev, g.K, plan, stream);
+    if (rc) return rc;
     if (dbg && dbg->qinput) {
         const long long n = (long long)g.N * g.H * g.W * g.C;
         if (n > 0) {
             const unsigned blocks = unsigned(n / 256 + 1 < 4096 ? n / 256 + 1 : 4096);
-            quantize_tensor_kernel<<<blocks, 256, 0, stream>>>(input, n, q.in_off, q.in_inv, dbg->qinput);
+            quantize_tensor_kernel<<<blocks, 256, 0, stream>>>(input, n, dq, dbg->qinput);
             AXC_CUDA(cudaGetLastError());
             count_launch();
         }
     }
     if (scheduled) {
-        rc = launch_plan(lut_dev, table_uid, g, q, filter, plan, L, dbg ? dbg->qfilter : nullptr, stream);
+        rc = launch_plan(lut_dev, table_uid, g, filter, plan, L, dbg ? dbg->qfilter : nullptr, stream);
         if (rc) return rc;
         float *asum = reinterpret_cast<float *>(wsb + ws.total);
         rc = launch_patch_sums(g, input, asum, stream);
         if (rc) return rc;
-        rc = launch_dense_sched(g, q, input, asum, output, plan, L, dbg ? dbg->acc : nullptr, di, stream);
+        rc = launch_dense_sched(g, input, asum, output, plan, L, dbg ? dbg->acc : nullptr, di, stream);
         if (rc) return rc;
         gate = &reinterpret_cast<const PlanHeader *>(plan)->fallback;
     }
     {
         const long long items = (long long)((g.K + 3) / 4) * g.Cout;
         const unsigned blocks = unsigned((items + 255) / 256);
-        filter_prep_kernel<<<blocks, 256, 0, stream>>>(filter, g.K, g.Cout, q.f_off, q.f_inv, prog,
+        filter_prep_kernel<<<blocks, 256, 0, stream>>>(filter, g.K, g.Cout, dq, prog,
                                                        (dbg && !scheduled) ? dbg->qfilter : nullptr, status, gate);
         AXC_CUDA(cudaGetLastError());
         filter_sum_kernel<<<unsigned((g.Cout + 31) / 32), 32, 0, stream>>>(filter, g.K, g.Cout, bsum, gate);
@@ -556,12 +562,7 @@ int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, con
     P.sh = g.sh; P.sw = g.sw; P.dh = g.dh; P.dw = g.dw; P.ph = g.ph; P.pw = g.pw; P.OH = g.OH; P.OW = g.OW;
     P.K = g.K; P.M = g.M;
     P.tiles_n = 0; P.tiles_total = 0;
-    P.in_off = q.in_off; P.in_inv = q.in_inv; P.s1s2 = q.s1s2; P.m1 = q.m1; P.m2 = q.m2;
-    {
-        volatile float kf = float(g.K);
-        volatile float t3 = kf * q.m1m2;
-        P.km1m2 = t3;
-    }
+    P.dq = dq;
     P.vec_ok = (g.C % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
     if (g.Cout <= 32) return launch_dense_variant<1>(P, di, stream);
     return launch_dense_variant<2>(P, di, stream);

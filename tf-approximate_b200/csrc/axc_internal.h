@@ -68,8 +68,9 @@ size_t dense_workspace_total(int K, int Cout, long long M);   // plan of the sch
 Workspace depthwise_workspace(int KHW, int C, int mult);
 
 // Kernel launchers (axc_conv.cu / axc_depthwise.cu).
-int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const Quant &q, const float *input,
-                 const float *filter, float *output, void *workspace, const axc_debug_out *dbg,
+// ranges_dev: NULL, or {in_min, in_max, f_min, f_max} in device memory (then `q` is ignored).
+int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const Quant &q, const float *ranges_dev,
+                 const float *input, const float *filter, float *output, void *workspace, const axc_debug_out *dbg,
                  int device, cudaStream_t stream);
 int launch_depthwise(const uint16_t *lut_dev, const Geom &g, const Quant &q, const float *input,
                      const float *filter, float *output, void *workspace, const axc_debug_out *dbg,

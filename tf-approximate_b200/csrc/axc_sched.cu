@@ -89,16 +89,17 @@ __device__ __forceinline__ int slot_bank(int s) { return ((s & 127) >> 1) & 31; 
 // ------------------------------------------------------------------------------------------------
 // plan_check: quantised filter vs. stored copy
 // ------------------------------------------------------------------------------------------------
-__global__ void plan_check_kernel(const float *__restrict__ filter, long long count, float f_off, float f_inv,
+__global__ void plan_check_kernel(const float *__restrict__ filter, long long count, const DevQuant *__restrict__ dq,
                                   uint8_t *__restrict__ qf, uint8_t *__restrict__ qf_debug, PlanHeader *hdr,
                                   PlanHeader want)
 {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const float f_off = dq->f_off, f_inv = dq->f_inv;
     if (idx == 0) {
         const bool same = hdr->magic == want.magic && hdr->K == want.K && hdr->Cout == want.Cout && hdr->G == want.G &&
                           hdr->NCH == want.NCH && hdr->KC == want.KC && hdr->sqcap == want.sqcap &&
-                          hdr->table_uid == want.table_uid && hdr->f_off_bits == want.f_off_bits &&
-                          hdr->f_inv_bits == want.f_inv_bits;
+                          hdr->table_uid == want.table_uid && hdr->f_off_bits == __float_as_uint(f_off) &&
+                          hdr->f_inv_bits == __float_as_uint(f_inv);
         if (!same) atomicOr(&hdr->dirty, 1);
         hdr->status = 0;
     }
@@ -116,7 +117,7 @@ __global__ void plan_check_kernel(const float *__restrict__ filter, long long co
 // the 32 banks (largest first, into the bank with the smallest mass that still has one of its 8 slots)
 // ------------------------------------------------------------------------------------------------
 __global__ void plan_sigma_kernel(const uint8_t *__restrict__ qf, long long count, uint8_t *__restrict__ sigma,
-                                  PlanHeader *hdr, PlanHeader want)
+                                  PlanHeader *hdr, PlanHeader want, const DevQuant *__restrict__ dq)
 {
     if (hdr->dirty == 0) return;
     __shared__ unsigned hist[256];
@@ -164,7 +165,7 @@ __global__ void plan_sigma_kernel(const uint8_t *__restrict__ qf, long long coun
     if (t == 0) {
         hdr->magic = want.magic; hdr->K = want.K; hdr->Cout = want.Cout; hdr->G = want.G; hdr->NCH = want.NCH;
         hdr->KC = want.KC; hdr->sqcap = want.sqcap; hdr->table_uid = want.table_uid;
-        hdr->f_off_bits = want.f_off_bits; hdr->f_inv_bits = want.f_inv_bits;
+        hdr->f_off_bits = __float_as_uint(dq->f_off); hdr->f_inv_bits = __float_as_uint(dq->f_inv);
         hdr->fallback = 0;
     }
 }
@@ -370,7 +371,6 @@ struct SchedParams {
     int g_base, g_count;      // channel groups [g_base, g_base + g_count) are served by this launch
     int tiles_n;              // channel tiles of 32*GW channels
     long long tiles_total;    // pixel tile groups x channel tiles
-    float in_off, in_inv, s1s2, m1, m2, km1m2;
     int vec_ok;
     unsigned long long magic_c, magic_kw;   // ceil(2^40 / C), ceil(2^40 / KW): n / d == (n * magic) >> 40 for n*d < 2^40
 };
@@ -407,6 +407,7 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
     asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
     const int KC = P.L.KC;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const DevQuant Q = *reinterpret_cast<const DevQuant *>(P.plan + kDevQuantOffset);
     // small tables below the table planes, then as many activation buffers as fit; the rest above the planes
     unsigned cur = (dyn0 + 15u) & ~15u;
     const unsigned sGeo = cur;               cur += unsigned(NT) * kTilePix * 16u;
@@ -564,10 +565,10 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
                             const int lq = lq_first + 8 * (s0 + u);
                             const unsigned a = bb + unsigned(lq * 4) * 16u;
                             const float4 v = st[u];
-                            sts8(a, q_u8(v.x, P.in_off, P.in_inv));
-                            if (lq * 4 + 1 < kc) sts8(a + 16, q_u8(v.y, P.in_off, P.in_inv));
-                            if (lq * 4 + 2 < kc) sts8(a + 32, q_u8(v.z, P.in_off, P.in_inv));
-                            if (lq * 4 + 3 < kc) sts8(a + 48, q_u8(v.w, P.in_off, P.in_inv));
+                            sts8(a, q_u8(v.x, Q.in_off, Q.in_inv));
+                            if (lq * 4 + 1 < kc) sts8(a + 16, q_u8(v.y, Q.in_off, Q.in_inv));
+                            if (lq * 4 + 2 < kc) sts8(a + 32, q_u8(v.z, Q.in_off, Q.in_inv));
+                            if (lq * 4 + 3 < kc) sts8(a + 48, q_u8(v.w, Q.in_off, Q.in_inv));
                         }
                     }
                 }
@@ -646,7 +647,7 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
         }
         {
             const int j = (P.g_base + nt * GW + gl) * 32 + lane;
-            if (nt != t2_nt) { t2 = j < P.Cout ? __fmul_rn(P.m1, __ldg(bsum + j)) : 0.0f; t2_nt = nt; }
+            if (nt != t2_nt) { t2 = j < P.Cout ? __fmul_rn(Q.m1, __ldg(bsum + j)) : 0.0f; t2_nt = nt; }
         }
         for (int c = 0; c < NCH; ++c) {
             // first two quads of the next (tile group, chunk): requested now, consumed after the barrier
@@ -697,9 +698,9 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
                     const long long pix = m0 + (slot * NTW + i) * kTilePix + x;
                     const float a_sum = __shfl_sync(0xffffffffu, asum_lane[i], x);
                     if (live && pix < P.M) {
-                        const float t0 = __fmul_rn(float(acc[i][x]), P.s1s2);
-                        const float t1 = __fmul_rn(P.m2, a_sum);
-                        P.output[pix * P.Cout + j] = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), P.km1m2);
+                        const float t0 = __fmul_rn(float(acc[i][x]), Q.s1s2);
+                        const float t1 = __fmul_rn(Q.m2, a_sum);
+                        P.output[pix * P.Cout + j] = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), Q.km1m2);
                         if (P.acc_out) P.acc_out[pix * P.Cout + j] = acc[i][x];
                     }
                     acc[i][x] = 0;
@@ -884,22 +885,70 @@ PlanLayout plan_layout(int K, int Cout)
     return L;
 }
 
-int launch_plan(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const Quant &q, const float *filter,
+// Range nudging on the device, operation by operation as on the host (axc_api.cu var_quant_props).
+__device__ void dev_var_quant(float min_v, float max_v, float *scale, float *inv, float *offset)
+{
+    float s = 0.0f, i = 0.0f, nudged_min = 0.0f;
+    if (min_v != 0.0f || max_v != 0.0f) {
+        s = __fdiv_rn(__fsub_rn(max_v, min_v), 255.0f);
+        const float zp_from_min = __fsub_rn(0.0f, __fdiv_rn(min_v, s));
+        float zp;
+        if (zp_from_min < 0.0f) zp = 0.0f;
+        else if (zp_from_min > 255.0f) zp = 255.0f;
+        else zp = roundf(zp_from_min);                       // half away from zero, like std::round
+        nudged_min = __fmul_rn(__fsub_rn(0.0f, zp), s);      // a true subtraction: +0.0 for zp == 0
+        i = __fdiv_rn(1.0f, s);
+    }
+    *scale = s; *inv = i; *offset = nudged_min;
+}
+
+__global__ void quant_from_ranges_kernel(const float *__restrict__ ranges, int K, DevQuant *out)
+{
+    float s1, i1, o1, s2, i2, o2;
+    dev_var_quant(ranges[0], ranges[1], &s1, &i1, &o1);
+    dev_var_quant(ranges[2], ranges[3], &s2, &i2, &o2);
+    DevQuant q;
+    q.in_off = o1; q.in_inv = i1; q.f_off = o2; q.f_inv = i2;
+    q.s1s2 = __fmul_rn(s1, s2); q.m1 = o1; q.m2 = o2;
+    q.km1m2 = __fmul_rn(float(K), __fmul_rn(o1, o2));
+    *out = q;
+}
+
+__global__ void quant_store_kernel(DevQuant q, DevQuant *out) { *out = q; }
+
+int launch_quant(const Quant &q, const float *ranges_dev, int K, unsigned char *plan, cudaStream_t stream)
+{
+    DevQuant *dst = reinterpret_cast<DevQuant *>(plan + kDevQuantOffset);
+    if (ranges_dev) {
+        quant_from_ranges_kernel<<<1, 1, 0, stream>>>(ranges_dev, K, dst);
+    } else {
+        DevQuant d;
+        d.in_off = q.in_off; d.in_inv = q.in_inv; d.f_off = q.f_off; d.f_inv = q.f_inv;
+        d.s1s2 = q.s1s2; d.m1 = q.m1; d.m2 = q.m2;
+        volatile float kf = float(K);
+        volatile float t3 = kf * q.m1m2;
+        d.km1m2 = t3;
+        quant_store_kernel<<<1, 1, 0, stream>>>(d, dst);
+    }
+    AXC_CUDA(cudaGetLastError());
+    count_launch();
+    return AXC_OK;
+}
+
+int launch_plan(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const float *filter,
                 unsigned char *plan, const PlanLayout &L, uint8_t *qf_debug, cudaStream_t stream)
 {
     PlanHeader want = {};
     want.magic = 0x41584333u;  // "AXC3"
     want.K = g.K; want.Cout = g.Cout; want.G = L.G; want.NCH = L.NCH; want.KC = L.KC; want.sqcap = L.sqcap;
     want.table_uid = table_uid;
-    memcpy(&want.f_off_bits, &q.f_off, 4);
-    memcpy(&want.f_inv_bits, &q.f_inv, 4);
     PlanHeader *hdr = reinterpret_cast<PlanHeader *>(plan);
     AXC_CUDA(cudaMemsetAsync(&hdr->dirty, 0, sizeof(int), stream));
     const long long count = (long long)g.K * g.Cout;
-    plan_check_kernel<<<unsigned((count + 255) / 256), 256, 0, stream>>>(filter, count, q.f_off, q.f_inv,
-                                                                       plan + L.qf_off, qf_debug, hdr, want);
+    const DevQuant *dq = reinterpret_cast<const DevQuant *>(plan + kDevQuantOffset);
+    plan_check_kernel<<<unsigned((count + 255) / 256), 256, 0, stream>>>(filter, count, dq, plan + L.qf_off, qf_debug, hdr, want);
     AXC_CUDA(cudaGetLastError());
-    plan_sigma_kernel<<<1, 256, 0, stream>>>(plan + L.qf_off, count, plan + L.sigma_off, hdr, want);
+    plan_sigma_kernel<<<1, 256, 0, stream>>>(plan + L.qf_off, count, plan + L.sigma_off, hdr, want, dq);
     AXC_CUDA(cudaGetLastError());
     const unsigned blocks = unsigned(L.G * L.NCH + 256 + (g.Cout + 31) / 32);
     const size_t sched_smem = size_t(32) * L.KC * 2 + 2 * size_t(32) * 256 * 2 + 32 * 32;
@@ -943,7 +992,7 @@ int launch_patch_sums(const Geom &g, const float *input, float *asum, cudaStream
     return AXC_OK;
 }
 
-int launch_dense_sched(const Geom &g, const Quant &q, const float *input, const float *asum, float *output,
+int launch_dense_sched(const Geom &g, const float *input, const float *asum, float *output,
                        const unsigned char *plan, const PlanLayout &L, int32_t *acc_out, const DeviceInfo &di,
                        cudaStream_t stream)
 {
@@ -952,12 +1001,6 @@ int launch_dense_sched(const Geom &g, const Quant &q, const float *input, const 
     P.N = g.N; P.H = g.H; P.W = g.W; P.C = g.C; P.KH = g.KH; P.KW = g.KW; P.Cout = g.Cout;
     P.sh = g.sh; P.sw = g.sw; P.dh = g.dh; P.dw = g.dw; P.ph = g.ph; P.pw = g.pw; P.OH = g.OH; P.OW = g.OW;
     P.K = g.K; P.M = g.M; P.tiles_n = 0; P.tiles_total = 0;
-    P.in_off = q.in_off; P.in_inv = q.in_inv; P.s1s2 = q.s1s2; P.m1 = q.m1; P.m2 = q.m2;
-    {
-        volatile float kf = float(g.K);
-        volatile float t3 = kf * q.m1m2;
-        P.km1m2 = t3;
-    }
     P.vec_ok = (g.C % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
     // n / d == (n * magic) >> 40 holds while n * d < 2^40; launch_dense keeps shapes beyond that on the common-K kernel
     P.magic_c = ((1ull << 40) + unsigned(g.C) - 1) / unsigned(g.C);

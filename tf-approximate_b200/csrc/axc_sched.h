@@ -25,6 +25,13 @@ struct PlanHeader {
     int pad[3];
 };
 
+// Quantisation parameters of a call as the kernels read them.  Filled from host values, or on the device from
+// four range scalars that live in device memory (no host round trip).  Kept in the workspace header.
+struct DevQuant {
+    float in_off, in_inv, f_off, f_inv, s1s2, m1, m2, km1m2;
+};
+constexpr size_t kDevQuantOffset = 128;   // inside the 256-byte plan header block
+
 struct PlanLayout {
     int G, NCH, KC, sqcap;   // channel groups of 32, K chunks, chunk length, step-quads reserved per (group, chunk)
     size_t qf_off, sigma_off, lut_off, bsum_off, steps_off, prog_off, total;
@@ -32,13 +39,17 @@ struct PlanLayout {
 
 PlanLayout plan_layout(int K, int Cout);
 
-int launch_plan(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const Quant &q, const float *filter,
+// Writes the DevQuant block of `plan`: from the host values `q`, or - when ranges_dev is given - on the device
+// from {in_min, in_max, f_min, f_max} read there (same arithmetic as the host: tf2/src/approx_ops_types.h:29-49,135-197).
+int launch_quant(const Quant &q, const float *ranges_dev, int K, unsigned char *plan, cudaStream_t stream);
+
+int launch_plan(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const float *filter,
                 unsigned char *plan, const PlanLayout &L, uint8_t *qf_debug, cudaStream_t stream);
 
 // aSum[p] for every output pixel, in the reference's order of additions.
 int launch_patch_sums(const Geom &g, const float *input, float *asum, cudaStream_t stream);
 
-int launch_dense_sched(const Geom &g, const Quant &q, const float *input, const float *asum, float *output,
+int launch_dense_sched(const Geom &g, const float *input, const float *asum, float *output,
                        const unsigned char *plan, const PlanLayout &L, int32_t *acc_out, const DeviceInfo &di,
                        cudaStream_t stream);
 

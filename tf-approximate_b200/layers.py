@@ -8,34 +8,40 @@ from .ops import approx_conv2d_with_min_max_vars
 
 
 def _nudge(min_v, max_v, num_bits=8):
-    """TensorFlow fake-quant range nudging (restated in the reference at tf2/src/approx_ops_types.h:29-49),
-    in fp32 like the op."""
+    """TensorFlow fake-quant range nudging (restated in the reference at tf2/src/approx_ops_types.h:29-49), in fp32
+    like the op.  Works on 0-d tensors of any device, so nothing is synchronised with the host.  Returns tensors
+    (nudged_min, nudged_max, scale); a zero range gives zeros (tf2/src/approx_ops_types.h:135-152)."""
     f32 = torch.float32
-    qmin, qmax = 0.0, float((1 << num_bits) - 1)
     mn = torch.as_tensor(min_v, dtype=f32)
-    mx = torch.as_tensor(max_v, dtype=f32)
-    scale = (mx - mn) / torch.tensor(qmax - qmin, dtype=f32)
-    zp_from_min = torch.tensor(qmin, dtype=f32) - mn / scale
-    zp = torch.where(zp_from_min < qmin, torch.tensor(qmin), torch.where(
-        zp_from_min > qmax, torch.tensor(qmax), torch.sign(zp_from_min) * torch.floor(torch.abs(zp_from_min) + 0.5)))
-    nudged_min = (torch.tensor(qmin, dtype=f32) - zp) * scale
-    nudged_max = (torch.tensor(qmax, dtype=f32) - zp) * scale
-    return float(nudged_min), float(nudged_max), float(scale)
+    mx = torch.as_tensor(max_v, dtype=f32).to(mn.device)
+    qmin = torch.zeros((), dtype=f32, device=mn.device)
+    qmax = torch.full((), float((1 << num_bits) - 1), dtype=f32, device=mn.device)
+    zero_range = (mn == 0) & (mx == 0)
+    scale = (mx - mn) / (qmax - qmin)
+    safe = torch.where(zero_range, torch.ones_like(scale), scale)
+    zp_from_min = qmin - mn / safe
+    rounded = torch.sign(zp_from_min) * torch.floor(torch.abs(zp_from_min) + 0.5)   # half away from zero
+    zp = torch.where(zp_from_min < qmin, qmin, torch.where(zp_from_min > qmax, qmax, rounded))
+    nudged_min = (qmin - zp) * safe
+    nudged_max = (qmax - zp) * safe
+    z = torch.zeros_like(scale)
+    return (torch.where(zero_range, z, nudged_min), torch.where(zero_range, z, nudged_max),
+            torch.where(zero_range, z, scale))
 
 
 def fake_quant_with_min_max_vars(x, min_v, max_v, num_bits=8):
     """Forward of TensorFlow's FakeQuantWithMinMaxVars: clamp to the nudged range and snap to its grid.
     The reference applies it to input and kernel before the op
-    (tf2/python/keras/layers/fake_approx_convolutional.py:233-242)."""
-    min_v = float(min_v)
-    max_v = float(max_v)
-    if min_v == 0.0 and max_v == 0.0:
-        return torch.zeros_like(x)
-    nmin, nmax, scale = _nudge(min_v, max_v, num_bits)
-    inv = torch.tensor(1.0, dtype=torch.float32) / torch.tensor(scale, dtype=torch.float32)
-    clamped = torch.clamp(x, nmin, nmax)
-    q = torch.floor((clamped - nmin) * float(inv) + 0.5)
-    return q * scale + nmin
+    (tf2/python/keras/layers/fake_approx_convolutional.py:233-242).  min_v / max_v may be Python floats or 0-d
+    tensors on x's device (then no host synchronisation happens)."""
+    mn = torch.as_tensor(min_v, dtype=torch.float32).to(x.device)
+    mx = torch.as_tensor(max_v, dtype=torch.float32).to(x.device)
+    nmin, nmax, scale = _nudge(mn, mx, num_bits)
+    zero_range = scale == 0
+    inv = torch.ones((), dtype=torch.float32, device=x.device) / torch.where(zero_range, torch.ones_like(scale), scale)
+    clamped = torch.minimum(torch.maximum(x, nmin), nmax)
+    q = torch.floor((clamped - nmin) * inv + 0.5)
+    return torch.where(zero_range, torch.zeros_like(x), q * scale + nmin)
 
 
 class _ApproxConvFn(torch.autograd.Function):
@@ -88,9 +94,10 @@ class FakeApproxConv2D(torch.nn.Module):
         self.bias = torch.nn.Parameter(torch.zeros(filters)) if use_bias else None
 
     def forward(self, inputs):
-        input_min, input_max = float(inputs.detach().min()), float(inputs.detach().max())
+        # per-batch ranges stay on the device: 0-d tensors, consumed by the op without a host round trip
+        input_min, input_max = torch.aminmax(inputs.detach())
         q_in = fake_quant_with_min_max_vars(inputs, input_min, input_max, self.num_bits)
-        k_min, k_max = float(self.kernel.detach().min()), float(self.kernel.detach().max())
+        k_min, k_max = torch.aminmax(self.kernel.detach())
         q_k = fake_quant_with_min_max_vars(self.kernel, k_min, k_max, self.num_bits)
         # straight-through estimator for the fake-quant steps, as TF's fake-quant gradient inside the range
         q_in = inputs + (q_in - inputs).detach()

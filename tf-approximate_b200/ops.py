@@ -183,11 +183,21 @@ def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_
                  "acc": torch.empty(oshape, dtype=torch.int32, device=dev)}
         dbg = _lib.DebugOut(dbg_t["qinput"].data_ptr(), dbg_t["qfilter"].data_ptr(), dbg_t["acc"].data_ptr())
         dbg_ptr = C.byref(dbg)
-    fwd = L.axc_depthwise_conv2d_forward if depthwise else L.axc_conv2d_forward
     stream = torch.cuda.current_stream(dev).cuda_stream
-    st = fwd(table.handle, C.byref(d), x.data_ptr(), f.data_ptr(), _scalar(input_min), _scalar(input_max),
-             _scalar(filter_min), _scalar(filter_max), out.data_ptr(), ws.data_ptr(), ws.numel(), dbg_ptr,
-             dev.index if dev.index is not None else torch.cuda.current_device(), C.c_void_p(stream))
+    dev_index = dev.index if dev.index is not None else torch.cuda.current_device()
+    ranges = (input_min, input_max, filter_min, filter_max)
+    if not depthwise and all(isinstance(v, torch.Tensor) and v.is_cuda for v in ranges):
+        # the four scalars already live on the GPU (e.g. fresh reductions): hand them over as they are, no
+        # device-to-host synchronisation
+        r = torch.stack([v.reshape(()).to(torch.float32) for v in ranges]).contiguous()
+        st = L.axc_conv2d_forward_device_ranges(table.handle, C.byref(d), x.data_ptr(), f.data_ptr(), r.data_ptr(),
+                                                out.data_ptr(), ws.data_ptr(), ws.numel(), dbg_ptr, dev_index,
+                                                C.c_void_p(stream))
+    else:
+        fwd = L.axc_depthwise_conv2d_forward if depthwise else L.axc_conv2d_forward
+        st = fwd(table.handle, C.byref(d), x.data_ptr(), f.data_ptr(), _scalar(input_min), _scalar(input_max),
+                 _scalar(filter_min), _scalar(filter_max), out.data_ptr(), ws.data_ptr(), ws.numel(), dbg_ptr,
+                 dev_index, C.c_void_p(stream))
     raise_for_status(st, "ApproxConv2D", _cuda_detail() if st == 100 else "")
     if debug:
         if not depthwise:
@@ -205,7 +215,8 @@ def approx_conv2d_with_min_max_vars(input, filter, input_min, input_max, filter_
     """Forward pass of `ApproxConv2DWithMinMaxVars`.
 
     input [N,H,W,C] and filter [KH,KW,C,Cout] are fp32 CUDA tensors; the four min/max values are
-    host scalars (Python floats or 0-d tensors); `mul_map_file` is the raw uint16[65536] table file
+    host scalars (Python floats or 0-d CPU tensors) or - all four - 0-d CUDA tensors, which are then consumed on
+    the device without a host round trip; `mul_map_file` is the raw uint16[65536] table file
     ('' = exact products) or a `Table`.  Returns the fp32 output [N,OH,OW,Cout]; with `debug=True`
     also the quantised operands and the int32 accumulators."""
     return _forward(False, input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
