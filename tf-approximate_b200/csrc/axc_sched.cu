@@ -237,7 +237,9 @@ __global__ void __launch_bounds__(32) plan_build_kernel(const float *__restrict_
     const int g = int(blockIdx.x) / L.NCH, c = int(blockIdx.x) % L.NCH;
     const int l_base = c * L.KC;
     const int kc = min(L.KC, K - l_base);
-    const int j = g * 32 + lane;
+    // at most 16 output channels: the two half warps carry the same channels (for two different pixel tiles)
+    const bool dual = L.G == 1 && Cout <= 16;
+    const int j = g * 32 + (dual ? (lane & 15) : lane);
     const bool live = j < Cout;
     unsigned short *my_order = order + lane * L.KC;
     unsigned short *my_pos = pos + lane * 256;
@@ -369,6 +371,7 @@ struct SchedParams {
     int sh, sw, dh, dw, ph, pw, OH, OW, K;
     long long M;
     int g_base, g_count;      // channel groups [g_base, g_base + g_count) are served by this launch
+    int dual;                 // Cout <= 16: lanes 16..31 repeat the channels of lanes 0..15 on a second pixel tile
     int tiles_n;              // channel tiles of 32*GW channels
     long long tiles_total;    // pixel tile groups x channel tiles
     int vec_ok;
@@ -408,9 +411,10 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
     const int KC = P.L.KC;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const DevQuant Q = *reinterpret_cast<const DevQuant *>(P.plan + kDevQuantOffset);
+    const int nt_eff = P.dual ? 2 * NT : NT;         // pixel tiles per tile group
     // small tables below the table planes, then as many activation buffers as fit; the rest above the planes
     unsigned cur = (dyn0 + 15u) & ~15u;
-    const unsigned sGeo = cur;               cur += unsigned(NT) * kTilePix * 16u;
+    const unsigned sGeo = cur;               cur += unsigned(nt_eff) * kTilePix * 16u;
     const bool tap_table = !P.vec_ok && P.K <= kTapTableMax;
     const unsigned sTap = cur;               cur += tap_table ? unsigned(P.K) * 8u : 0u;
     const int n_sched = P.L.G * P.L.NCH;
@@ -422,11 +426,11 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
     const int n_a = cur < kLutBase ? int((kLutBase - cur) / buf_bytes) : 0;
     const unsigned sBufB = kBuf1Base + 128u;         // after the 32 zero words
     const int n_b = int((kWindowEnd - sBufB) / buf_bytes);
-    if (cur > kLutBase || n_a + n_b < 2 * NT || dyn0 + dyn_size < kWindowEnd) {
+    if (cur > kLutBase || n_a + n_b < 2 * nt_eff || dyn0 + dyn_size < kWindowEnd) {
         if (tid == 0) atomicExch(const_cast<int *>(&hdr->status), 2);
         return;
     }
-    auto buf_addr = [&](int k) -> unsigned {          // k = parity * NT + tile
+    auto buf_addr = [&](int k) -> unsigned {          // k = parity * nt_eff + tile
         return k < n_a ? sBufA + unsigned(k) * buf_bytes : sBufB + unsigned(k - n_a) * buf_bytes;
     };
 
@@ -435,7 +439,7 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
         const uint4 *src = reinterpret_cast<const uint4 *>(P.plan + P.L.lut_off);
         for (int i = tid; i < 8192; i += kSchedThreads) sts128(kLutBase + unsigned(i) * 16u, __ldg(src + i));
         if (tid < 8) sts128(kBuf1Base + tid * 16, make_uint4(0, 0, 0, 0));
-        for (int i = tid; i < 2 * NT * 8; i += kSchedThreads) sts128(buf_addr(i >> 3) + unsigned(i & 7) * 16u, make_uint4(0, 0, 0, 0));
+        for (int i = tid; i < 2 * nt_eff * 8; i += kSchedThreads) sts128(buf_addr(i >> 3) + unsigned(i & 7) * 16u, make_uint4(0, 0, 0, 0));
         if (steps_in_smem) {
             const int *sq = reinterpret_cast<const int *>(P.plan + P.L.steps_off);
             for (int i = tid; i < n_sched; i += kSchedThreads) sts32(sSteps + unsigned(i) * 4u, unsigned(__ldg(sq + i)));
@@ -463,7 +467,7 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
         const long long tile = blockIdx.x + tl * gridDim.x;
         const long long mt = tile / P.tiles_n;
         *nt = int(tile - mt * P.tiles_n);
-        *m0 = mt * (kTilePix * NT);
+        *m0 = mt * (kTilePix * nt_eff);
     };
 
     if (warp >= kComputeWarps) {
@@ -484,7 +488,7 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
                 // geometry of the NT*16 pixels of the tile group: {element offset of the patch origin, iy0, ix0}
                 long long m0; int nt;
                 group_coords(tl, &m0, &nt);
-                for (int x = ptid; x < NT * kTilePix; x += kLoaderThreads) {
+                for (int x = ptid; x < nt_eff * kTilePix; x += kLoaderThreads) {
                     const long long pix = m0 + x;
                     int y0 = -(1 << 28), x0 = -(1 << 28);
                     long long b = 0;
@@ -507,11 +511,11 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
             const int LQ = (kc + 3) >> 2;
             const int lq_first = ptid >> 4;                 // this thread's quads: lq_first + 8 * s
             const int stages = lq_first < LQ ? (LQ - lq_first + 7) / 8 : 0;
-            for (int t = 0; t < NT; ++t) {
+            for (int t = 0; t < nt_eff; ++t) {
                 const uint4 gq = lds128(sGeo + unsigned(t * kTilePix + p) * 16u);
                 const long long base = (long long)(((unsigned long long)gq.y << 32) | gq.x);
                 const int iy0 = int(gq.z), ix0 = int(gq.w);
-                const unsigned bb = buf_addr(int(parity) * NT + t) + 8u * 16u + unsigned(p);
+                const unsigned bb = buf_addr(int(parity) * nt_eff + t) + 8u * 16u + unsigned(p);
                 int l0 = l_base + lq_first * 4;
                 int tap = l0 / P.C;
                 int cc = l0 - tap * P.C;
@@ -592,6 +596,8 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
 
     // ========================================= consumers =========================================
     const int gl = warp % GW, slot = warp / GW;
+    const int half = P.dual ? (lane >> 4) : 0;       // which of the warp's two pixel tiles this lane works on
+    const int chan_lane = P.dual ? (lane & 15) : lane;
     const int *steps_q = reinterpret_cast<const int *>(P.plan + P.L.steps_off);
     const uint4 *prog = reinterpret_cast<const uint4 *>(P.plan + P.L.prog_off);
     const float *bsum = reinterpret_cast<const float *>(P.plan + P.L.bsum_off);
@@ -601,8 +607,9 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
     for (int i = 0; i < NTW; ++i) {
 #pragma unroll
         for (int x = 0; x < kTilePix; ++x) acc[i][x] = 0;
-        base0[i] = buf_addr(slot * NTW + i);
-        base1[i] = buf_addr(NT + slot * NTW + i);
+        const int tile = P.dual ? 2 * (slot * NTW + i) + half : slot * NTW + i;
+        base0[i] = buf_addr(tile);
+        base1[i] = buf_addr(nt_eff + tile);
     }
 
     // the schedule of (channel tile nt, chunk c) that this warp walks
@@ -642,11 +649,12 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
         float asum_lane[NTW];
 #pragma unroll
         for (int i = 0; i < NTW; ++i) {
-            const long long pix = m0 + (slot * NTW + i) * kTilePix + lane;
-            asum_lane[i] = (lane < kTilePix && pix < P.M) ? __ldg(P.asum + pix) : 0.0f;
+            const int tile = P.dual ? 2 * (slot * NTW + i) + half : slot * NTW + i;
+            const long long pix = m0 + tile * kTilePix + (lane & 15);
+            asum_lane[i] = ((P.dual || lane < kTilePix) && pix < P.M) ? __ldg(P.asum + pix) : 0.0f;
         }
         {
-            const int j = (P.g_base + nt * GW + gl) * 32 + lane;
+            const int j = (P.g_base + nt * GW + gl) * 32 + chan_lane;
             if (nt != t2_nt) { t2 = j < P.Cout ? __fmul_rn(Q.m1, __ldg(bsum + j)) : 0.0f; t2_nt = nt; }
         }
         for (int c = 0; c < NCH; ++c) {
@@ -689,14 +697,15 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
         }
         // ---- the tile group is complete: dequantise and store ------------------------------------
         {
-            const int j = (P.g_base + nt * GW + gl) * 32 + lane;
+            const int j = (P.g_base + nt * GW + gl) * 32 + chan_lane;
             const bool live = (nt * GW + gl) < P.g_count && j < P.Cout;
 #pragma unroll
             for (int i = 0; i < NTW; ++i) {
+                const int tile = P.dual ? 2 * (slot * NTW + i) + half : slot * NTW + i;
 #pragma unroll
                 for (int x = 0; x < kTilePix; ++x) {
-                    const long long pix = m0 + (slot * NTW + i) * kTilePix + x;
-                    const float a_sum = __shfl_sync(0xffffffffu, asum_lane[i], x);
+                    const long long pix = m0 + tile * kTilePix + x;
+                    const float a_sum = __shfl_sync(0xffffffffu, asum_lane[i], x + 16 * half);
                     if (live && pix < P.M) {
                         const float t0 = __fmul_rn(float(acc[i][x]), Q.s1s2);
                         const float t1 = __fmul_rn(Q.m2, a_sum);
@@ -816,8 +825,9 @@ template <int GW, int NTW>
 int launch_sched_variant(SchedParams P, const DeviceInfo &di, cudaStream_t stream)
 {
     constexpr int NT = (kComputeWarps / GW) * NTW;
+    const int nt_eff = P.dual ? 2 * NT : NT;
     P.tiles_n = (P.g_count + GW - 1) / GW;
-    P.tiles_total = ((P.M + kTilePix * NT - 1) / (kTilePix * NT)) * P.tiles_n;
+    P.tiles_total = ((P.M + kTilePix * nt_eff - 1) / (kTilePix * nt_eff)) * P.tiles_n;
     AXC_CUDA(cudaFuncSetAttribute(dense_sched_kernel<GW, NTW>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
     const long long grid = P.tiles_total < di.sm_count ? P.tiles_total : di.sm_count;
     dense_sched_kernel<GW, NTW><<<unsigned(grid), kSchedThreads, size_t(di.max_smem_optin), stream>>>(P);
@@ -868,7 +878,8 @@ PlanLayout plan_layout(int K, int Cout)
         if (gw < smallest) smallest = gw;
         rem -= count;
     }
-    const int kc_max = smallest == 1 ? 320 : smallest == 2 ? 608 : kMaxChunk;
+    // one group of at most 16 channels runs two pixel tiles per warp: twice the buffers
+    const int kc_max = (L.G == 1 && Cout <= 16) ? 152 : smallest == 1 ? 320 : smallest == 2 ? 608 : kMaxChunk;
     L.NCH = (K + kc_max - 1) / kc_max;
     L.KC = (((K + L.NCH - 1) / L.NCH) + 3) & ~3;
     if (L.KC > kc_max) L.KC = kc_max;
@@ -1002,6 +1013,7 @@ int launch_dense_sched(const Geom &g, const float *input, const float *asum, flo
     P.sh = g.sh; P.sw = g.sw; P.dh = g.dh; P.dw = g.dw; P.ph = g.ph; P.pw = g.pw; P.OH = g.OH; P.OW = g.OW;
     P.K = g.K; P.M = g.M; P.tiles_n = 0; P.tiles_total = 0;
     P.vec_ok = (g.C % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
+    P.dual = (L.G == 1 && g.Cout <= 16) ? 1 : 0;
     // n / d == (n * magic) >> 40 holds while n * d < 2^40; launch_dense keeps shapes beyond that on the common-K kernel
     P.magic_c = ((1ull << 40) + unsigned(g.C) - 1) / unsigned(g.C);
     P.magic_kw = ((1ull << 40) + unsigned(g.KW) - 1) / unsigned(g.KW);
@@ -1015,7 +1027,7 @@ int launch_dense_sched(const Geom &g, const float *input, const float *asum, flo
         P.g_base = g_done;
         P.g_count = count;
         // pixel tiles per consumer warp: as many as the shared-memory budget allows (two sets of buffers)
-        const int slots = kComputeWarps / gw;
+        const int slots = (kComputeWarps / gw) * (P.dual ? 2 : 1);   // pixel tiles in flight per unit of NTW
         int ntw = 4;
         while (ntw > 1 && buffers_that_fit(P, slots * ntw) < 2 * slots * ntw) ntw >>= 1;
         if (buffers_that_fit(P, slots * ntw) < 2 * slots * ntw) return AXC_INTERNAL;
