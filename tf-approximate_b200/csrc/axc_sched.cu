@@ -53,6 +53,14 @@ __device__ __forceinline__ unsigned prmt(unsigned a, unsigned b)
     return d;
 }
 
+// the same with the selector in a register
+__device__ __forceinline__ unsigned prmt_r(unsigned a, unsigned b, unsigned sel)
+{
+    unsigned d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
 __device__ __forceinline__ unsigned lds16(unsigned addr)
 {
     unsigned v;
@@ -225,130 +233,218 @@ __global__ void __launch_bounds__(32) plan_build_kernel(const float *__restrict_
         return;
     }
 
-    // dynamic shared memory: per lane, the chunk's elements sorted by (bank, row class), and for each of the
-    // 256 (bank, class) runs a cursor and an end
+    // Items of the 16 lane pairs, packed {k:10, bank:5, bank2:5, kind:2}.  kind 0: both lanes look up row k
+    // (banks bank / bank2); kind 1 / 2: only the even / odd lane does (its bank in `bank`), the other lane idles
+    // on the same row.  A K element whose two weights fall into the same bank becomes one item of each kind.
     extern __shared__ __align__(16) unsigned char sched_smem[];
-    unsigned short *order = reinterpret_cast<unsigned short *>(sched_smem);   // [32][KC]
-    unsigned short *pos = order + 32 * L.KC;                                  // [32][256] next element of the run
-    unsigned short *end = pos + 32 * 256;                                     // [32][256] one past its last element
-    unsigned char *rmask = reinterpret_cast<unsigned char *>(end + 32 * 256); // [32][32]  classes with elements left, per bank
-    __shared__ int bank_at_rank[32];
+    const int cap = 2 * L.KC;
+    uint32_t *items = reinterpret_cast<uint32_t *>(sched_smem);               // [16][cap]
+    __shared__ int cnt[16], pick[16], order[16], own_cls[16], load[32], own_bank[32];
 
     const int g = int(blockIdx.x) / L.NCH, c = int(blockIdx.x) % L.NCH;
     const int l_base = c * L.KC;
     const int kc = min(L.KC, K - l_base);
     // at most 16 output channels: the two half warps carry the same channels (for two different pixel tiles)
     const bool dual = L.G == 1 && Cout <= 16;
-    const int j = g * 32 + (dual ? (lane & 15) : lane);
-    const bool live = j < Cout;
-    unsigned short *my_order = order + lane * L.KC;
-    unsigned short *my_pos = pos + lane * 256;
-    unsigned short *my_end = end + lane * 256;
-    unsigned char *my_rmask = rmask + lane * 32;
+    auto channel_of = [&](int ln) { return g * 32 + (dual ? (ln & 15) : ln); };
+    auto bank_of = [&](int k, int j) { return slot_bank(sigma[qf[(size_t)(l_base + k) * Cout + j]]); };
+    auto item_banks = [](uint32_t it) -> unsigned {
+        return (1u << ((it >> 10) & 31u)) | (((it >> 20) & 3u) == 0u ? (1u << ((it >> 15) & 31u)) : 0u);
+    };
 
-    for (int key = 0; key < 256; ++key) my_pos[key] = 0;   // histogram first
-    if (live)
-        for (int i = 0; i < kc; ++i) my_pos[slot_bank(sigma[qf[(size_t)(l_base + i) * Cout + j]]) * 8 + (i & 7)]++;
-    {
-        int run = 0;
-        for (int key = 0; key < 256; ++key) {
-            const int n = my_pos[key];
-            my_pos[key] = (unsigned short)run;
-            my_end[key] = (unsigned short)run;     // insertion cursor of the second pass
-            run += n;
+    load[lane] = 0;
+    if (lane < 16) cnt[lane] = 0;
+    __syncwarp();
+    int total = 0;
+    for (int p = 0; p < 16; ++p) {
+        const int ja = channel_of(2 * p), jb = channel_of(2 * p + 1);
+        const bool la = ja < Cout, lb = jb < Cout;
+        int n_pair = 0;
+        for (int k0 = 0; k0 < kc; k0 += 32) {
+            const int k = k0 + lane;
+            uint32_t it0 = 0, it1 = 0;
+            int n = 0;
+            if (k < kc && (la || lb)) {
+                const int ba = la ? bank_of(k, ja) : 0, bb = lb ? bank_of(k, jb) : 0;
+                if (la && lb && ba != bb) { it0 = uint32_t(k) | (uint32_t(ba) << 10) | (uint32_t(bb) << 15); n = 1; }
+                else {
+                    if (la) { it0 = uint32_t(k) | (uint32_t(ba) << 10) | (1u << 20); n = 1; }
+                    if (lb) { const uint32_t t = uint32_t(k) | (uint32_t(bb) << 10) | (2u << 20); if (n) it1 = t; else it0 = t; ++n; }
+                }
+            }
+            int pre = n;                                // inclusive scan over the warp
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, pre, o); if (lane >= o) pre += v; }
+            const int at = n_pair + pre - n;
+            if (n > 0) { items[p * cap + at] = it0; atomicAdd(&load[(it0 >> 10) & 31u], 1); if (((it0 >> 20) & 3u) == 0u) atomicAdd(&load[(it0 >> 15) & 31u], 1); }
+            if (n > 1) { items[p * cap + at + 1] = it1; atomicAdd(&load[(it1 >> 10) & 31u], 1); }
+            n_pair += __shfl_sync(0xffffffffu, pre, 31);
         }
-    }
-    if (live)
-        for (int i = 0; i < kc; ++i) {
-            const int key = slot_bank(sigma[qf[(size_t)(l_base + i) * Cout + j]]) * 8 + (i & 7);
-            my_order[my_end[key]] = (unsigned short)i;
-            my_end[key]++;
-        }
-    for (int b = 0; b < 32; ++b) {
-        unsigned m = 0;
-        for (int r = 0; r < 8; ++r)
-            if (my_pos[b * 8 + r] < my_end[b * 8 + r]) m |= 1u << r;
-        my_rmask[b] = (unsigned char)m;
+        if (lane == 0) cnt[p] = n_pair;
+        total += n_pair;
     }
     __syncwarp();
 
-    int lane_rem = live ? kc : 0;
-    int load = 0;                                  // lane b: remaining elements of bank b over all lanes
-    for (int x = 0; x < 32; ++x)
-        for (int r = 0; r < 8; ++r) load += int(end[x * 256 + lane * 8 + r]) - int(pos[x * 256 + lane * 8 + r]);
-    int total = 0;
-    {
-        int v = lane_rem;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        total = v;
-    }
+    // best admissible item of pair p: banks free in `used`, row class free in `cls` (the pair's half warp);
+    // heaviest banks first.  Returns the item index or -1 (the same value in every lane).
+    auto scan_best = [&](int p, unsigned used, unsigned cls) -> int {
+        const int n = cnt[p];
+        unsigned best = 0;
+        for (int i = lane; i < n; i += 32) {
+            const uint32_t it = items[p * cap + i];
+            if ((cls >> (it & 7u)) & 1u) continue;
+            if (used & item_banks(it)) continue;
+            const int l1 = load[(it >> 10) & 31u];
+            const int l2 = ((it >> 20) & 3u) == 0u ? load[(it >> 15) & 31u] : l1;
+            const unsigned key = (unsigned(l1 + l2) << 12) | unsigned(4095 - i);
+            best = key > best ? key : best;
+        }
+        best = __reduce_max_sync(0xffffffffu, best);
+        return best == 0u ? -1 : 4095 - int(best & 4095u);
+    };
+    // book-keeping of one choice (sign = +1 take, -1 give back); every lane calls it with the same arguments
+    auto account = [&](int p, uint32_t it, int sign) {
+        if (lane == 0) {
+            const int b1 = (it >> 10) & 31u, b2 = (it >> 15) & 31u;
+            const bool both = ((it >> 20) & 3u) == 0u;
+            own_bank[b1] = sign > 0 ? p : -1;
+            load[b1] -= sign;
+            if (both) { own_bank[b2] = sign > 0 ? p : -1; load[b2] -= sign; }
+            own_cls[(p >> 3) * 8 + int(it & 7u)] = sign > 0 ? p : -1;
+        }
+        __syncwarp();
+    };
 
     uint4 *prog = reinterpret_cast<uint4 *>(plan + L.prog_off) + (size_t)blockIdx.x * L.sqcap * 32;
     const int step_cap = L.sqcap * 4;
-    const int quarter = lane >> 3;
+    const int my_pair = lane >> 1, side = lane & 1, my_half = lane >> 4;
+    const int j = channel_of(lane);
     uint32_t wq[4] = {0, 0, 0, 0};
     int step = 0;
     bool overflow = false;
     while (total > 0) {
         if (step >= step_cap) { overflow = true; break; }
-        // banks by remaining load, largest first
-        int rank = 0;
-        for (int x = 0; x < 32; ++x) {
-            const int lx = __shfl_sync(0xffffffffu, load, x);
-            rank += (lx > load || (lx == load && x < lane)) ? 1 : 0;
+        own_bank[lane] = -1;
+        if (lane < 16) {
+            own_cls[lane] = -1;
+            pick[lane] = -1;
+            const int mine = cnt[lane];
+            int rank = 0;
+            for (int x = 0; x < 16; ++x) { const int cx = cnt[x]; rank += (cx > mine || (cx == mine && x < lane)) ? 1 : 0; }
+            order[rank] = lane;
         }
-        bank_at_rank[rank] = lane;
         __syncwarp();
-        unsigned used = 0, taken = 0;
-        unsigned used_rho = 0;                     // byte q: row classes taken in quarter q
-        int my_bank = -1, my_l = 0;
-        for (int r = 0; r < 32; ++r) {
-            const int b = bank_at_rank[r];
-            if (__shfl_sync(0xffffffffu, load, b) == 0) break;
-            const unsigned free_rho = unsigned(my_rmask[b]) & ~((used_rho >> (8 * quarter)) & 0xFFu);
-            const bool has = free_rho != 0u && !((used >> lane) & 1u);
-            const unsigned key = has ? ((unsigned(lane_rem) << 5) | unsigned(31 - lane)) : 0u;
-            const unsigned best = __reduce_max_sync(0xffffffffu, key);
-            if (best == 0u) continue;
-            const int chosen = 31 - int(best & 31u);
-            int rho = 0;
-            if (lane == chosen) {
-                rho = __ffs(int(free_rho)) - 1;
-                const int key2 = b * 8 + rho;
-                my_l = my_order[my_pos[key2]];
-                if (++my_pos[key2] == my_end[key2]) my_rmask[b] = (unsigned char)(my_rmask[b] & ~(1u << rho));
-                my_bank = b;
-                lane_rem--;
+        unsigned used = 0, cls[2] = {0, 0};
+        // greedy pass: pairs with the most items left choose first
+        for (int r = 0; r < 16; ++r) {
+            const int p = order[r];
+            if (cnt[p] == 0) break;
+            const int idx = scan_best(p, used, cls[p >> 3]);
+            if (idx < 0) continue;
+            const uint32_t it = items[p * cap + idx];
+            if (lane == 0) pick[p] = idx;
+            used |= item_banks(it);
+            cls[p >> 3] |= 1u << (it & 7u);
+            account(p, it, +1);
+        }
+        // repair pass: a pair left without an item takes one that a single other pair blocks, if that pair can
+        // move to another of its items
+        for (int r = 0; r < 16; ++r) {
+            const int p = order[r];
+            const int n = cnt[p];
+            if (n == 0) break;
+            if (pick[p] >= 0) continue;
+            const int h = p >> 3;
+            bool found = false;
+            int tries = 0;
+            for (int base = 0; base < n && !found && tries < 6; base += 32) {
+                const int i = base + lane;
+                uint32_t it = 0;
+                int q = -2;                                  // -2: not a candidate
+                if (i < n) {
+                    it = items[p * cap + i];
+                    const int o1 = own_bank[(it >> 10) & 31u];
+                    const int o2 = ((it >> 20) & 3u) == 0u ? own_bank[(it >> 15) & 31u] : -1;
+                    const int o3 = own_cls[h * 8 + int(it & 7u)];
+                    const int m = max(o1, max(o2, o3));
+                    if ((o1 < 0 || o1 == m) && (o2 < 0 || o2 == m) && (o3 < 0 || o3 == m)) q = m;   // -1: free as it is
+                }
+                unsigned mask = __ballot_sync(0xffffffffu, q > -2);
+                while (mask != 0u && !found && tries < 6) {
+                    const int src = __ffs(int(mask)) - 1;
+                    mask &= mask - 1u;
+                    ++tries;
+                    const uint32_t itc = __shfl_sync(0xffffffffu, it, src);
+                    const int qq = __shfl_sync(0xffffffffu, q, src);
+                    if (qq < 0) {
+                        if (lane == 0) pick[p] = base + src;
+                        used |= item_banks(itc);
+                        cls[h] |= 1u << (itc & 7u);
+                        account(p, itc, +1);
+                        found = true;
+                        break;
+                    }
+                    const uint32_t itq = items[qq * cap + pick[qq]];
+                    const int hq = qq >> 3;
+                    const unsigned used2 = (used & ~item_banks(itq)) | item_banks(itc);
+                    unsigned cls2[2] = {cls[0], cls[1]};
+                    cls2[hq] &= ~(1u << (itq & 7u));
+                    cls2[h] |= 1u << (itc & 7u);
+                    const int alt = scan_best(qq, used2, cls2[hq]);
+                    if (alt < 0) continue;
+                    const uint32_t ita = items[qq * cap + alt];
+                    account(qq, itq, -1);
+                    account(p, itc, +1);
+                    account(qq, ita, +1);
+                    if (lane == 0) { pick[p] = base + src; pick[qq] = alt; }
+                    used = used2 | item_banks(ita);
+                    cls2[hq] |= 1u << (ita & 7u);
+                    cls[0] = cls2[0]; cls[1] = cls2[1];
+                    found = true;
+                }
             }
-            rho = __shfl_sync(0xffffffffu, rho, chosen);
-            if (lane == b) load--;
-            used |= 1u << chosen;
-            taken |= 1u << b;
-            used_rho |= 1u << (8 * (chosen >> 3) + rho);
-            total--;
+            __syncwarp();
         }
         __syncwarp();
+        // program words of the step
+        const int pk = pick[my_pair];
+        bool active = false;
+        int row, k_mine = 0;
+        if (pk >= 0) {
+            const uint32_t it = items[my_pair * cap + pk];
+            const unsigned kind = (it >> 20) & 3u;
+            k_mine = int(it & 1023u);
+            row = k_mine + 8;
+            active = kind == 0u || kind == unsigned(1 + side);
+        } else {
+            row = __ffs(int(~cls[my_half] & 0xFFu)) - 1;     // an all-zero row of a class nobody in the half warp reads
+        }
+        const unsigned idle_mask = __ballot_sync(0xffffffffu, !active);
+        const unsigned rowoff = unsigned(row) * 16u;
         uint32_t w;
-        if (my_bank >= 0) {
-            const int s = sigma[qf[(size_t)(l_base + my_l) * Cout + j]];
-            const unsigned rowoff = unsigned(my_l + 8) * 16u;
+        if (active) {
+            const int s = sigma[qf[(size_t)(l_base + k_mine) * Cout + j]];
             w = uint32_t(2 * (s & 127)) | ((rowoff >> 8) << 8) | (uint32_t(1 + (s >> 7)) << 16) | ((rowoff & 255u) << 24);
         } else {
-            const unsigned idle = ~used;
-            const int k = __popc(idle & ((1u << lane) - 1u));
-            const int bank = __fns(~taken, 0, k + 1);   // k-th bank nobody looks up in this step
-            const unsigned mine = (used_rho >> (8 * quarter)) & 0xFFu;
-            const int rho = __ffs(int(~mine & 0xFFu)) - 1;   // a row class no active lane of the quarter reads
-            const unsigned rowoff = unsigned(rho) * 16u;
-            w = uint32_t(4 * bank) | (3u << 16) | (rowoff << 24);
+            const int nth = __popc(idle_mask & ((1u << lane) - 1u));
+            const int zb = __fns(~used, 0, nth + 1);         // nth bank nobody looks up in this step
+            w = uint32_t(4 * zb) | ((rowoff >> 8) << 8) | (1u << 14) | (3u << 16) | ((rowoff & 255u) << 24);
         }
         wq[step & 3] = w;
         if ((step & 3) == 3) prog[(size_t)(step >> 2) * 32 + lane] = make_uint4(wq[0], wq[1], wq[2], wq[3]);
         ++step;
+        // retire the chosen items (the last item of the pair takes the freed place)
+        if (lane < 16 && pick[lane] >= 0) {
+            const int last = cnt[lane] - 1;
+            items[lane * cap + pick[lane]] = items[lane * cap + last];
+            cnt[lane] = last;
+        }
+        total -= __popc(__ballot_sync(0xffffffffu, lane < 16 && pick[lane] >= 0));
+        __syncwarp();
     }
     if (step & 3) {
-        for (int e = step & 3; e < 4; ++e) wq[e] = uint32_t(4 * lane) | (3u << 16) | (uint32_t((lane & 7) * 16) << 24);
+        for (int e = step & 3; e < 4; ++e)
+            wq[e] = uint32_t(4 * lane) | (1u << 14) | (3u << 16) | (uint32_t(((lane >> 1) & 7) * 16) << 24);
         prog[(size_t)(step >> 2) * 32 + lane] = make_uint4(wq[0], wq[1], wq[2], wq[3]);
     }
     if (lane == 0) {
@@ -676,6 +772,11 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
                 for (int e = 0; e < 4; ++e) {
                     const uint32_t w = ws[e];
                     const unsigned rowoff = (w >> 24) | (w & 0x3F00u);     // 16 * activation row
+                    // byte selectors {column byte of w, activation byte i, plane byte of w, 0}; an idle lane (bit 14)
+                    // takes 0 for the activation byte, whatever row it reads along with its neighbour
+                    const unsigned idle = (w >> 14) & 1u;
+                    const unsigned sel0 = 0xA240u + idle * 0x60u, sel_inc = 16u - idle * 16u;
+                    const unsigned sel1 = sel0 + sel_inc, sel2 = sel1 + sel_inc, sel3 = sel2 + sel_inc;
 #pragma unroll
                     for (int i = 0; i < NTW; ++i) {
                         const uint4 av = lds128((parity ? base1[i] : base0[i]) + rowoff);
@@ -683,10 +784,10 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
 #pragma unroll
                         for (int i4 = 0; i4 < kTilePix / 4; ++i4) {
                             // table address = {column byte of w, activation byte, plane byte of w, 0}
-                            acc[i][i4 * 4 + 0] += int(lds16(prmt<0xA240>(w, aw[i4])));
-                            acc[i][i4 * 4 + 1] += int(lds16(prmt<0xA250>(w, aw[i4])));
-                            acc[i][i4 * 4 + 2] += int(lds16(prmt<0xA260>(w, aw[i4])));
-                            acc[i][i4 * 4 + 3] += int(lds16(prmt<0xA270>(w, aw[i4])));
+                            acc[i][i4 * 4 + 0] += int(lds16(prmt_r(w, aw[i4], sel0)));
+                            acc[i][i4 * 4 + 1] += int(lds16(prmt_r(w, aw[i4], sel1)));
+                            acc[i][i4 * 4 + 2] += int(lds16(prmt_r(w, aw[i4], sel2)));
+                            acc[i][i4 * 4 + 3] += int(lds16(prmt_r(w, aw[i4], sel3)));
                         }
                     }
                 }
@@ -962,7 +1063,7 @@ int launch_plan(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, cons
     plan_sigma_kernel<<<1, 256, 0, stream>>>(plan + L.qf_off, count, plan + L.sigma_off, hdr, want, dq);
     AXC_CUDA(cudaGetLastError());
     const unsigned blocks = unsigned(L.G * L.NCH + 256 + (g.Cout + 31) / 32);
-    const size_t sched_smem = size_t(32) * L.KC * 2 + 2 * size_t(32) * 256 * 2 + 32 * 32;
+    const size_t sched_smem = size_t(16) * 2 * L.KC * sizeof(uint32_t);   // the items of the 16 lane pairs
     AXC_CUDA(cudaFuncSetAttribute(plan_build_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sched_smem)));
     plan_build_kernel<<<blocks, 32, sched_smem, stream>>>(filter, lut_dev, plan, L, g.K, g.Cout);
     AXC_CUDA(cudaGetLastError());
