@@ -434,6 +434,7 @@ __global__ void __launch_bounds__(32) plan_build_kernel(const float *__restrict_
         if ((step & 3) == 3) prog[(size_t)(step >> 2) * 32 + lane] = make_uint4(wq[0], wq[1], wq[2], wq[3]);
         ++step;
         // retire the chosen items (the last item of the pair takes the freed place)
+        __syncwarp();
         if (lane < 16 && pick[lane] >= 0) {
             const int last = cnt[lane] - 1;
             items[lane * cap + pick[lane]] = items[lane * cap + last];
@@ -980,7 +981,7 @@ PlanLayout plan_layout(int K, int Cout)
         rem -= count;
     }
     // one group of at most 16 channels runs two pixel tiles per warp: twice the buffers
-    const int kc_max = (L.G == 1 && Cout <= 16) ? 152 : smallest == 1 ? 320 : smallest == 2 ? 608 : kMaxChunk;
+    const int kc_max = (L.G == 1 && Cout <= 16) ? 152 : smallest == 1 ? 160 : smallest == 2 ? 304 : kMaxChunk;
     L.NCH = (K + kc_max - 1) / kc_max;
     L.KC = (((K + L.NCH - 1) / L.NCH) + 3) & ~3;
     if (L.KC > kc_max) L.KC = kc_max;
