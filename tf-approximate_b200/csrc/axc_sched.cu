@@ -121,18 +121,33 @@ __global__ void plan_check_kernel(const float *__restrict__ filter, long long co
 }
 
 // ------------------------------------------------------------------------------------------------
-// plan_sigma: histogram of the quantised weights -> balanced assignment of the 256 table columns to
-// the 32 banks (largest first, into the bank with the smallest mass that still has one of its 8 slots)
+// plan_sigma: assignment of the 256 table columns to the 32 banks (8 columns per bank).
+//  1. histogram of the quantised weights; largest column first into the bank with the smallest mass that still
+//     has a free slot: balances the banks over the whole filter;
+//  2. local search on the blocks the schedules are built for ((32 channels) x (K chunk)): a schedule cannot be
+//     shorter than the heaviest bank of its block, so columns are swapped between banks while that lowers the
+//     sum over blocks of max(heaviest bank, the block's own lower bound).  Deterministic.
+// One block of 256 threads; dynamic shared memory: per block 128 words of packed 16-bit column counts and 32
+// words of bank loads (skipped when that does not fit).
 // ------------------------------------------------------------------------------------------------
-__global__ void plan_sigma_kernel(const uint8_t *__restrict__ qf, long long count, uint8_t *__restrict__ sigma,
-                                  PlanHeader *hdr, PlanHeader want, const DevQuant *__restrict__ dq)
+constexpr int kSigmaMaxBlocks = 320;
+constexpr int kSigmaIters = 600;
+
+__global__ void __launch_bounds__(256) plan_sigma_kernel(const uint8_t *__restrict__ qf, int K, int Cout, PlanLayout L,
+                                                         int search_blocks, uint8_t *__restrict__ sigma, PlanHeader *hdr,
+                                                         PlanHeader want, const DevQuant *__restrict__ dq)
 {
     if (hdr->dirty == 0) return;
+    extern __shared__ __align__(16) unsigned sigma_smem[];
     __shared__ unsigned hist[256];
     __shared__ int value_at_rank[256];
     __shared__ unsigned long long mass[32];
     __shared__ int used[32];
+    __shared__ unsigned char bank_of[256];
+    __shared__ long long red_key[8];
+    __shared__ int s_target, s_b1, s_done;
     const int t = threadIdx.x;
+    const long long count = (long long)K * Cout;
     hist[t] = 0;
     __syncthreads();
     for (long long i = t; i < count; i += 256) atomicAdd(&hist[qf[i]], 1u);
@@ -160,15 +175,141 @@ __global__ void plan_sigma_kernel(const uint8_t *__restrict__ qf, long long coun
             }
             const int bank = int(key & 31ull);
             if (t == bank) {
-                const int k = used[t];
-                // the 8 slots of a bank: word bank or bank+32 of a plane row, low/high half, plane 0/1
-                const int slot = (k >> 2) * 128 + 2 * (bank + 32 * ((k >> 1) & 1)) + (k & 1);
-                sigma[v] = uint8_t(slot);
-                used[t] = k + 1;
+                bank_of[v] = (unsigned char)bank;
+                used[t]++;
                 mass[t] += hist[v];
             }
             __syncwarp();
         }
+    }
+    __syncthreads();
+
+    const int B = search_blocks;                       // 0: no local search
+    if (B > 0) {
+        unsigned *H = sigma_smem;                      // [B][128]: counts of columns 2i, 2i+1 in the halves of word i
+        int *Ld = reinterpret_cast<int *>(H + (size_t)B * 128);   // [B][32] bank loads
+        int *top = Ld + (size_t)B * 32;                // [B][4]: the three largest loads packed {load:26, bank:5}, then the floor
+        for (int i = t; i < B * 128; i += 256) H[i] = 0;
+        __syncthreads();
+        const int NCH = L.NCH, KC = L.KC;
+        for (long long i = t; i < count; i += 256) {
+            const int l = int(i / Cout), j = int(i - (long long)l * Cout);
+            const int blk = (j >> 5) * NCH + l / KC;
+            const unsigned v = qf[i];
+            atomicAdd(&H[blk * 128 + (v >> 1)], 1u << (16 * (v & 1u)));
+        }
+        __syncthreads();
+        auto h_at = [&](int blk, int v) -> int { return int((H[blk * 128 + (v >> 1)] >> (16 * (v & 1))) & 0xFFFFu); };
+        for (int i = t; i < B * 32; i += 256) {
+            const int blk = i >> 5, b = i & 31;
+            int sum = 0;
+            for (int v = 0; v < 256; ++v) sum += bank_of[v] == b ? h_at(blk, v) : 0;
+            Ld[i] = sum;
+        }
+        __syncthreads();
+        for (int i = t; i < B; i += 256) {
+            // lower bound of the block's schedule that no column assignment changes: its K elements plus the
+            // share that ends up split (two weights of a lane pair in one bank), about 1/32
+            const int c = i % NCH;
+            const int kc = min(KC, K - c * KC);
+            top[i * 4 + 3] = kc + (kc >> 5);
+        }
+        if (t == 0) s_done = 0;
+        __syncthreads();
+        for (int iter = 0; iter < kSigmaIters; ++iter) {
+            // the three heaviest banks of every block
+            for (int i = t; i < B; i += 256) {
+                int a0 = -1, a1 = -1, a2 = -1;
+                for (int b = 0; b < 32; ++b) {
+                    const int key = (Ld[i * 32 + b] << 5) | b;
+                    if (key > a0) { a2 = a1; a1 = a0; a0 = key; }
+                    else if (key > a1) { a2 = a1; a1 = key; }
+                    else if (key > a2) a2 = key;
+                }
+                top[i * 4 + 0] = a0; top[i * 4 + 1] = a1; top[i * 4 + 2] = a2;
+            }
+            __syncthreads();
+            // target: the block that exceeds its floor the most (flagged blocks excluded); ties -> lowest block
+            {
+                long long key = -1;
+                for (int i = t; i < B; i += 256) {
+                    const int fl = top[i * 4 + 3];
+                    if (fl < 0) continue;                                  // flagged: no improving swap last time
+                    const int ex = (top[i * 4 + 0] >> 5) - fl;
+                    if (ex > 0) { const long long k2 = ((long long)ex << 20) | (long long)(0xFFFFF - i); key = k2 > key ? k2 : key; }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) { const long long other = __shfl_xor_sync(0xffffffffu, key, o); key = other > key ? other : key; }
+                if ((t & 31) == 0) red_key[t >> 5] = key;
+                __syncthreads();
+                if (t == 0) {
+                    long long best = -1;
+                    for (int w = 0; w < 8; ++w) best = red_key[w] > best ? red_key[w] : best;
+                    if (best < 0) s_done = 1;
+                    else { s_target = 0xFFFFF - int(best & 0xFFFFF); s_b1 = top[s_target * 4 + 0] & 31; }
+                }
+                __syncthreads();
+            }
+            if (s_done) break;
+            const int target = s_target, b1 = s_b1;
+            // candidate swaps: a column of bank b1 against column t of another bank; change of the objective
+            long long best_key = 0;                     // {-(delta) : 32, v1 : 8, v2 : 8}, 0 = none
+            const int b2 = bank_of[t];
+            if (b2 != b1) {
+                for (int v1 = 0; v1 < 256; ++v1) {
+                    if (bank_of[v1] != b1) continue;
+                    int delta = 0;
+                    for (int i = 0; i < B; ++i) {
+                        const int d = h_at(i, v1) - h_at(i, t);
+                        if (d == 0) continue;
+                        const int fl = top[i * 4 + 3] & 0x7FFFFFFF;
+                        const int k0 = top[i * 4 + 0], k1 = top[i * 4 + 1], k2 = top[i * 4 + 2];
+                        // heaviest bank other than b1 and b2
+                        int others = ((k0 & 31) != b1 && (k0 & 31) != b2) ? (k0 >> 5) : ((k1 & 31) != b1 && (k1 & 31) != b2) ? (k1 >> 5) : (k2 >> 5);
+                        const int n1 = Ld[i * 32 + b1] - d, n2 = Ld[i * 32 + b2] + d;
+                        const int new_max = max(others, max(n1, n2));
+                        delta += max(new_max, fl) - max(k0 >> 5, fl);
+                    }
+                    if (delta < 0) {
+                        const long long key = ((long long)(-delta) << 16) | (long long)((255 - v1) << 8) | (long long)(255 - t);
+                        best_key = key > best_key ? key : best_key;
+                    }
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) { const long long other = __shfl_xor_sync(0xffffffffu, best_key, o); best_key = other > best_key ? other : best_key; }
+            if ((t & 31) == 0) red_key[t >> 5] = best_key;
+            __syncthreads();
+            long long best = 0;
+            for (int w = 0; w < 8; ++w) best = red_key[w] > best ? red_key[w] : best;
+            __syncthreads();
+            if (best == 0) {
+                if (t == 0) top[target * 4 + 3] |= int(0x80000000u);      // flag: leave this block alone
+                __syncthreads();
+                continue;
+            }
+            const int v1 = 255 - int((best >> 8) & 255), v2 = 255 - int(best & 255);
+            const int bb2 = bank_of[v2];
+            __syncthreads();
+            for (int i = t; i < B; i += 256) {
+                const int d = h_at(i, v1) - h_at(i, v2);
+                Ld[i * 32 + b1] -= d;
+                Ld[i * 32 + bb2] += d;
+                top[i * 4 + 3] &= 0x7FFFFFFF;                              // loads changed: every block is eligible again
+            }
+            if (t == 0) { bank_of[v1] = (unsigned char)bb2; bank_of[v2] = (unsigned char)b1; }
+            __syncthreads();
+        }
+    }
+    __syncthreads();
+    // slots: the 8 columns of a bank in increasing order; slot = word bank or bank+32 of a plane row, low/high
+    // half, plane 0/1
+    {
+        const int bank = bank_of[t];
+        int k = 0;
+        for (int v = 0; v < t; ++v) k += bank_of[v] == bank ? 1 : 0;
+        const int slot = (k >> 2) * 128 + 2 * (bank + 32 * ((k >> 1) & 1)) + (k & 1);
+        sigma[t] = uint8_t(slot);
     }
     if (t == 0) {
         hdr->magic = want.magic; hdr->K = want.K; hdr->Cout = want.Cout; hdr->G = want.G; hdr->NCH = want.NCH;
@@ -1061,8 +1202,15 @@ int launch_plan(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, cons
     const DevQuant *dq = reinterpret_cast<const DevQuant *>(plan + kDevQuantOffset);
     plan_check_kernel<<<unsigned((count + 255) / 256), 256, 0, stream>>>(filter, count, dq, plan + L.qf_off, qf_debug, hdr, want);
     AXC_CUDA(cudaGetLastError());
-    plan_sigma_kernel<<<1, 256, 0, stream>>>(plan + L.qf_off, count, plan + L.sigma_off, hdr, want, dq);
-    AXC_CUDA(cudaGetLastError());
+    {
+        // the local search of plan_sigma_kernel needs 640 bytes of shared memory per schedule block
+        const int blocks = L.G * L.NCH;
+        const int search_blocks = blocks <= kSigmaMaxBlocks ? blocks : 0;
+        const size_t sigma_smem = size_t(search_blocks) * (128 + 32 + 4) * sizeof(int);
+        AXC_CUDA(cudaFuncSetAttribute(plan_sigma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSigmaMaxBlocks * 164 * sizeof(int))));
+        plan_sigma_kernel<<<1, 256, sigma_smem, stream>>>(plan + L.qf_off, g.K, g.Cout, L, search_blocks, plan + L.sigma_off, hdr, want, dq);
+        AXC_CUDA(cudaGetLastError());
+    }
     const unsigned blocks = unsigned(L.G * L.NCH + 256 + (g.Cout + 31) / 32);
     const size_t sched_smem = size_t(16) * 2 * L.KC * sizeof(uint32_t);   // the items of the 16 lane pairs
     AXC_CUDA(cudaFuncSetAttribute(plan_build_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sched_smem)));
