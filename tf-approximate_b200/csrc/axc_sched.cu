@@ -607,7 +607,8 @@ struct SchedParams {
     int32_t *acc_out;
     int N, H, W, C, KH, KW, Cout;
     int sh, sw, dh, dw, ph, pw, OH, OW, K;
-    long long M;
+    long long M;              // end of the pixel range of this launch (all pixels: N*OH*OW)
+    long long pix_base;       // first pixel of the range
     int g_base, g_count;      // channel groups [g_base, g_base + g_count) are served by this launch
     int dual;                 // Cout <= 16: lanes 16..31 repeat the channels of lanes 0..15 on a second pixel tile
     int tiles_n;              // channel tiles of 32*GW channels
@@ -705,7 +706,7 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
         const long long tile = blockIdx.x + tl * gridDim.x;
         const long long mt = tile / P.tiles_n;
         *nt = int(tile - mt * P.tiles_n);
-        *m0 = mt * (kTilePix * nt_eff);
+        *m0 = P.pix_base + mt * (kTilePix * nt_eff);
     };
 
     if (warp >= kComputeWarps) {
@@ -1070,7 +1071,7 @@ int launch_sched_variant(SchedParams P, const DeviceInfo &di, cudaStream_t strea
     constexpr int NT = (kComputeWarps / GW) * NTW;
     const int nt_eff = P.dual ? 2 * NT : NT;
     P.tiles_n = (P.g_count + GW - 1) / GW;
-    P.tiles_total = ((P.M + kTilePix * nt_eff - 1) / (kTilePix * nt_eff)) * P.tiles_n;
+    P.tiles_total = ((P.M - P.pix_base + kTilePix * nt_eff - 1) / (kTilePix * nt_eff)) * P.tiles_n;
     AXC_CUDA(cudaFuncSetAttribute(dense_sched_kernel<GW, NTW>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
     const long long grid = P.tiles_total < di.sm_count ? P.tiles_total : di.sm_count;
     dense_sched_kernel<GW, NTW><<<unsigned(grid), kSchedThreads, size_t(di.max_smem_optin), stream>>>(P);
@@ -1261,7 +1262,7 @@ int launch_dense_sched(const Geom &g, const float *input, const float *asum, flo
     P.plan = plan; P.L = L; P.input = input; P.asum = asum; P.output = output; P.acc_out = acc_out;
     P.N = g.N; P.H = g.H; P.W = g.W; P.C = g.C; P.KH = g.KH; P.KW = g.KW; P.Cout = g.Cout;
     P.sh = g.sh; P.sw = g.sw; P.dh = g.dh; P.dw = g.dw; P.ph = g.ph; P.pw = g.pw; P.OH = g.OH; P.OW = g.OW;
-    P.K = g.K; P.M = g.M; P.tiles_n = 0; P.tiles_total = 0;
+    P.K = g.K; P.M = g.M; P.pix_base = 0; P.tiles_n = 0; P.tiles_total = 0;
     P.vec_ok = (g.C % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
     P.dual = (L.G == 1 && g.Cout <= 16) ? 1 : 0;
     // n / d == (n * magic) >> 40 holds while n * d < 2^40; launch_dense keeps shapes beyond that on the common-K kernel
@@ -1281,19 +1282,58 @@ int launch_dense_sched(const Geom &g, const float *input, const float *asum, flo
         int ntw = 4;
         while (ntw > 1 && buffers_that_fit(P, slots * ntw) < 2 * slots * ntw) ntw >>= 1;
         if (buffers_that_fit(P, slots * ntw) < 2 * slots * ntw) return AXC_INTERNAL;
-        // few pixels: do not make tile groups larger than the work available per SM
-        while (ntw > 1 && (P.M + kTilePix * slots * ntw - 1) / (kTilePix * slots * ntw) * ((count + gw - 1) / gw) < 2LL * di.sm_count) ntw >>= 1;
+        // Tile groups are handed out round-robin to one CTA per SM, so a launch takes ceil(groups / SMs) rounds.
+        // Choose between one launch (any admissible number of tiles per warp) and a main launch of whole rounds
+        // followed by a tail launch with smaller tile groups for the pixels that are left; estimate: a round
+        // costs per warp step 18 shared-memory cycles per tile plus about 2.6 that do not depend on the tiles.
+        const long long unit = (long long)kTilePix * slots;           // pixels per tile group and unit of NTW
+        const int tiles_n = (count + gw - 1) / gw;
+        const double step_us = double(g.K) * 1.08 * 8.0 / 1965.0;     // one pipe cycle per step, in microseconds
+        auto rounds = [&](long long pixels, int n) -> long long {
+            const long long groups = (pixels + unit * n - 1) / (unit * n) * tiles_n;
+            return (groups + di.sm_count - 1) / di.sm_count;
+        };
+        auto cost = [&](long long pixels, int n) -> double {
+            return pixels > 0 ? double(rounds(pixels, n)) * (18.0 * n + 2.6) * step_us + 12.0 : 0.0;   // + launch, table fill
+        };
+        int best_main = ntw, best_tail = 0;
+        long long best_split = g.M;
+        double best_cost = 1e300;
+        for (int n = ntw; n >= 1; n >>= 1) {
+            const double c1 = cost(g.M, n);
+            if (c1 < best_cost) { best_cost = c1; best_main = n; best_tail = 0; best_split = g.M; }
+            // main launch: the whole rounds of the pixel groups; tail: the rest
+            const long long pg = (g.M + unit * n - 1) / (unit * n);
+            const long long full_groups = (pg * tiles_n / di.sm_count) * di.sm_count;
+            const long long pg_main = full_groups / tiles_n;
+            if (pg_main <= 0 || pg_main >= pg) continue;
+            const long long split = pg_main * unit * n;
+            for (int nt2 = n; nt2 >= 1; nt2 >>= 1) {
+                const double c2 = cost(split, n) + cost(g.M - split, nt2);
+                if (c2 < best_cost) { best_cost = c2; best_main = n; best_tail = nt2; best_split = split; }
+            }
+        }
         int rc = AXC_INTERNAL;
-#define AXC_DISPATCH(GWV)                                                          \
+#define AXC_DISPATCH(GWV, NTWV)                                                    \
         if (gw == GWV) {                                                           \
-            if (ntw == 4) rc = launch_sched_variant<GWV, 4>(P, di, stream);        \
-            else if (ntw == 2) rc = launch_sched_variant<GWV, 2>(P, di, stream);   \
+            if (NTWV == 4) rc = launch_sched_variant<GWV, 4>(P, di, stream);       \
+            else if (NTWV == 2) rc = launch_sched_variant<GWV, 2>(P, di, stream);  \
             else rc = launch_sched_variant<GWV, 1>(P, di, stream);                 \
         }
-        AXC_DISPATCH(1)
-        AXC_DISPATCH(2)
-        AXC_DISPATCH(4)
-        AXC_DISPATCH(8)
+        P.pix_base = 0; P.M = best_split;
+        AXC_DISPATCH(1, best_main)
+        AXC_DISPATCH(2, best_main)
+        AXC_DISPATCH(4, best_main)
+        AXC_DISPATCH(8, best_main)
+        if (rc) return rc;
+        if (best_tail > 0) {
+            P.pix_base = best_split; P.M = g.M;
+            rc = AXC_INTERNAL;
+            AXC_DISPATCH(1, best_tail)
+            AXC_DISPATCH(2, best_tail)
+            AXC_DISPATCH(4, best_tail)
+            AXC_DISPATCH(8, best_tail)
+        }
 #undef AXC_DISPATCH
         if (rc) return rc;
         g_done += count;
