@@ -114,6 +114,11 @@ SHAPES = [
     (5, 7, 7, 20, 3, 3, 64, (1, 1), (1, 1), "SAME"),      # K = 180: chunk tail, pixel tail
     (1, 30, 30, 2, 5, 5, 3, (3, 3), (1, 1), "VALID"),
     (1, 9, 9, 6, 2, 2, 5, (1, 1), (3, 3), "SAME"),
+    # more tile groups than SMs: several rounds per CTA, main launch + tail launch with smaller tile groups
+    (2, 112, 112, 8, 3, 3, 32, (1, 1), (1, 1), "SAME"),
+    (4, 100, 100, 4, 3, 3, 12, (1, 1), (1, 1), "SAME"),   # at most 16 channels: two pixel tiles per warp
+    (1, 120, 120, 16, 1, 1, 96, (1, 1), (1, 1), "SAME"),  # three channel groups in a launch of four
+    (1, 150, 150, 8, 3, 3, 33, (1, 1), (1, 1), "VALID"),  # runs of 1 + 1 groups, odd channel tail
 ]
 
 
