@@ -31,6 +31,20 @@ LOOKUPS_PER_CLK_PER_SM = 32   # one 32-bit shared-memory bank transaction per la
 NCU_DRAM_OVER_ALGORITHMIC = (209.3 + 165.3) / 411.2
 
 
+# name -> (description for `config.workload`, default batch per GPU, input description)
+WORKLOADS = {
+    "resnet50": ("resnet50_approx_conv (BASELINE config 4): ImageNet-shaped ResNet-50 v1.5, 53 table "
+                 "convolutions, truncated truth table, random He-init filters, frozen per-layer ranges",
+                 256, "224x224x3 fp32 NHWC"),
+    "resnet20": ("resnet20_approx_conv (BASELINE config 3): CIFAR-shaped ResNet-20, 3x3 table convolutions with "
+                 "16/32/64 channels, truncated truth table, random He-init filters, frozen per-layer ranges",
+                 1024, "32x32x3 fp32 NHWC"),
+    "mobilenet_stack": ("mobilenet_stack_approx_conv (BASELINE config 5): 3x3 depthwise + 1x1 pointwise table "
+                        "convolutions, 32-384 channels at 112/56/28/14, truncated truth table, random He-init "
+                        "filters, frozen per-layer ranges", 512, "112x112x32 fp32 NHWC"),
+}
+
+
 def build_params(kind):
     from tf_approximate_b200 import workloads as W
     import tf_approximate_b200 as ax
@@ -175,7 +189,7 @@ def run_gpu(args):
         dist.init_process_group("nccl", device_id=dev)
 
     net, filters, lut = build_params(args.workload)
-    batch = args.batch
+    batch = args.batch if args.batch else WORKLOADS[args.workload][1]
     runner = W.GpuRunner(net, [lut], filters, dev)
     x_host = torch.from_numpy(W.make_input(batch, net.hw, net.in_channels, 1000 + CFG_INDEX + rank)).pin_memory()
     x = x_host.to(dev)
@@ -297,9 +311,8 @@ def run_gpu(args):
         "metric": "lut_macs_per_s", "value": value, "unit": "LUT-MAC/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "u8 operands, u16 table entries, i32 accumulate", "data": "synthetic",
-        "config": {"workload": "resnet50_approx_conv (BASELINE config 4): ImageNet-shaped ResNet-50 v1.5, 53 table "
-                               "convolutions, truncated truth table, random He-init filters, frozen per-layer ranges",
-                   "batch_per_gpu": batch, "global_batch": batch * world, "input": "224x224x3 fp32 NHWC",
+        "config": {"workload": WORKLOADS[args.workload][0],
+                   "batch_per_gpu": batch, "global_batch": batch * world, "input": WORKLOADS[args.workload][2],
                    "parallelism": "dp%d (batch shards, per-GPU table replica, no collective in the step)" % world,
                    "l2": "not flushed: every layer's input and output are larger than the 126 MB L2"},
         "images_per_s": batch * world / (ms_step * 1e-3),
@@ -364,7 +377,7 @@ def run_reference(args):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["seconds_per_step"] * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "u8 operands, u16 table entries, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": "resnet50_approx_conv (BASELINE config 4), bounded sample: %s" % r["sample"]},
+        "config": {"workload": "%s, bounded sample: %s" % (WORKLOADS[args.workload][0].split(":")[0], r["sample"])},
         "images_per_s": r["images_per_s"],
         "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": r["value"], "unit": "LUT-MAC/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -378,7 +391,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=256, help="images per GPU")
+    ap.add_argument("--batch", type=int, default=0, help="images per GPU (default: the workload's own batch)")
     ap.add_argument("--workload", default="resnet50", choices=["resnet50", "resnet20", "mobilenet_stack"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--per-layer", action="store_true", help="add per-layer times and lookups/clk/SM to the JSON line")
