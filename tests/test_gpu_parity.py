@@ -119,6 +119,15 @@ SHAPES = [
     (4, 100, 100, 4, 3, 3, 12, (1, 1), (1, 1), "SAME"),   # at most 16 channels: two pixel tiles per warp
     (1, 120, 120, 16, 1, 1, 96, (1, 1), (1, 1), "SAME"),  # three channel groups in a launch of four
     (1, 150, 150, 8, 3, 3, 33, (1, 1), (1, 1), "VALID"),  # runs of 1 + 1 groups, odd channel tail
+    # extremes
+    (1, 6, 6, 3, 1, 1, 2100, (1, 1), (1, 1), "SAME"),     # 66 channel groups, K = 3
+    (2, 5, 5, 1, 1, 1, 1, (1, 1), (1, 1), "SAME"),        # K = 1
+    (1, 9, 9, 512, 7, 7, 20, (1, 1), (1, 1), "SAME"),     # K = 25088: 25 chunks
+    (1, 20, 20, 4, 3, 3, 17, (4, 4), (1, 1), "SAME"),     # stride larger than the window
+    (1, 1, 300, 4, 1, 3, 16, (1, 1), (1, 1), "SAME"),     # one row
+    (1, 64, 64, 32, 3, 3, 224, (1, 1), (1, 1), "SAME"),   # 7 channel groups in a launch of 8
+    (1, 64, 64, 32, 1, 1, 160, (1, 1), (1, 1), "SAME"),   # 5 groups: 4 + 1
+    (1, 64, 64, 32, 1, 1, 192, (2, 2), (1, 1), "SAME"),   # 6 groups: 4 + 2
 ]
 
 
