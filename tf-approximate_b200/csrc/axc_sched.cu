@@ -30,9 +30,8 @@ constexpr unsigned kLutBase = 65536u;          // table planes at 64 KiB and 128
 constexpr unsigned kBuf1Base = 196608u;        // 32 zero words (one per bank), then activation buffers
 constexpr unsigned kWindowEnd = 233472u;       // 228 KiB shared window of an SM
 constexpr int kComputeWarps = 8;
-constexpr int kLoaderWarps = 4;
-constexpr int kLoaderThreads = kLoaderWarps * 32;
-constexpr int kSchedThreads = (kComputeWarps + kLoaderWarps) * 32;
+// loader warps per CTA: 4 (168 registers per thread), or 8 for launches of one channel group, whose loaders
+// otherwise cannot keep up (each activation byte then serves only 32 or 16 output channels)
 constexpr int kTilePix = 16;
 constexpr int kTapTableMax = 512;
 constexpr int kStepsInSmemMax = 1024;
@@ -635,9 +634,13 @@ constexpr int kBarIter = 2;   // consumers + loaders: next activation buffers co
 //             bytes]; the schedule guarantees that the 8 rows a quarter warp reads in one LDS.128 fall into 8
 //             different 16-byte bank groups.
 // The patch sums come from patch_sum_kernel, which runs before this kernel.
-template <int GW, int NTW>
-__global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const SchedParams P)
+template <int GW, int NTW, int LW>
+__global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kernel(const SchedParams P)
 {
+    constexpr int kLoaderWarps = LW;
+    constexpr int kLoaderThreads = LW * 32;
+    constexpr int kSchedThreads = (kComputeWarps + LW) * 32;
+    constexpr int QS = kLoaderThreads / 16;          // quads of a pixel that the loaders fetch side by side
     constexpr int SLOTS = kComputeWarps / GW;        // pixel-tile slots
     constexpr int NT = SLOTS * NTW;                  // pixel tiles per tile group
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -748,8 +751,8 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
             const int l_base = c * KC;
             const int kc = min(KC, P.K - l_base);
             const int LQ = (kc + 3) >> 2;
-            const int lq_first = ptid >> 4;                 // this thread's quads: lq_first + 8 * s
-            const int stages = lq_first < LQ ? (LQ - lq_first + 7) / 8 : 0;
+            const int lq_first = ptid >> 4;                 // this thread's quads: lq_first + QS * s
+            const int stages = lq_first < LQ ? (LQ - lq_first + QS - 1) / QS : 0;
             for (int t = 0; t < nt_eff; ++t) {
                 const uint4 gq = lds128(sGeo + unsigned(t * kTilePix + p) * 16u);
                 const long long base = (long long)(((unsigned long long)gq.y << 32) | gq.x);
@@ -771,7 +774,7 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
                                 if (iy >= 0 && iy < P.H && ix >= 0 && ix < P.W)
                                     v = __ldg(reinterpret_cast<const float4 *>(
                                         P.input + base + ((long long)(ky * P.dh) * P.W + kx * P.dw) * P.C + cc));
-                                cc += 32;
+                                cc += 4 * QS;
                                 while (cc >= P.C) { cc -= P.C; if (++kx >= P.KW) { kx = 0; ++ky; } }
                             } else {
                                 float e4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -796,7 +799,7 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
                                 }
                                 v = make_float4(e4[0], e4[1], e4[2], e4[3]);
                             }
-                            l0 += 32;
+                            l0 += 4 * QS;
                         }
                         st[u] = v;
                     }
@@ -805,7 +808,7 @@ __global__ void __launch_bounds__(kSchedThreads, 1) dense_sched_kernel(const Sch
 #pragma unroll
                     for (int u = 0; u < kBatch; ++u) {
                         if (s0 + u < stages) {
-                            const int lq = lq_first + 8 * (s0 + u);
+                            const int lq = lq_first + QS * (s0 + u);
                             const unsigned a = bb + unsigned(lq * 4) * 16u;
                             const float4 v = st[u];
                             sts8(a, q_u8(v.x, Q.in_off, Q.in_inv));
@@ -1065,16 +1068,17 @@ __global__ void __launch_bounds__(kPsThreads) patch_sum_kernel(const PatchSumPar
     if (tid < tp) P.asum[((long long)n * P.OH + oh) * P.OW + ow0 + tid] = sum;
 }
 
-template <int GW, int NTW>
+template <int GW, int NTW, int LW>
 int launch_sched_variant(SchedParams P, const DeviceInfo &di, cudaStream_t stream)
 {
+    constexpr int kSchedThreads = (kComputeWarps + LW) * 32;
     constexpr int NT = (kComputeWarps / GW) * NTW;
     const int nt_eff = P.dual ? 2 * NT : NT;
     P.tiles_n = (P.g_count + GW - 1) / GW;
     P.tiles_total = ((P.M - P.pix_base + kTilePix * nt_eff - 1) / (kTilePix * nt_eff)) * P.tiles_n;
-    AXC_CUDA(cudaFuncSetAttribute(dense_sched_kernel<GW, NTW>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
+    AXC_CUDA(cudaFuncSetAttribute(dense_sched_kernel<GW, NTW, LW>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
     const long long grid = P.tiles_total < di.sm_count ? P.tiles_total : di.sm_count;
-    dense_sched_kernel<GW, NTW><<<unsigned(grid), kSchedThreads, size_t(di.max_smem_optin), stream>>>(P);
+    dense_sched_kernel<GW, NTW, LW><<<unsigned(grid), kSchedThreads, size_t(di.max_smem_optin), stream>>>(P);
     AXC_CUDA(cudaGetLastError());
     count_launch();
     return AXC_OK;
@@ -1314,11 +1318,13 @@ int launch_dense_sched(const Geom &g, const float *input, const float *asum, flo
             }
         }
         int rc = AXC_INTERNAL;
-#define AXC_DISPATCH(GWV, NTWV)                                                    \
-        if (gw == GWV) {                                                           \
-            if (NTWV == 4) rc = launch_sched_variant<GWV, 4>(P, di, stream);       \
-            else if (NTWV == 2) rc = launch_sched_variant<GWV, 2>(P, di, stream);  \
-            else rc = launch_sched_variant<GWV, 1>(P, di, stream);                 \
+#define AXC_DISPATCH(GWV, NTWV)                                                       \
+        if (gw == GWV) {                                                              \
+            if (NTWV == 4) rc = launch_sched_variant<GWV, 4, 4>(P, di, stream);       \
+            else if (GWV == 1 && NTWV == 2) rc = launch_sched_variant<1, 2, 8>(P, di, stream);  \
+            else if (GWV == 1) rc = launch_sched_variant<1, 1, 8>(P, di, stream);     \
+            else if (NTWV == 2) rc = launch_sched_variant<GWV, 2, 4>(P, di, stream);  \
+            else rc = launch_sched_variant<GWV, 1, 4>(P, di, stream);                 \
         }
         P.pix_base = 0; P.M = best_split;
         AXC_DISPATCH(1, best_main)
