@@ -640,7 +640,7 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
     constexpr int kLoaderWarps = LW;
     constexpr int kLoaderThreads = LW * 32;
     constexpr int kSchedThreads = (kComputeWarps + LW) * 32;
-    constexpr int QS = kLoaderThreads / 16;          // quads of a pixel that the loaders fetch side by side
+    constexpr int QS = 2;                            // a loader warp fetches 16 pixels x 2 neighbouring quads per load
     constexpr int SLOTS = kComputeWarps / GW;        // pixel-tile slots
     constexpr int NT = SLOTS * NTW;                  // pixel tiles per tile group
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -751,9 +751,10 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
             const int l_base = c * KC;
             const int kc = min(KC, P.K - l_base);
             const int LQ = (kc + 3) >> 2;
-            const int lq_first = ptid >> 4;                 // this thread's quads: lq_first + QS * s
+            const int lq_first = (ptid & 31) >> 4;          // this thread's quads: lq_first + QS * s
+            const int lw = ptid >> 5;                       // a loader warp owns whole tiles: lw, lw + LW, ...
             const int stages = lq_first < LQ ? (LQ - lq_first + QS - 1) / QS : 0;
-            for (int t = 0; t < nt_eff; ++t) {
+            for (int t = lw; t < nt_eff; t += kLoaderWarps) {
                 const uint4 gq = lds128(sGeo + unsigned(t * kTilePix + p) * 16u);
                 const long long base = (long long)(((unsigned long long)gq.y << 32) | gq.x);
                 const int iy0 = int(gq.z), ix0 = int(gq.w);
