@@ -128,6 +128,8 @@ SHAPES = [
     (1, 64, 64, 32, 3, 3, 224, (1, 1), (1, 1), "SAME"),   # 7 channel groups in a launch of 8
     (1, 64, 64, 32, 1, 1, 160, (1, 1), (1, 1), "SAME"),   # 5 groups: 4 + 1
     (1, 64, 64, 32, 1, 1, 192, (2, 2), (1, 1), "SAME"),   # 6 groups: 4 + 2
+    (1, 64, 64, 16, 3, 3, 144, (1, 1), (1, 1), "SAME"),   # 4 + 1 groups, the last with 16 channels on two pixel tiles
+    (1, 40, 40, 8, 1, 1, 267, (1, 1), (1, 1), "SAME"),    # 8 + 1 groups, the last with 11 channels
 ]
 
 

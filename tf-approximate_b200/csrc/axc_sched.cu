@@ -384,8 +384,9 @@ __global__ void __launch_bounds__(32) plan_build_kernel(const float *__restrict_
     const int g = int(blockIdx.x) / L.NCH, c = int(blockIdx.x) % L.NCH;
     const int l_base = c * L.KC;
     const int kc = min(L.KC, K - l_base);
-    // at most 16 output channels: the two half warps carry the same channels (for two different pixel tiles)
-    const bool dual = L.G == 1 && Cout <= 16;
+    // at most 16 live channels in a group launched alone: the two half warps carry the same channels (for two
+    // different pixel tiles)
+    const bool dual = plan_group_dual(g, L.G, Cout, K);
     auto channel_of = [&](int ln) { return g * 32 + (dual ? (ln & 15) : ln); };
     auto bank_of = [&](int k, int j) { return slot_bank(sigma[qf[(size_t)(l_base + k) * Cout + j]]); };
     auto item_banks = [](uint32_t it) -> unsigned {
@@ -609,7 +610,7 @@ struct SchedParams {
     long long M;              // end of the pixel range of this launch (all pixels: N*OH*OW)
     long long pix_base;       // first pixel of the range
     int g_base, g_count;      // channel groups [g_base, g_base + g_count) are served by this launch
-    int dual;                 // Cout <= 16: lanes 16..31 repeat the channels of lanes 0..15 on a second pixel tile
+    int dual;                 // plan_group_dual: lanes 16..31 repeat the channels of lanes 0..15 on a second pixel tile
     int tiles_n;              // channel tiles of 32*GW channels
     long long tiles_total;    // pixel tile groups x channel tiles
     int vec_ok;
@@ -1127,8 +1128,8 @@ PlanLayout plan_layout(int K, int Cout)
         if (gw < smallest) smallest = gw;
         rem -= count;
     }
-    // one group of at most 16 channels runs two pixel tiles per warp: twice the buffers
-    const int kc_max = (L.G == 1 && Cout <= 16) ? 152 : smallest == 1 ? 160 : smallest == 2 ? 304 : kMaxChunk;
+    // a group of at most 16 channels launched alone runs two pixel tiles per warp: twice the buffers
+    const int kc_max = plan_group_dual(L.G - 1, L.G, Cout, K) ? 152 : smallest == 1 ? 160 : smallest == 2 ? 304 : kMaxChunk;
     L.NCH = (K + kc_max - 1) / kc_max;
     L.KC = (((K + L.NCH - 1) / L.NCH) + 3) & ~3;
     if (L.KC > kc_max) L.KC = kc_max;
@@ -1269,7 +1270,7 @@ int launch_dense_sched(const Geom &g, const float *input, const float *asum, flo
     P.sh = g.sh; P.sw = g.sw; P.dh = g.dh; P.dw = g.dw; P.ph = g.ph; P.pw = g.pw; P.OH = g.OH; P.OW = g.OW;
     P.K = g.K; P.M = g.M; P.pix_base = 0; P.tiles_n = 0; P.tiles_total = 0;
     P.vec_ok = (g.C % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
-    P.dual = (L.G == 1 && g.Cout <= 16) ? 1 : 0;
+    P.dual = 0;
     // n / d == (n * magic) >> 40 holds while n * d < 2^40; launch_dense keeps shapes beyond that on the common-K kernel
     P.magic_c = ((1ull << 40) + unsigned(g.C) - 1) / unsigned(g.C);
     P.magic_kw = ((1ull << 40) + unsigned(g.KW) - 1) / unsigned(g.KW);
@@ -1282,6 +1283,7 @@ int launch_dense_sched(const Geom &g, const float *input, const float *asum, flo
         next_group_run(L.G - g_done, &gw, &count);
         P.g_base = g_done;
         P.g_count = count;
+        P.dual = (count == 1 && plan_group_dual(g_done, L.G, g.Cout, g.K)) ? 1 : 0;
         // pixel tiles per consumer warp: as many as the shared-memory budget allows (two sets of buffers)
         const int slots = (kComputeWarps / gw) * (P.dual ? 2 : 1);   // pixel tiles in flight per unit of NTW
         int ntw = 4;

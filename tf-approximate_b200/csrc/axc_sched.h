@@ -39,6 +39,16 @@ struct PlanLayout {
 
 PlanLayout plan_layout(int K, int Cout);
 
+// A channel group with at most 16 live channels that is served by a launch of its own (the last group when the
+// group count is 1, 5, 9, ...: see next_group_run) runs "dual": lanes 16..31 repeat the channels of lanes 0..15
+// on a second pixel tile, so no lane is left without work.
+// Doubling the pixel tiles caps the K chunk at 152 for the whole filter, so with several groups it is only done
+// when K fits one such chunk anyway.
+__host__ __device__ inline bool plan_group_dual(int g, int G, int Cout, int K)
+{
+    return g == G - 1 && (G % 4) == 1 && Cout - 32 * g <= 16 && (G == 1 || K <= 152);
+}
+
 // Writes the DevQuant block of `plan`: from the host values `q`, or - when ranges_dev is given - on the device
 // from {in_min, in_max, f_min, f_max} read there (same arithmetic as the host: tf2/src/approx_ops_types.h:29-49,135-197).
 int launch_quant(const Quant &q, const float *ranges_dev, int K, unsigned char *plan, cudaStream_t stream);
