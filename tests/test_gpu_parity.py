@@ -210,6 +210,36 @@ def test_device_resident_ranges_match_host_ranges(ax):
         assert torch.equal(y_host.view(torch.int32), y_dev.view(torch.int32)), mm
 
 
+def test_two_streams_two_layers(ax):
+    """Calls on different streams, each with its own workspace, may be in flight together: two layers
+    launched back to back on two streams, several times over, give the bits each gives alone."""
+    import torch
+    rng = np.random.Generator(np.random.PCG64(41))
+    lut = cases.make_table(("noisy", 36))
+    t = ax.Table(array=lut)
+    xa = torch.from_numpy(rng.uniform(-1, 1, (4, 40, 40, 16)).astype(np.float32)).cuda()
+    fa = torch.from_numpy(rng.normal(0, 0.1, (3, 3, 16, 64)).astype(np.float32)).cuda()
+    xb = torch.from_numpy(rng.uniform(-1, 1, (2, 28, 28, 64)).astype(np.float32)).cuda()
+    fb = torch.from_numpy(rng.normal(0, 0.1, (1, 1, 64, 160)).astype(np.float32)).cuda()
+
+    def conv(x, f):
+        return ax.approx_conv2d_with_min_max_vars(x, f, -1.0, 1.0, -0.4, 0.4, strides=[1, 1, 1, 1], num_bits=8,
+                                                  mul_map_file=t, padding="SAME")
+    ya, yb = conv(xa, fa), conv(xb, fb)
+    torch.cuda.synchronize()
+    sa, sb = torch.cuda.Stream(), torch.cuda.Stream()
+    outs = []
+    for _ in range(5):
+        with torch.cuda.stream(sa):
+            oa = conv(xa, fa)
+        with torch.cuda.stream(sb):
+            ob = conv(xb, fb)
+        outs.append((oa, ob))
+    torch.cuda.synchronize()
+    for oa, ob in outs:
+        assert torch.equal(oa, ya) and torch.equal(ob, yb)
+
+
 def test_empty_batch(ax):
     import torch
     y = ax.approx_conv2d_with_min_max_vars(torch.zeros(0, 8, 8, 4).cuda(), torch.zeros(3, 3, 4, 8).cuda(),
