@@ -8,13 +8,14 @@
 // at every step, the 32 lanes look up 32 different banks: a step is one conflict-free wavefront per pixel.
 //
 //   plan_check_kernel   quantise the filter, compare with the stored copy -> `dirty`
-//   plan_sigma_kernel   column permutation sigma of the table that spreads the weight histogram evenly
-//                       over the 32 banks (8 table columns per bank)
-//   plan_build_kernel   per (channel group, chunk): greedy edge colouring lanes x banks (banks by
-//                       remaining load, lane with most remaining work first); also the permuted table
-//                       image and the sequential per-channel filter sums
-//   dense_sched_kernel  the convolution: 16 pixels per tile, activation bytes stored 8 times side by side
-//                       so that a lane can fetch "its" K row with one conflict-free LDS.128
+//   plan_sigma_kernel   column permutation sigma of the table (8 columns per bank): spreads the weight histogram
+//                       over the 32 banks, then lowers the heaviest bank of every (group, chunk) by local search
+//   plan_build_kernel   per (channel group, chunk): the schedule.  The two lanes of a pair (2p, 2p+1) always work
+//                       on the same K element, so that they fetch the same activation row; also the permuted
+//                       table image and the sequential per-channel filter sums
+//   dense_sched_kernel  the convolution: 16 pixels per tile; a lane fetches the 16 activation bytes of "its" K row
+//                       with one LDS.128 (2 pipe cycles because neighbouring lanes share the address and the 8
+//                       rows of a half warp lie in different bank groups), then 16 x (PRMT, LDS.U16, IADD)
 //
 // Arithmetic (quantiser, table index, dequantisation) is the reference's,
 // tf2/src/approx_nn_conv_kernels.cpp:167-296; results are bit-identical to the common-K kernel.
@@ -322,16 +323,19 @@ __global__ void __launch_bounds__(256) plan_sigma_kernel(const uint8_t *__restri
 // plan_build.  blockIdx.x < G*NCH: schedule of (group, chunk), one warp.  Then 256 blocks that write the
 // permuted table image, then ceil(Cout/32) blocks for the filter sums.
 //
-// A step assigns to every lane (= output channel of the group) one K element of the chunk such that
-//   (1) the 32 table columns looked up lie in 32 different banks, and
-//   (2) within each quarter warp the 8 activation rows read (16 bytes each, one LDS.128) lie in 8
-//       different 16-byte bank groups, i.e. have different (row mod 8);
-// greedy: banks by remaining load, largest first; among the lanes that still have an element in the bank
-// with an admissible row class, the lane with the most remaining elements.  Idle lanes look up one of 32
-// zero words (one per bank) through one of 8 all-zero activation rows (one per row class).
+// A step assigns to every lane pair (= two neighbouring output channels of the group) one K element of the
+// chunk such that
+//   (1) the table columns looked up by the 32 lanes lie in 32 different banks,
+//   (2) both lanes of the pair read the same activation row (16 bytes, one LDS.128), and
+//   (3) the 8 rows read by a half warp lie in 8 different 16-byte bank groups, i.e. have different (row mod 8).
+// An element whose two weights fall into the same bank is split: each lane does it in a step of its own while
+// its neighbour idles on the same row.  Greedy: pairs with the most work left first, each taking the admissible
+// item with the heaviest banks; then a repair pass (see the loop).  Idle lanes look up one of 32 zero words (one
+// per bank); bit 14 of their program word makes the kernel put 0 in place of the activation byte, whatever row
+// they read; a pair without an item reads one of 8 all-zero rows (one per row class).
 //
 // Program word of a step:  byte0 = 2*(slot&127)  byte2 = 1 + (slot>>7)   {byte1:byte3} = 16 * row
-// with row = 8 + (l - chunk start); idle: byte0 = 4*bank, byte2 = 3, row = an unused row class 0..7.
+// with row = 8 + (l - chunk start); idle: byte0 = 4*bank, byte2 = 3, bit 14 set.
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(32) plan_build_kernel(const float *__restrict__ filter, const uint16_t *__restrict__ lut,
                                                         unsigned char *__restrict__ plan, PlanLayout L, int K, int Cout)
@@ -630,10 +634,11 @@ constexpr int kBarIter = 2;   // consumers + loaders: next activation buffers co
 // Tile group = NT pixel tiles of 16 pixels x (32*GW) channels, NT = (8/GW) * NTW.
 // Warps 0..7  "consumers": warp w serves channel group w % GW and the NTW pixel tiles (w / GW)*NTW + i; it walks
 //             the whole schedule of its (group, chunk) and reuses every program word for its NTW tiles.
-// Warps 8..11 "loaders": gather + quantise the activation rows of the next (tile group, chunk) into the other
-//             set of buffers while the consumers work.  An activation buffer is [8 zero rows + KC rows][16 pixel
-//             bytes]; the schedule guarantees that the 8 rows a quarter warp reads in one LDS.128 fall into 8
-//             different 16-byte bank groups.
+// Warps 8..   "loaders" (LW of them, each owning whole pixel tiles): gather + quantise the activation rows of the
+//             next (tile group, chunk) into the other set of buffers while the consumers work.  An activation
+//             buffer is [8 zero rows + KC rows][16 pixel bytes]; the schedule guarantees that the two lanes of a
+//             pair read the same row and that the 8 rows a half warp reads in one LDS.128 fall into 8 different
+//             16-byte bank groups.
 // The patch sums come from patch_sum_kernel, which runs before this kernel.
 template <int GW, int NTW, int LW>
 __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kernel(const SchedParams P)
