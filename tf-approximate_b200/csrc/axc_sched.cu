@@ -40,8 +40,9 @@ constexpr int kStepsInSmemMax = 1024;
 __device__ __forceinline__ unsigned q_u8(float x, float off, float inv)
 {
     const float v = __fadd_rn(__fmul_rn(__fsub_rn(x, off), inv), 0.5f);
-    const unsigned u = __float2uint_rz(v);
-    return u > 255u ? 255u : u;
+    unsigned u;
+    asm("cvt.rzi.u8.f32 %0, %1;" : "=r"(u) : "f"(v));     // truncates and clamps to 0..255 (NaN -> 0)
+    return u;
 }
 
 // prmt.b32 with an immediate selector; a selector nibble with bit 3 set replicates the sign of the byte
@@ -1110,11 +1111,12 @@ int buffers_that_fit(const SchedParams &P, int NT)
 // Next run of channel groups for a launch: `rem` groups are left; returns the GW of the launch and how many
 // groups it covers.  Whole multiples of 8 go together; 5 and 6 are cut into 4 + 1 and 4 + 2; 3 and 7 are rounded
 // up to a launch of 4 resp. 8 with one idle consumer-warp column (cheaper than a second launch).
-static void next_group_run(int rem, int *gw, int *count)
+static void next_group_run(int rem, int K, int *gw, int *count)
 {
     if (rem >= 8) { *gw = 8; *count = (rem / 8) * 8; return; }
     if (rem == 7) { *gw = 8; *count = 7; return; }
     if (rem >= 4) { *gw = 4; *count = 4; return; }
+    if (rem == 3 && K <= 64) { *gw = 2; *count = 2; return; }   // short schedules: 2 + 1 measured faster than 4 with a gap
     if (rem == 3) { *gw = 4; *count = 3; return; }
     *gw = rem; *count = rem;
 }
@@ -1129,7 +1131,7 @@ PlanLayout plan_layout(int K, int Cout)
     int smallest = 8;
     for (int rem = L.G; rem > 0;) {
         int gw, count;
-        next_group_run(rem, &gw, &count);
+        next_group_run(rem, K, &gw, &count);
         if (gw < smallest) smallest = gw;
         rem -= count;
     }
@@ -1285,7 +1287,7 @@ int launch_dense_sched(const Geom &g, const float *input, const float *asum, flo
     int g_done = 0;
     while (g_done < L.G) {
         int gw, count;
-        next_group_run(L.G - g_done, &gw, &count);
+        next_group_run(L.G - g_done, g.K, &gw, &count);
         P.g_base = g_done;
         P.g_count = count;
         P.dual = (count == 1 && plan_group_dual(g_done, L.G, g.Cout, g.K)) ? 1 : 0;
