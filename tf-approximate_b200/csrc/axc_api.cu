@@ -147,9 +147,9 @@ Workspace dense_workspace(int K, int Cout)
     return w;
 }
 
-size_t dense_workspace_total(int K, int Cout, long long M)
+size_t dense_workspace_total(int K, int Cout, long long)
 {
-    return plan_layout(K, Cout).total + dense_workspace(K, Cout).total + round256(size_t(M) * 4);
+    return plan_layout(K, Cout).total + dense_workspace(K, Cout).total;
 }
 
 Workspace depthwise_workspace(int KHW, int C, int mult)

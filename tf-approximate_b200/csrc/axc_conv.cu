@@ -535,10 +535,7 @@ int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, con
     if (scheduled) {
         rc = launch_plan(lut_dev, table_uid, g, filter, plan, L, dbg ? dbg->qfilter : nullptr, stream);
         if (rc) return rc;
-        float *asum = reinterpret_cast<float *>(wsb + ws.total);
-        rc = launch_patch_sums(g, input, asum, stream);
-        if (rc) return rc;
-        rc = launch_dense_sched(g, input, asum, output, plan, L, dbg ? dbg->acc : nullptr, di, stream);
+        rc = launch_dense_sched(g, input, output, plan, L, dbg ? dbg->acc : nullptr, di, stream);
         if (rc) return rc;
         gate = &reinterpret_cast<const PlanHeader *>(plan)->fallback;
     }

@@ -607,7 +607,6 @@ struct SchedParams {
     const unsigned char *plan;
     PlanLayout L;
     const float *input;
-    const float *asum;        // [M] patch sums from patch_sum_kernel
     float *output;
     int32_t *acc_out;
     int N, H, W, C, KH, KW, Cout;
@@ -664,6 +663,7 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
     // small tables below the table planes, then as many activation buffers as fit; the rest above the planes
     unsigned cur = (dyn0 + 15u) & ~15u;
     const unsigned sGeo = cur;               cur += unsigned(nt_eff) * kTilePix * 16u;
+    const unsigned sAsum = cur;              cur += 3u * unsigned(nt_eff) * kTilePix * 4u;   // patch sums, 3 tile groups in rotation
     const bool tap_table = !P.vec_ok && P.K <= kTapTableMax;
     const unsigned sTap = cur;               cur += tap_table ? unsigned(P.K) * 8u : 0u;
     const int n_sched = P.L.G * P.L.NCH;
@@ -760,8 +760,15 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
             const int LQ = (kc + 3) >> 2;
             const int lq_first = (ptid & 31) >> 4;          // this thread's quads: lq_first + QS * s
             const int lw = ptid >> 5;                       // a loader warp owns whole tiles: lw, lw + LW, ...
-            const int stages = lq_first < LQ ? (LQ - lq_first + QS - 1) / QS : 0;
+            const int stages = (LQ + QS - 1) / QS;          // the same for both halves of the warp; quads >= LQ are masked
             for (int t = lw; t < nt_eff; t += kLoaderWarps) {
+                // Patch sum of pixel p (lanes 0..15): the raw taps added in K order, as the reference does
+                // (tf2/src/approx_nn_conv_kernels.cpp:272-295).  Lane p holds the even quads of the pixel, lane
+                // p + 16 the odd ones; the running sum takes the four values of the even quad, then the four of
+                // the odd quad handed over by shuffles.  It is carried from chunk to chunk in shared memory.
+                const unsigned sa = sAsum + ((unsigned(tl % 3) * unsigned(nt_eff) + unsigned(t)) * kTilePix + unsigned(p)) * 4u;
+                float rs = 0.0f;
+                if (c != 0 && (ptid & 31) < 16) rs = __uint_as_float(lds32(sa));
                 const uint4 gq = lds128(sGeo + unsigned(t * kTilePix + p) * 16u);
                 const long long base = (long long)(((unsigned long long)gq.y << 32) | gq.x);
                 const int iy0 = int(gq.z), ix0 = int(gq.w);
@@ -776,7 +783,7 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
 #pragma unroll
                     for (int u = 0; u < kBatch; ++u) {
                         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (s0 + u < stages) {
+                        if (lq_first + QS * (s0 + u) < LQ) {
                             if (P.vec_ok) {
                                 const int iy = iy0 + ky * P.dh, ix = ix0 + kx * P.dw;
                                 if (iy >= 0 && iy < P.H && ix >= 0 && ix < P.W)
@@ -815,17 +822,24 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
                     // into two groups of four consecutive words
 #pragma unroll
                     for (int u = 0; u < kBatch; ++u) {
-                        if (s0 + u < stages) {
+                        if (s0 + u < stages) {                  // uniform over the warp
                             const int lq = lq_first + QS * (s0 + u);
                             const unsigned a = bb + unsigned(lq * 4) * 16u;
-                            const float4 v = st[u];
-                            sts8(a, q_u8(v.x, Q.in_off, Q.in_inv));
-                            if (lq * 4 + 1 < kc) sts8(a + 16, q_u8(v.y, Q.in_off, Q.in_inv));
-                            if (lq * 4 + 2 < kc) sts8(a + 32, q_u8(v.z, Q.in_off, Q.in_inv));
-                            if (lq * 4 + 3 < kc) sts8(a + 48, q_u8(v.w, Q.in_off, Q.in_inv));
+                            const float4 v = st[u];             // zeros beyond the chunk
+                            if (lq < LQ) {
+                                sts8(a, q_u8(v.x, Q.in_off, Q.in_inv));
+                                if (lq * 4 + 1 < kc) sts8(a + 16, q_u8(v.y, Q.in_off, Q.in_inv));
+                                if (lq * 4 + 2 < kc) sts8(a + 32, q_u8(v.z, Q.in_off, Q.in_inv));
+                                if (lq * 4 + 3 < kc) sts8(a + 48, q_u8(v.w, Q.in_off, Q.in_inv));
+                            }
+                            const float ox = __shfl_down_sync(0xffffffffu, v.x, 16), oy = __shfl_down_sync(0xffffffffu, v.y, 16);
+                            const float oz = __shfl_down_sync(0xffffffffu, v.z, 16), ow = __shfl_down_sync(0xffffffffu, v.w, 16);
+                            rs = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(rs, v.x), v.y), v.z), v.w);
+                            rs = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(rs, ox), oy), oz), ow);
                         }
                     }
                 }
+                if ((ptid & 31) < 16) sts32(sa, __float_as_uint(rs));
             }
         };
 
@@ -894,15 +908,6 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
         long long m0_next = 0;
         int nt_next = 0;
         if (tl + 1 < my_groups) group_coords(tl + 1, &m0_next, &nt_next);
-        // epilogue operands, requested a whole tile group ahead of their use: lane x of the warp holds the
-        // patch sum of pixel x of each of the warp's tiles
-        float asum_lane[NTW];
-#pragma unroll
-        for (int i = 0; i < NTW; ++i) {
-            const int tile = P.dual ? 2 * (slot * NTW + i) + half : slot * NTW + i;
-            const long long pix = m0 + tile * kTilePix + (lane & 15);
-            asum_lane[i] = ((P.dual || lane < kTilePix) && pix < P.M) ? __ldg(P.asum + pix) : 0.0f;
-        }
         {
             const int j = (P.g_base + nt * GW + gl) * 32 + chan_lane;
             if (nt != t2_nt) { t2 = j < P.Cout ? __fmul_rn(Q.m1, __ldg(bsum + j)) : 0.0f; t2_nt = nt; }
@@ -960,7 +965,7 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
 #pragma unroll
                 for (int x = 0; x < kTilePix; ++x) {
                     const long long pix = m0 + tile * kTilePix + x;
-                    const float a_sum = __shfl_sync(0xffffffffu, asum_lane[i], x + 16 * half);
+                    const float a_sum = __uint_as_float(lds32(sAsum + ((unsigned(tl % 3) * unsigned(nt_eff) + unsigned(tile)) * kTilePix + unsigned(x)) * 4u));
                     if (live && pix < P.M) {
                         const float t0 = __fmul_rn(float(acc[i][x]), Q.s1s2);
                         const float t1 = __fmul_rn(Q.m2, a_sum);
@@ -974,106 +979,6 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
         m0 = m0_next;
         nt = nt_next;
     }
-}
-
-// ------------------------------------------------------------------------------------------------
-// patch sums: aSum[p] = sum over the patch of output pixel p of the raw fp32 taps, added in K order
-// (ky, kx, c) like the reference (tf2/src/approx_nn_conv_kernels.cpp:272-295).  A block owns up to 64
-// consecutive output pixels of one output row; per filter row ky it stages the input row segment they
-// touch in shared memory (coalesced), then one thread per pixel walks its taps.  Out-of-image taps are
-// zeros in the reference; adding +0.0 never changes a sum that started at +0.0, so they are skipped.
-// When a whole row segment does not fit, the segment of one kx (and one channel chunk, for 1-wide
-// filters) is staged at a time; the order of additions is the same.
-// ------------------------------------------------------------------------------------------------
-constexpr int kPsPixels = 64;
-constexpr int kPsThreads = 128;
-constexpr int kPsFloats = 11 * 1024;   // at most 44 KiB of staging per block
-
-struct PatchSumParams {
-    const float *input;
-    float *asum;
-    int N, H, W, C, KH, KW, sh, sw, dh, dw, ph, pw, OH, OW;
-    int tiles_per_row;
-    int kx_group;     // KW (whole row segment staged) or 1
-    int cc;           // channels staged at a time
-    int ccp;          // shared-memory pixel stride (odd, to spread banks)
-    int vec;          // C % 4 == 0, 16-byte aligned input, cc % 4 == 0
-};
-
-__global__ void __launch_bounds__(kPsThreads) patch_sum_kernel(const PatchSumParams P)
-{
-    extern __shared__ __align__(16) float tile[];   // span * ccp floats, sized by the launcher
-    const int tid = threadIdx.x;
-    long long b = blockIdx.x;
-    const int tr = int(b % P.tiles_per_row); b /= P.tiles_per_row;
-    const int oh = int(b % P.OH);
-    const int n = int(b / P.OH);
-    const int ow0 = tr * kPsPixels;
-    const int tp = min(kPsPixels, P.OW - ow0);
-    const int ix_base = ow0 * P.sw - P.pw;
-    float sum = 0.0f;
-    for (int ky = 0; ky < P.KH; ++ky) {
-        const int iy = oh * P.sh - P.ph + ky * P.dh;
-        if (iy < 0 || iy >= P.H) continue;                       // uniform over the block
-        const float *row = P.input + (((long long)n * P.H + iy) * P.W) * P.C;
-        for (int kx0 = 0; kx0 < P.KW; kx0 += P.kx_group) {
-            const int nkx = min(P.kx_group, P.KW - kx0);
-            const int ix_lo = ix_base + kx0 * P.dw;
-            const int span = (tp - 1) * P.sw + (nkx - 1) * P.dw + 1;   // input pixels staged
-            for (int c0 = 0; c0 < P.C; c0 += P.cc) {
-                const int ccn = min(P.cc, P.C - c0);
-                __syncthreads();
-                if (P.vec) {
-                    const int q4 = ccn >> 2;
-                    const int total = span * q4;
-                    for (int i0 = tid; i0 < total; i0 += 4 * kPsThreads) {
-                        float4 v[4];
-                        int dst[4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {      // four independent loads in flight per thread
-                            const int i = i0 + u * kPsThreads;
-                            v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                            dst[u] = -1;
-                            if (i < total) {
-                                const int x = i / q4, c4 = (i - x * q4) * 4;
-                                const int ix = ix_lo + x;
-                                if (ix >= 0 && ix < P.W) v[u] = __ldg(reinterpret_cast<const float4 *>(row + (long long)ix * P.C + c0 + c4));
-                                dst[u] = x * P.ccp + c4;
-                            }
-                        }
-#pragma unroll
-                        for (int u = 0; u < 4; ++u)
-                            if (dst[u] >= 0) {
-                                float *d = tile + dst[u];
-                                d[0] = v[u].x; d[1] = v[u].y; d[2] = v[u].z; d[3] = v[u].w;
-                            }
-                    }
-                } else {
-                    for (int i = tid; i < span * ccn; i += kPsThreads) {
-                        const int x = i / ccn, c = i - x * ccn;
-                        const int ix = ix_lo + x;
-                        tile[x * P.ccp + c] = (ix >= 0 && ix < P.W) ? __ldg(row + (long long)ix * P.C + c0 + c) : 0.0f;
-                    }
-                }
-                __syncthreads();
-                if (tid < tp) {
-                    for (int kx = 0; kx < nkx; ++kx) {
-                        const float *src = tile + (tid * P.sw + kx * P.dw) * P.ccp;
-                        int c = 0;
-                        for (; c + 8 <= ccn; c += 8) {
-                            float v[8];
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) v[e] = src[c + e];
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) sum = __fadd_rn(sum, v[e]);
-                        }
-                        for (; c < ccn; ++c) sum = __fadd_rn(sum, src[c]);
-                    }
-                }
-            }
-        }
-    }
-    if (tid < tp) P.asum[((long long)n * P.OH + oh) * P.OW + ow0 + tid] = sum;
 }
 
 template <int GW, int NTW, int LW>
@@ -1097,6 +1002,7 @@ int buffers_that_fit(const SchedParams &P, int NT)
 {
     unsigned cur = 1024u;                                     // first byte after the driver's reserved kilobyte
     cur += unsigned(NT) * kTilePix * 16u;
+    cur += 3u * unsigned(NT) * kTilePix * 4u;
     if (!P.vec_ok && P.K <= kTapTableMax) cur += unsigned(P.K) * 8u;
     if (P.L.G * P.L.NCH <= kStepsInSmemMax) cur += unsigned(P.L.G * P.L.NCH) * 4u;
     cur = (cur + 127u) & ~127u;
@@ -1234,45 +1140,12 @@ int launch_plan(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, cons
     return AXC_OK;
 }
 
-int launch_patch_sums(const Geom &g, const float *input, float *asum, cudaStream_t stream)
-{
-    PatchSumParams S;
-    S.input = input; S.asum = asum;
-    S.N = g.N; S.H = g.H; S.W = g.W; S.C = g.C; S.KH = g.KH; S.KW = g.KW;
-    S.sh = g.sh; S.sw = g.sw; S.dh = g.dh; S.dw = g.dw; S.ph = g.ph; S.pw = g.pw; S.OH = g.OH; S.OW = g.OW;
-    S.tiles_per_row = (g.OW + kPsPixels - 1) / kPsPixels;
-    const int tp = g.OW < kPsPixels ? g.OW : kPsPixels;
-    auto odd = [](int v) { return v | 1; };
-    const long long full_span = (long long)(tp - 1) * g.sw + (long long)(g.KW - 1) * g.dw + 1;
-    if (full_span * odd(g.C) <= kPsFloats) {
-        S.kx_group = g.KW; S.cc = g.C;                      // the whole row segment of a filter row
-    } else {
-        S.kx_group = 1;
-        const long long span1 = (long long)(tp - 1) * g.sw + 1;
-        long long cc = kPsFloats / span1 - 1;               // room for the odd stride
-        if (cc >= g.C) cc = g.C;
-        else cc &= ~3ll;
-        if (cc < 4) return AXC_INVALID_ARGUMENT;            // stride > ~170: no layer of the reference's nets
-        S.cc = int(cc);
-    }
-    S.ccp = odd(S.cc);
-    S.vec = (g.C % 4 == 0) && (S.cc % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
-    const long long blocks = (long long)g.N * g.OH * S.tiles_per_row;
-    // only what one staging step needs, so that many blocks share an SM and hide each other's load latency
-    const long long span = (long long)(tp - 1) * g.sw + (long long)(S.kx_group - 1) * g.dw + 1;
-    const size_t smem = size_t(span) * S.ccp * sizeof(float);
-    patch_sum_kernel<<<unsigned(blocks), kPsThreads, smem, stream>>>(S);
-    AXC_CUDA(cudaGetLastError());
-    count_launch();
-    return AXC_OK;
-}
-
-int launch_dense_sched(const Geom &g, const float *input, const float *asum, float *output,
+int launch_dense_sched(const Geom &g, const float *input, float *output,
                        const unsigned char *plan, const PlanLayout &L, int32_t *acc_out, const DeviceInfo &di,
                        cudaStream_t stream)
 {
     SchedParams P;
-    P.plan = plan; P.L = L; P.input = input; P.asum = asum; P.output = output; P.acc_out = acc_out;
+    P.plan = plan; P.L = L; P.input = input; P.output = output; P.acc_out = acc_out;
     P.N = g.N; P.H = g.H; P.W = g.W; P.C = g.C; P.KH = g.KH; P.KW = g.KW; P.Cout = g.Cout;
     P.sh = g.sh; P.sw = g.sw; P.dh = g.dh; P.dw = g.dw; P.ph = g.ph; P.pw = g.pw; P.OH = g.OH; P.OW = g.OW;
     P.K = g.K; P.M = g.M; P.pix_base = 0; P.tiles_n = 0; P.tiles_total = 0;

@@ -56,10 +56,7 @@ int launch_quant(const Quant &q, const float *ranges_dev, int K, unsigned char *
 int launch_plan(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const float *filter,
                 unsigned char *plan, const PlanLayout &L, uint8_t *qf_debug, cudaStream_t stream);
 
-// aSum[p] for every output pixel, in the reference's order of additions.
-int launch_patch_sums(const Geom &g, const float *input, float *asum, cudaStream_t stream);
-
-int launch_dense_sched(const Geom &g, const float *input, const float *asum, float *output,
+int launch_dense_sched(const Geom &g, const float *input, float *output,
                        const unsigned char *plan, const PlanLayout &L, int32_t *acc_out, const DeviceInfo &di,
                        cudaStream_t stream);
 
