@@ -92,7 +92,7 @@ int axc_depthwise_conv2d_output_dims(const axc_conv_desc *desc, int64_t out4[4])
 /* Device scratch a forward call needs; stands in for the reference's allocate_temp buffers
  * (tf2/src/approx_nn_conv_ops.cpp:590-617).  The caller allocates it, 256-byte aligned.
  * For the dense op it holds the filter's lookup plan (quantised filter copy, table image, per-lane lookup
- * schedule, filter sums) and the per-pixel patch sums.  The plan is rebuilt only when the buffer does not
+ * schedule, filter sums) and the fallback kernel's filter program.  The plan is rebuilt only when the buffer does not
  * already hold the plan of this very filter (values, ranges, table): keep one buffer per layer between
  * calls, leave it untouched, and the preparation is paid once; a fresh or recycled buffer is always safe
  * (its first 256 bytes decide), only slower.  One buffer serves one stream at a time. */

@@ -64,7 +64,7 @@ struct Workspace {
     size_t prog_bytes, sums_off, status_off, total;
 };
 Workspace dense_workspace(int K, int Cout);      // region of the common-K kernel
-size_t dense_workspace_total(int K, int Cout, long long M);   // plan of the scheduled kernel + that region + patch sums [M]
+size_t dense_workspace_total(int K, int Cout, long long M);   // plan of the scheduled kernel + that region (M unused)
 Workspace depthwise_workspace(int KHW, int C, int mult);
 
 // Kernel launchers (axc_conv.cu / axc_depthwise.cu).

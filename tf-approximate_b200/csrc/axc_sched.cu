@@ -639,7 +639,7 @@ constexpr int kBarIter = 2;   // consumers + loaders: next activation buffers co
 //             buffer is [8 zero rows + KC rows][16 pixel bytes]; the schedule guarantees that the two lanes of a
 //             pair read the same row and that the 8 rows a half warp reads in one LDS.128 fall into 8 different
 //             16-byte bank groups.
-// The patch sums come from patch_sum_kernel, which runs before this kernel.
+// The loaders also add up the raw taps of every pixel (the patch sums of the dequantisation).
 template <int GW, int NTW, int LW>
 __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kernel(const SchedParams P)
 {
