@@ -6,6 +6,7 @@ the generated TensorFlow wrapper of `ApproxConv2DWithMinMaxVars`
 torch is used for device memory and streams only."""
 import collections
 import ctypes as C
+import hashlib
 import threading
 
 import numpy as np
@@ -67,6 +68,14 @@ def _table_for(mul_map_file, num_bits):
     if isinstance(mul_map_file, Table):
         return mul_map_file
     key = (mul_map_file or "", int(num_bits))
+    if mul_map_file:
+        # key by content, so that a file rewritten under the same name is not served from the cache and two
+        # names of the same table share one device replica; an unreadable file goes on to raise in Table()
+        try:
+            with open(mul_map_file, "rb") as fh:
+                key = ("sha256", hashlib.sha256(fh.read(131072)).hexdigest(), int(num_bits))
+        except OSError:
+            pass
     with _tables_lock:
         t = _tables.get(key)
         if t is None:

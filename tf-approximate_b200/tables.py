@@ -35,3 +35,64 @@ def read_table(path):
     if t.size < 65536:
         raise ValueError("ApproxTF: Couldn't read the lookup table!")
     return t[:65536].astype(np.uint16)
+
+
+def table_from_function(fn):
+    """Tabulates fn(a, b) -> product for all 8-bit a (activation) and b (weight), the loop of the reference's
+    generation recipe (tf2/README.md:104-117).  `fn` may take numpy arrays (tried first) or scalars."""
+    a = np.repeat(np.arange(256, dtype=np.uint32), 256)
+    b = np.tile(np.arange(256, dtype=np.uint32), 256)
+    try:
+        v = np.asarray(fn(a, b))
+        if v.shape != (65536,):
+            raise TypeError
+    except Exception:
+        v = np.array([fn(int(x), int(y)) for x, y in zip(a, b)])
+    if v.min() < 0 or v.max() > 65535:
+        raise ValueError("a table entry does not fit 16 bits")
+    return v.astype(np.uint16)
+
+
+def table_from_c_source(c_path, symbol, cc="gcc"):
+    """Compiles a C file that defines `uint16_t symbol(uint8_t a, uint8_t b)` - the form of the EvoApprox
+    multipliers the reference ships (tf1/axqconv/axmult/*.c) - and tabulates it."""
+    import ctypes
+    import os
+    import subprocess
+    import tempfile
+    with tempfile.TemporaryDirectory() as tmp:
+        so = os.path.join(tmp, "mul.so")
+        subprocess.run([cc, "-O2", "-shared", "-fPIC", "-o", so, c_path], check=True, capture_output=True)
+        lib = ctypes.CDLL(so)
+        f = getattr(lib, symbol)
+        f.restype = ctypes.c_uint16
+        f.argtypes = [ctypes.c_uint8, ctypes.c_uint8]
+        return table_from_function(lambda a, b: f(a, b))
+
+
+def table_report(table):
+    """Figures that characterise an approximate multiplier table against the exact product."""
+    t = np.asarray(table, dtype=np.int64).reshape(256, 256)
+    e = exact_table().astype(np.int64).reshape(256, 256)
+    err = t - e
+    return {"exact": bool((err == 0).all()),
+            "symmetric": bool((t == t.T).all()),          # operand order matters for the others
+            "max_abs_error": int(np.abs(err).max()),
+            "mean_abs_error": float(np.abs(err).mean()),
+            "mean_rel_error": float((np.abs(err)[1:, 1:] / e[1:, 1:]).mean()),
+            "zero_row_is_zero": bool((t[0] == 0).all() and (t[:, 0] == 0).all())}
+
+
+def validate_table_file(path):
+    """Checks the on-disk format (raw little-endian uint16, at least 65536 entries, no header:
+    tf2/src/approx_ops_types.h:205-216) and returns table_report() of its content plus size and sha256."""
+    import hashlib
+    import os
+    size = os.path.getsize(path)
+    if size < 131072:
+        raise ValueError("ApproxTF: Couldn't read the lookup table! (%d bytes, 131072 needed)" % size)
+    with open(path, "rb") as fh:
+        raw = fh.read(131072)
+    rep = table_report(np.frombuffer(raw, dtype="<u2"))
+    rep.update({"bytes": size, "trailing_bytes": size - 131072, "sha256": hashlib.sha256(raw).hexdigest()})
+    return rep
