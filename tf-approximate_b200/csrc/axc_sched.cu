@@ -614,6 +614,7 @@ struct SchedParams {
     long long M;              // end of the pixel range of this launch (all pixels: N*OH*OW)
     long long pix_base;       // first pixel of the range
     int g_base, g_count;      // channel groups [g_base, g_base + g_count) are served by this launch
+    int split;                // consumer halves with barriers of their own (kernels with two or more slots)
     int dual;                 // plan_group_dual: lanes 16..31 repeat the channels of lanes 0..15 on a second pixel tile
     int tiles_n;              // channel tiles of 32*GW channels
     long long tiles_total;    // pixel tile groups x channel tiles
@@ -630,6 +631,7 @@ __device__ __forceinline__ int fast_div(int n, unsigned long long magic)
 #define AXC_BAR(id, count) asm volatile("bar.sync %0, %1;" ::"n"(id), "n"(count) : "memory")
 constexpr int kBarLoad = 1;   // loaders: pixel geometry of the tile group published
 constexpr int kBarIter = 2;   // consumers + loaders: next activation buffers complete, current ones released
+constexpr int kBarIterB = 3;  // the same for the second half of the pixel-tile slots (kernels with two or more slots)
 
 // Tile group = NT pixel tiles of 16 pixels x (32*GW) channels, NT = (8/GW) * NTW.
 // Warps 0..7  "consumers": warp w serves channel group w % GW and the NTW pixel tiles (w / GW)*NTW + i; it walks
@@ -648,6 +650,12 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
     constexpr int kSchedThreads = (kComputeWarps + LW) * 32;
     constexpr int QS = 2;                            // a loader warp fetches 16 pixels x 2 neighbouring quads per load
     constexpr int SLOTS = kComputeWarps / GW;        // pixel-tile slots
+    // With two or more slots the consumer warps form two halves (lower / upper slots) that meet the loaders at
+    // barriers of their own, half an iteration apart: while one half dequantises and stores, waits or starts up,
+    // the other keeps the shared-memory pipe busy.  The loaders fill the buffers of the lower half first.
+    constexpr int kHalfCount = (kComputeWarps / 2 + LW) * 32;
+    constexpr int kFullCount = (kComputeWarps + LW) * 32;
+    const bool split = SLOTS >= 2 && P.split != 0;
     constexpr int NT = SLOTS * NTW;                  // pixel tiles per tile group
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const PlanHeader *hdr = reinterpret_cast<const PlanHeader *>(P.plan);
@@ -732,8 +740,10 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
             return (iy < unsigned(P.H) && ix < unsigned(P.W)) ? __ldg(P.input + base + int(off)) : 0.0f;
         };
 
-        auto produce = [&](long long tl, int c, unsigned parity) {
-            if (c == 0) {
+        // half_sel: -1 all tiles, else only the tiles of that half of the slots; the pixel geometry of a tile group
+        // is computed with its first part
+        auto produce = [&](long long tl, int c, unsigned parity, int half_sel) {
+            if (c == 0 && half_sel <= 0) {
                 // geometry of the NT*16 pixels of the tile group: {element offset of the patch origin, iy0, ix0}
                 long long m0; int nt;
                 group_coords(tl, &m0, &nt);
@@ -762,6 +772,7 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
             const int lw = ptid >> 5;                       // a loader warp owns whole tiles: lw, lw + LW, ...
             const int stages = (LQ + QS - 1) / QS;          // the same for both halves of the warp; quads >= LQ are masked
             for (int t = lw; t < nt_eff; t += kLoaderWarps) {
+                if (half_sel >= 0 && (t >= nt_eff / 2 ? 1 : 0) != half_sel) continue;
                 // Patch sum of pixel p (lanes 0..15): the raw taps added in K order, as the reference does
                 // (tf2/src/approx_nn_conv_kernels.cpp:272-295).  Lane p holds the even quads of the pixel, lane
                 // p + 16 the odd ones; the running sum takes the four values of the even quad, then the four of
@@ -843,17 +854,32 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
             }
         };
 
-        if (my_groups > 0) produce(0, 0, 0u);
-        AXC_BAR(kBarIter, (kComputeWarps + kLoaderWarps) * 32);
         long long tl = 0;
         int c = 0;
         unsigned parity = 0;
         const long long total_iters = my_groups * NCH;
-        for (long long it = 0; it < total_iters; ++it) {
-            if (++c == NCH) { c = 0; ++tl; }
-            parity ^= 1u;
-            if (it + 1 < total_iters) produce(tl, c, parity);
-            AXC_BAR(kBarIter, (kComputeWarps + kLoaderWarps) * 32);
+        if (split) {
+            if (my_groups > 0) produce(0, 0, 0u, 0);
+            AXC_BAR(kBarIter, kHalfCount);
+            if (my_groups > 0) produce(0, 0, 0u, 1);
+            AXC_BAR(kBarIterB, kHalfCount);
+            for (long long it = 0; it < total_iters; ++it) {
+                if (++c == NCH) { c = 0; ++tl; }
+                parity ^= 1u;
+                if (it + 1 < total_iters) produce(tl, c, parity, 0);
+                AXC_BAR(kBarIter, kHalfCount);
+                if (it + 1 < total_iters) produce(tl, c, parity, 1);
+                AXC_BAR(kBarIterB, kHalfCount);
+            }
+        } else {
+            if (my_groups > 0) produce(0, 0, 0u, -1);
+            AXC_BAR(kBarIter, kFullCount);
+            for (long long it = 0; it < total_iters; ++it) {
+                if (++c == NCH) { c = 0; ++tl; }
+                parity ^= 1u;
+                if (it + 1 < total_iters) produce(tl, c, parity, -1);
+                AXC_BAR(kBarIter, kFullCount);
+            }
         }
         return;
     }
@@ -899,7 +925,13 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
         if (nq > 0) w_a = __ldg(pp);
         if (nq > 1) w_b = __ldg(pp + 32);
     }
-    AXC_BAR(kBarIter, (kComputeWarps + kLoaderWarps) * 32);
+    const bool upper_half = slot >= SLOTS / 2;
+    auto iter_barrier = [&]() {
+        if (!split) AXC_BAR(kBarIter, kFullCount);
+        else if (upper_half) AXC_BAR(kBarIterB, kHalfCount);
+        else AXC_BAR(kBarIter, kHalfCount);
+    };
+    iter_barrier();
 
     unsigned parity = 0;
     float t2 = 0.0f;          // m1 * bSum[j] of this lane's channel
@@ -952,7 +984,7 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
                 }
             }
             pp = pp_n; nq = nq_n; w_a = n_a; w_b = n_b;
-            AXC_BAR(kBarIter, (kComputeWarps + kLoaderWarps) * 32);
+            iter_barrier();
             parity ^= 1u;
         }
         // ---- the tile group is complete: dequantise and store ------------------------------------
@@ -1164,6 +1196,9 @@ int launch_dense_sched(const Geom &g, const float *input, float *output,
         P.g_base = g_done;
         P.g_count = count;
         P.dual = (count == 1 && plan_group_dual(g_done, L.G, g.Cout, g.K)) ? 1 : 0;
+        // two consumer halves pay off once an iteration is long enough to hide the second barrier (measured:
+        // +1-3 % for K >= 144, -14 % for K = 32)
+        P.split = L.KC >= 128 ? 1 : 0;
         // pixel tiles per consumer warp: as many as the shared-memory budget allows (two sets of buffers)
         const int slots = (kComputeWarps / gw) * (P.dual ? 2 : 1);   // pixel tiles in flight per unit of NTW
         int ntw = 4;
