@@ -229,18 +229,47 @@ def run_gpu(args):
     conv_events, runner.conv_events = runner.conv_events, None
 
     # ---- timed region 2: end to end from pinned host memory ----------------------------------------
+    # Every step copies its batch from pinned host memory and its result back.  The copies run on streams of
+    # their own (two device input buffers), so the copy of the next batch and the read-back of the last result
+    # overlap with the convolutions, as a serving loop would arrange it; all of it lies between f0 and f1.
     y_host = torch.empty(tuple(y.shape), dtype=y.dtype).pin_memory()
-    x_dev = torch.empty_like(x)
-    for _ in range(2):
-        x_dev.copy_(x_host, non_blocking=True)
-        y_host.copy_(runner.forward(x_dev), non_blocking=True)
+    main = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    x_bufs = [torch.empty_like(x), torch.empty_like(x)]
+
+    def e2e_steps(steps, start_event):
+        ready = [torch.cuda.Event(), torch.cuda.Event()]
+        consumed = [torch.cuda.Event(), torch.cuda.Event()]
+        s_in.wait_event(start_event)
+        with torch.cuda.stream(s_in):
+            x_bufs[0].copy_(x_host, non_blocking=True)
+            ready[0].record(s_in)
+        for i in range(steps):
+            b = i & 1
+            if i + 1 < steps:
+                if i >= 1:
+                    s_in.wait_event(consumed[b ^ 1])     # the forward pass that read this buffer has finished
+                with torch.cuda.stream(s_in):
+                    x_bufs[b ^ 1].copy_(x_host, non_blocking=True)
+                    ready[b ^ 1].record(s_in)
+            main.wait_event(ready[b])
+            out = runner.forward(x_bufs[b])
+            consumed[b].record(main)
+            s_out.wait_event(consumed[b])
+            with torch.cuda.stream(s_out):
+                y_host.copy_(out, non_blocking=True)
+            out.record_stream(s_out)
+        main.wait_stream(s_out)
+        main.wait_stream(s_in)
+
+    warm = torch.cuda.Event()
+    warm.record(main)
+    e2e_steps(2, warm)
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record()
-    for _ in range(args.steps):
-        x_dev.copy_(x_host, non_blocking=True)
-        y_host.copy_(runner.forward(x_dev), non_blocking=True)
-    f1.record()
+    f0.record(main)
+    e2e_steps(args.steps, f0)
+    f1.record(main)
     barrier()
     ms_e2e = f0.elapsed_time(f1)
     clocks = sampler.stop() if rank == 0 else None
