@@ -28,7 +28,7 @@ import numpy as np  # noqa: E402
 CFG_INDEX = 4          # seeds follow 1000+cfg (input), 2000+100*cfg+layer (filters)
 SM_COUNT = 148
 LOOKUPS_PER_CLK_PER_SM = 32   # one 32-bit shared-memory bank transaction per lane per clock
-NCU_DRAM_OVER_ALGORITHMIC = (204.3 + 162.1) / 411.2
+NCU_DRAM_OVER_ALGORITHMIC = (205.0 + 162.1) / 411.2
 
 
 # name -> (description for `config.workload`, default batch per GPU, input description)
@@ -305,7 +305,7 @@ def run_gpu(args):
     except Exception:
         pass
     hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
-    # DRAM bytes per launch: ncu on the single 3x3 layer N=256, 56x56x64->64 read 204.3 MB and wrote 162.1 MB
+    # DRAM bytes per launch: ncu on the single 3x3 layer N=256, 56x56x64->64 read 205.0 MB and wrote 162.1 MB
     # against 411.2 MB algorithmic (profiles/dense_kernel_cfg2_3x3_64to64.md); the whole step is too large to
     # capture, so the measured ratio is applied to the average algorithmic bytes of a launch here.
     traffic = NCU_DRAM_OVER_ALGORITHMIC * io_bytes / dense_launches
