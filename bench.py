@@ -376,21 +376,22 @@ def run_layer(args):
     table = ax.Table(array=lut)
     mm = (-1.0, 1.0, float(f.min()), float(f.max()))
     fn = ax.approx_depthwise_conv2d_with_min_max_vars if dw else ax.approx_conv2d_with_min_max_vars
+    kw = {} if dw else {"accumulate": args.accumulate}
     out = None
     for _ in range(args.warmup):
-        out = fn(x, f, *mm, [1, stride, stride, 1], 8, table, "SAME", out=out)
+        out = fn(x, f, *mm, [1, stride, stride, 1], 8, table, "SAME", out=out, **kw)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        out = fn(x, f, *mm, [1, stride, stride, 1], 8, table, "SAME", out=out)
+        out = fn(x, f, *mm, [1, stride, stride, 1], 8, table, "SAME", out=out, **kw)
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
     oh, ow = -(-h // stride), -(-w // stride)
     macs = n * oh * ow * k * k * c * (1 if dw else cout)
     io = 4 * (x.numel() + out.numel() + f.numel())
-    print(json.dumps({"layer": args.layer, "table": args.table, "ms": ms, "lut_macs": macs,
+    print(json.dumps({"layer": args.layer, "table": args.table, "accumulate": args.accumulate, "ms": ms, "lut_macs": macs,
                       "glut_macs_per_s": macs / ms / 1e6, "lookups_per_clk_per_sm_at_1965MHz": macs / (ms * 1e-3) / (SM_COUNT * 1965e6),
                       "io_gbs": io / ms / 1e6}))
 
@@ -426,6 +427,8 @@ def main():
     ap.add_argument("--per-layer", action="store_true", help="add per-layer times and lookups/clk/SM to the JSON line")
     ap.add_argument("--layer", default=None, help="time one layer instead: N,H,W,C,K,Cout,stride[,dw]")
     ap.add_argument("--table", default="truncated", choices=["truncated", "noisy", "exact"])
+    ap.add_argument("--accumulate", default="exact", choices=["exact", "reference"],
+                    help="--layer only: exact integer sum (default) or the reference's fp32 running total in K order")
     args = ap.parse_args()
     if args.layer:
         run_layer(args)

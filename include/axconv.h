@@ -41,6 +41,16 @@ typedef enum {
 
 enum { AXC_PADDING_SAME = 0, AXC_PADDING_VALID = 1, AXC_PADDING_EXPLICIT = 2 };
 enum { AXC_FORMAT_NHWC = 0, AXC_FORMAT_NCHW = 1 };
+/* How the looked-up products of one output are added up.
+ * AXC_ACCUM_EXACT_I32 (default): exact integer sum, any order; the fp32 output is the dequantisation of the
+ *   exact sum.  Equal to the reference bit for bit whenever the reference's own running total is exact.
+ * AXC_ACCUM_REFERENCE_F32: the reference's arithmetic, `total += float(entry)` in K order with an fp32 running
+ *   total (tf2/src/approx_nn_conv_kernels.cpp:245-246), which rounds once a partial sum passes 2^24.  Output
+ *   bits equal the reference's CPU kernel for every K.  Where the table and K prove that no partial sum can
+ *   round (K * largest entry <= 2^24 * the power of two dividing every entry) the fast integer kernel serves
+ *   the call, since both give the same bits; otherwise a kernel that walks K in order does (about half the
+ *   speed).  Depthwise calls ignore the field (K = kh*kw never rounds). */
+enum { AXC_ACCUM_EXACT_I32 = 0, AXC_ACCUM_REFERENCE_F32 = 1 };
 
 /* Geometry of one call: what ApproxConv2DParameters + ApproxConv2DDimensions carry
  * (tf2/src/approx_nn_conv_ops.h:36-98, filled at tf2/src/approx_nn_conv_ops.cpp:254-404).
@@ -54,6 +64,7 @@ typedef struct {
     int32_t dil_h, dil_w;
     int32_t padding;      /* AXC_PADDING_*  */
     int32_t data_format;  /* AXC_FORMAT_*   */
+    int32_t accumulate;   /* AXC_ACCUM_*: 0 = exact int32 sum (default), 1 = the reference's fp32 running total */
 } axc_conv_desc;
 
 /* Optional taps into the integer pipeline, for parity checks (device pointers, any may be
@@ -62,7 +73,8 @@ typedef struct {
 typedef struct {
     uint8_t *qinput;  /* [n,h,w,c]            element-wise quantised input               */
     uint8_t *qfilter; /* [kh*kw*filter_c,cout] element-wise quantised filter             */
-    int32_t *acc;     /* output shape          exact integer sum of the looked-up entries */
+    int32_t *acc;     /* output shape          exact integer sum of the looked-up entries; when the call is
+                                               served in reference order: that fp32 running total as an integer */
 } axc_debug_out;
 
 typedef struct axc_table axc_table;
@@ -147,7 +159,8 @@ int axc_depthwise_conv2d_forward(axc_table *table, const axc_conv_desc *desc,
  *   - the table replica must already be on `device`: call axc_table_ensure_device() beforehand (that call
  *     allocates 128 KiB); otherwise AXC_INTERNAL;
  *   - the first call on a device looks up the array's device address; make that call before any stream
- *     capture starts;
+ *     capture starts; `device` must be below 64 (the addresses are remembered in a fixed table), else
+ *     AXC_INVALID_ARGUMENT;
  *   - all calls on a device share the one array and each call overwrites what the previous one left, so
  *     two calls may not be in flight on the same GPU at the same time (different streams or threads): they
  *     would race on the scratch.  Nothing in it has to be cleared by the caller: every call rewrites the

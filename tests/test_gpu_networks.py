@@ -1,8 +1,11 @@
 """GPU: the five benchmark configurations as layer stacks.  Every convolution of the network is run on the
 GPU and re-run by the CPU checker ON THE SAME INPUT TENSOR (the GPU's own activation of the previous layer),
 so each layer is compared bit for bit - int32 accumulators and fp32 output - without errors compounding.
-Spatial size and batch are reduced so that the checker finishes in seconds; channel counts, kernel sizes,
-strides and table kinds are those of the configurations."""
+The first three tests reduce spatial size and batch so that the checker finishes in seconds; channel counts,
+kernel sizes, strides and table kinds are those of the configurations.  The full-size tests run configurations 4
+and 5 at their real spatial size (224x224 and 112x112) on one or two images against the checker, and at their
+real batch (256 and 512) compare a slice of the batch with the same images run alone - the property batch
+sharding relies on."""
 import numpy as np
 import pytest
 
@@ -69,3 +72,46 @@ def test_config5_depthwise_separable_stack(built):
     import tf_approximate_b200 as ax
     t = ax.noisy_table(3000 + 500)
     _run_network("mobilenet_stack", 28, 2, lambda i: t, 5)
+
+
+def test_config4_resnet50_full_size_layers(built):
+    """224x224 input, two images: every one of the 53 convolutions against the checker, bit for bit (the tile
+    scheduling of the large layers: several rounds per CTA, main + tail launches)."""
+    import tf_approximate_b200 as ax
+    t = ax.truncated_table()
+    _run_network("resnet50", 224, 2, lambda i: t, 4)
+
+
+def test_config5_stack_full_size_layers(built):
+    """112x112x32 input, one image, the per-configuration noisy table: all 14 layers against the checker."""
+    import tf_approximate_b200 as ax
+    t = ax.noisy_table(3000 + 500)
+    _run_network("mobilenet_stack", 112, 1, lambda i: t, 5)
+
+
+def _slice_equals_alone(kind, batch, table, seed_cfg, lo, hi):
+    import torch
+    import tf_approximate_b200 as ax
+    from tf_approximate_b200 import workloads as W
+    net = W.Network(kind)
+    filters = W.make_filters(net.convs, 2000 + 100 * seed_cfg)
+    dev = torch.device("cuda", 0)
+    runner = W.GpuRunner(net, [table], filters, dev)
+    x = torch.from_numpy(W.make_input(batch, net.hw, net.in_channels, 1000 + seed_cfg)).to(dev)
+    runner.calibrate(x)                     # frozen per-layer ranges, as in the benchmark
+    y_all = runner.forward(x)
+    y_few = runner.forward(x[lo:hi].contiguous())
+    torch.cuda.synchronize()
+    assert torch.isfinite(y_all).all()
+    assert torch.equal(y_all[lo:hi].view(torch.int32), y_few.view(torch.int32))
+
+
+def test_config4_batch256_slice_equals_alone(built):
+    """The ResNet-50 workload at its real size: images 100..103 of the batch of 256 give the bits they give alone."""
+    import tf_approximate_b200 as ax
+    _slice_equals_alone("resnet50", 256, ax.truncated_table(), 4, 100, 104)
+
+
+def test_config5_batch512_slice_equals_alone(built):
+    import tf_approximate_b200 as ax
+    _slice_equals_alone("mobilenet_stack", 512, ax.noisy_table(3000 + 500), 5, 300, 303)

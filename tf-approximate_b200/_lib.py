@@ -20,7 +20,7 @@ SYMBOLS = [
 class ConvDesc(C.Structure):
     _fields_ = [(n, C.c_int32) for n in
                 ("n", "h", "w", "c", "kh", "kw", "filter_c", "cout", "stride_h", "stride_w",
-                 "dil_h", "dil_w", "padding", "data_format")]
+                 "dil_h", "dil_w", "padding", "data_format", "accumulate")]
 
 
 class DebugOut(C.Structure):

@@ -13,6 +13,8 @@
 
 struct axc_table {
     unsigned uid;
+    uint32_t max_entry;          // largest entry
+    int common_tz;               // trailing zero bits shared by all entries (16 for an all-zero table)
     std::vector<uint16_t> host;  // 65536 entries, index (a << 8) | b
     std::mutex mu;
     std::vector<uint16_t *> dev;  // per-device replica, lazily created
@@ -25,7 +27,31 @@ static std::atomic<uint64_t> g_launches{0};
 static std::atomic<unsigned> g_table_uid{1};
 
 unsigned table_uid(const axc_table *t) { return t->uid; }
-void stamp(axc_table *t) { t->uid = g_table_uid.fetch_add(1); }
+void stamp(axc_table *t)
+{
+    t->uid = g_table_uid.fetch_add(1);
+    uint32_t mx = 0, ored = 0;
+    for (uint16_t v : t->host) {
+        mx = v > mx ? v : mx;
+        ored |= v;
+    }
+    t->max_entry = mx;
+    int tz = 0;
+    while (tz < 16 && ((ored >> tz) & 1u) == 0u) ++tz;
+    t->common_tz = tz;
+}
+
+bool table_sum_exact_in_fp32(const axc_table *t, long long K)
+{
+    if (t->max_entry == 0) return true;
+    // K <= 2^22 here (resolve_geometry) and max_entry < 2^16: the product fits 64 bits with room
+    return K * (long long)t->max_entry <= (1ll << (24 + t->common_tz));
+}
+
+bool table_sum_fits_int32(const axc_table *t, long long K)
+{
+    return K * (long long)t->max_entry <= 0x7FFFFFFFll;
+}
 
 int cuda_failed(cudaError_t e)
 {
@@ -115,6 +141,8 @@ int resolve_geometry(const axc_conv_desc *d, bool depthwise, Geom *g)
     if (d->data_format != AXC_FORMAT_NHWC) return AXC_UNIMPLEMENTED;
     if (d->padding == AXC_PADDING_EXPLICIT) return AXC_UNIMPLEMENTED;
     if (d->c != d->filter_c) return AXC_UNIMPLEMENTED;  // grouped convolution
+    if (d->accumulate != AXC_ACCUM_EXACT_I32 && d->accumulate != AXC_ACCUM_REFERENCE_F32) return AXC_INVALID_ARGUMENT;
+    g->accum = d->accumulate;
 
     g->N = d->n; g->H = d->h; g->W = d->w; g->C = d->c;
     g->KH = d->kh; g->KW = d->kw; g->Cout = d->cout;
@@ -250,9 +278,13 @@ static int forward(bool depthwise, axc_table *table, const axc_conv_desc *desc, 
     AXC_CUDA(cudaGetDevice(&prev));
     if (prev != device) AXC_CUDA(cudaSetDevice(device));
     const Quant q = make_quant(in_min, in_max, f_min, f_max);
+    // The reference's fp32 running total is served by the integer kernels whenever it provably equals the exact
+    // sum; a sum that could overflow an int32 accumulator is always added up the reference's way.
+    const bool ref_order = !depthwise && ((g.accum == AXC_ACCUM_REFERENCE_F32 && !table_sum_exact_in_fp32(table, g.K)) ||
+                                          !table_sum_fits_int32(table, g.K));
     rc = depthwise ? launch_depthwise(lut, g, q, input, filter, output, workspace, dbg, device, cudaStream_t(stream))
                    : launch_dense(lut, table_uid(table), g, q, ranges_dev, input, filter, output, workspace, dbg, device,
-                                  cudaStream_t(stream));
+                                  cudaStream_t(stream), ref_order);
     if (prev != device) cudaSetDevice(prev);
     return rc;
 }

@@ -161,9 +161,20 @@ __global__ void quantize_tensor_kernel(const float *__restrict__ x, long long n,
     for (; i < n; i += stride) q[i] = uint8_t(quantize_u8(x[i], off, inv));
 }
 
+// The table entry `v` (0..65535) as fp32 without a conversion instruction: 2^23 + v is exact in fp32 and has the
+// bit pattern 0x4B000000 | v; subtracting 2^23 again is exact too.
+__device__ __forceinline__ float entry_to_float(unsigned v)
+{
+    return __fsub_rn(__uint_as_float(0x4B000000u | v), 8388608.0f);
+}
+
 // One CTA per SM, persistent over output tiles of TM pixels x TN channels
 // (TN = 32 * WN, TM = 16 * (8 / WN)).  Lane = output channel, 16 pixels per lane.
-template <int WN>
+// REF = false: exact int32 sum.  REF = true: the reference's arithmetic, an fp32 running total that takes the
+// entries one by one in K order (tf2/src/approx_nn_conv_kernels.cpp:245-246, 201-202); every lane walks K from
+// 0 upwards, chunk by chunk, so the additions - and their roundings once the total passes 2^24 - are the
+// reference's.
+template <int WN, bool REF>
 __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
 {
     constexpr int WM = kWarps / WN;
@@ -254,7 +265,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
             pix[s] = int(tx);
         }
 
-        int acc[kPixPerLane];
+        int acc[kPixPerLane];         // REF: the bits of the fp32 running total
 #pragma unroll
         for (int i = 0; i < kPixPerLane; ++i) acc[i] = 0;
 
@@ -429,12 +440,21 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
                     const unsigned aw[4] = {av.x, av.y, av.z, av.w};
 #pragma unroll
                     for (int pp = 0; pp < 4; ++pp) {
-                        int s = acc[pg * 4 + pp];
-                        s += int(lds_u16(__byte_perm(wv.x, aw[pp], 0x3240)));
-                        s += int(lds_u16(__byte_perm(wv.y, aw[pp], 0x3250)));
-                        s += int(lds_u16(__byte_perm(wv.z, aw[pp], 0x3260)));
-                        s += int(lds_u16(__byte_perm(wv.w, aw[pp], 0x3270)));
-                        acc[pg * 4 + pp] = s;
+                        if (REF) {
+                            float s = __int_as_float(acc[pg * 4 + pp]);
+                            s = __fadd_rn(s, entry_to_float(lds_u16(__byte_perm(wv.x, aw[pp], 0x3240))));
+                            s = __fadd_rn(s, entry_to_float(lds_u16(__byte_perm(wv.y, aw[pp], 0x3250))));
+                            s = __fadd_rn(s, entry_to_float(lds_u16(__byte_perm(wv.z, aw[pp], 0x3260))));
+                            s = __fadd_rn(s, entry_to_float(lds_u16(__byte_perm(wv.w, aw[pp], 0x3270))));
+                            acc[pg * 4 + pp] = __float_as_int(s);
+                        } else {
+                            int s = acc[pg * 4 + pp];
+                            s += int(lds_u16(__byte_perm(wv.x, aw[pp], 0x3240)));
+                            s += int(lds_u16(__byte_perm(wv.y, aw[pp], 0x3250)));
+                            s += int(lds_u16(__byte_perm(wv.z, aw[pp], 0x3260)));
+                            s += int(lds_u16(__byte_perm(wv.w, aw[pp], 0x3270)));
+                            acc[pg * 4 + pp] = s;
+                        }
                     }
                 }
             }
@@ -452,18 +472,19 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
                 const long long p = m0 + wm * kPixPerLane + i;
                 if (p < P.M) {
                     const float a_sum = lds_f32(sAsum + (wm * kPixPerLane + i) * 4);
-                    const float t0 = __fmul_rn(float(acc[i]), Q.s1s2);
+                    const float total = REF ? __int_as_float(acc[i]) : float(acc[i]);
+                    const float t0 = __fmul_rn(total, Q.s1s2);
                     const float t1 = __fmul_rn(Q.m2, a_sum);
                     const float o = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), Q.km1m2);
                     P.output[p * P.Cout + j] = o;
-                    if (P.acc_out) P.acc_out[p * P.Cout + j] = acc[i];
+                    if (P.acc_out) P.acc_out[p * P.Cout + j] = REF ? __float2int_rz(total) : acc[i];
                 }
             }
         }
     }
 }
 
-template <int WN>
+template <int WN, bool REF>
 int launch_dense_variant(const DenseParams &P, const DeviceInfo &di, cudaStream_t stream)
 {
     constexpr int TM = (kWarps / WN) * kPixPerLane;
@@ -471,17 +492,9 @@ int launch_dense_variant(const DenseParams &P, const DeviceInfo &di, cudaStream_
     DenseParams Q = P;
     Q.tiles_n = (P.Cout + TN - 1) / TN;
     Q.tiles_total = ((P.M + TM - 1) / TM) * Q.tiles_n;
-    static bool configured[64] = {};
-    int dev = 0;
-    AXC_CUDA(cudaGetDevice(&dev));
-    if (dev < 64 && !configured[dev]) {
-        AXC_CUDA(cudaFuncSetAttribute(dense_kernel<WN>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
-        configured[dev] = true;
-    } else if (dev >= 64) {
-        AXC_CUDA(cudaFuncSetAttribute(dense_kernel<WN>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
-    }
+    AXC_CUDA(cudaFuncSetAttribute(dense_kernel<WN, REF>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
     const long long grid = Q.tiles_total < di.sm_count ? Q.tiles_total : di.sm_count;
-    dense_kernel<WN><<<unsigned(grid), kThreads, size_t(di.max_smem_optin), stream>>>(Q);
+    dense_kernel<WN, REF><<<unsigned(grid), kThreads, size_t(di.max_smem_optin), stream>>>(Q);
     AXC_CUDA(cudaGetLastError());
     count_launch();
     return AXC_OK;
@@ -503,14 +516,15 @@ static int dense_variant()
 
 int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const Quant &q, const float *ranges_dev,
                  const float *input, const float *filter, float *output, void *workspace, const axc_debug_out *dbg,
-                 int device, cudaStream_t stream)
+                 int device, cudaStream_t stream, bool ref_order)
 {
     DeviceInfo di;
     int rc = device_info(device, &di);
     if (rc) return rc;
     if (di.max_smem_optin < 232448) return AXC_INTERNAL;   // the kernels are laid out for the 227 KiB of sm_100
-    // the scheduled kernel divides by C and KW with 40-bit reciprocals, exact while K * max(C, KW) < 2^40
-    const bool scheduled = dense_variant() == 0 && (long long)g.K * (g.C > g.KW ? g.C : g.KW) < (1ll << 40);
+    // the scheduled kernel divides by C and KW with 40-bit reciprocals, exact while K * max(C, KW) < 2^40; it
+    // lets every lane walk K in an order of its own, so a sum that has to be taken in K order is not its job
+    const bool scheduled = !ref_order && dense_variant() == 0 && (long long)g.K * (g.C > g.KW ? g.C : g.KW) < (1ll << 40);
     const PlanLayout L = plan_layout(g.K, g.Cout);
     const Workspace ws = dense_workspace(g.K, g.Cout);
     unsigned char *plan = static_cast<unsigned char *>(workspace);
@@ -561,8 +575,9 @@ int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, con
     P.tiles_n = 0; P.tiles_total = 0;
     P.dq = dq;
     P.vec_ok = (g.C % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
-    if (g.Cout <= 32) return launch_dense_variant<1>(P, di, stream);
-    return launch_dense_variant<2>(P, di, stream);
+    if (ref_order) return g.Cout <= 32 ? launch_dense_variant<1, true>(P, di, stream) : launch_dense_variant<2, true>(P, di, stream);
+    if (g.Cout <= 32) return launch_dense_variant<1, false>(P, di, stream);
+    return launch_dense_variant<2, false>(P, di, stream);
 }
 
 }  // namespace axc

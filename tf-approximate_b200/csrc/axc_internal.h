@@ -24,6 +24,7 @@ struct Geom {
     int OH, OW;
     int K;             // dense: KH*KW*C; depthwise: KH*KW
     long long M;       // N*OH*OW
+    int accum;         // AXC_ACCUM_*
 };
 
 void var_quant_props(float min_v, float max_v, float *scale, float *inv, float *offset);
@@ -49,6 +50,12 @@ const uint16_t *table_device_ptr(axc_table *t, int device, int *status);
 const uint16_t *table_device_ptr_if_resident(axc_table *t, int device);
 // Process-unique id of a table handle (tables are immutable after creation).
 unsigned table_uid(const axc_table *t);
+// True when a sum of K entries of the table, added one by one in fp32 in any order, cannot round: every partial
+// sum is a multiple of 2^tz (tz = trailing zero bits common to all entries) and at most K * largest entry, and
+// fp32 holds every such multiple up to 2^(24 + tz).
+bool table_sum_exact_in_fp32(const axc_table *t, long long K);
+// True when K entries cannot overflow an int32 accumulator.
+bool table_sum_fits_int32(const axc_table *t, long long K);
 
 struct DeviceInfo {
     int sm_count;
@@ -69,9 +76,11 @@ Workspace depthwise_workspace(int KHW, int C, int mult);
 
 // Kernel launchers (axc_conv.cu / axc_depthwise.cu).
 // ranges_dev: NULL, or {in_min, in_max, f_min, f_max} in device memory (then `q` is ignored).
+// ref_order: add the products up in K order with an fp32 running total (the reference's arithmetic) instead of
+// the exact integer sum.
 int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const Quant &q, const float *ranges_dev,
                  const float *input, const float *filter, float *output, void *workspace, const axc_debug_out *dbg,
-                 int device, cudaStream_t stream);
+                 int device, cudaStream_t stream, bool ref_order);
 int launch_depthwise(const uint16_t *lut_dev, const Geom &g, const Quant &q, const float *input,
                      const float *filter, float *output, void *workspace, const axc_debug_out *dbg,
                      int device, cudaStream_t stream);

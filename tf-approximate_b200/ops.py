@@ -17,6 +17,7 @@ from .errors import InvalidArgumentError, raise_for_status
 
 _PADDING = {"SAME": 0, "VALID": 1, "EXPLICIT": 2}
 _FORMAT = {"NHWC": 0, "NCHW": 1}
+_ACCUMULATE = {"exact": 0, "reference": 1}
 
 
 class Table:
@@ -94,7 +95,9 @@ def _scalar(v):
     return float(v)
 
 
-def _desc(input_shape, filter_shape, strides, padding, data_format, dilations, explicit_paddings):
+def _desc(input_shape, filter_shape, strides, padding, data_format, dilations, explicit_paddings, accumulate="exact"):
+    if accumulate not in _ACCUMULATE:
+        raise InvalidArgumentError("accumulate must be 'exact' or 'reference'")
     if len(input_shape) != 4:
         raise InvalidArgumentError("input must be 4-dimensional %s" % (tuple(input_shape),))
     if len(filter_shape) != 4:
@@ -119,7 +122,7 @@ def _desc(input_shape, filter_shape, strides, padding, data_format, dilations, e
     return _lib.ConvDesc(int(input_shape[n_i]), int(input_shape[h_i]), int(input_shape[w_i]), int(input_shape[c_i]),
                          int(filter_shape[0]), int(filter_shape[1]), int(filter_shape[2]), int(filter_shape[3]),
                          int(strides[h_i]), int(strides[w_i]), int(dilations[h_i]), int(dilations[w_i]),
-                         _PADDING[pad], _FORMAT[data_format])
+                         _PADDING[pad], _FORMAT[data_format], _ACCUMULATE[accumulate])
 
 
 def conv2d_output_shape(input_shape, filter_shape, strides, padding, data_format="NHWC", dilations=(1, 1, 1, 1),
@@ -155,7 +158,7 @@ def _workspace(device, nbytes, key):
 
 
 def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
-             mul_map_file, padding, explicit_paddings, data_format, dilations, out, debug):
+             mul_map_file, padding, explicit_paddings, data_format, dilations, out, debug, accumulate="exact"):
     L = _lib.load()
     if not isinstance(input, torch.Tensor) or not isinstance(filter, torch.Tensor):
         raise InvalidArgumentError("input and filter must be torch tensors")
@@ -166,7 +169,7 @@ def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_
     if filter.device != input.device:
         raise InvalidArgumentError("input and filter are on different devices")
     table = _table_for(mul_map_file, num_bits)
-    d = _desc(input.shape, filter.shape, strides, padding, data_format, dilations, explicit_paddings)
+    d = _desc(input.shape, filter.shape, strides, padding, data_format, dilations, explicit_paddings, accumulate)
     dims = (C.c_int64 * 4)()
     dims_fn = L.axc_depthwise_conv2d_output_dims if depthwise else L.axc_conv2d_output_dims
     raise_for_status(dims_fn(C.byref(d), dims), "ApproxConv2D")
@@ -220,16 +223,20 @@ def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_
 
 def approx_conv2d_with_min_max_vars(input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
                                     mul_map_file, padding, explicit_paddings=(), data_format="NHWC",
-                                    dilations=(1, 1, 1, 1), name=None, out=None, debug=False):
+                                    dilations=(1, 1, 1, 1), name=None, out=None, debug=False, accumulate="exact"):
     """Forward pass of `ApproxConv2DWithMinMaxVars`.
 
     input [N,H,W,C] and filter [KH,KW,C,Cout] are fp32 CUDA tensors; the four min/max values are
     host scalars (Python floats or 0-d CPU tensors) or - all four - 0-d CUDA tensors, which are then consumed on
     the device without a host round trip; `mul_map_file` is the raw uint16[65536] table file
     ('' = exact products) or a `Table`.  Returns the fp32 output [N,OH,OW,Cout]; with `debug=True`
-    also the quantised operands and the int32 accumulators."""
+    also the quantised operands and the int32 accumulators.
+
+    accumulate: "exact" (default) dequantises the exact integer sum of the looked-up products; "reference"
+    reproduces the reference's fp32 running total added in K order (tf2/src/approx_nn_conv_kernels.cpp:245-246),
+    whose roundings show once a partial sum passes 2^24 - the output then has the reference's bits for every K."""
     return _forward(False, input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
-                    mul_map_file, padding, list(explicit_paddings), data_format, list(dilations), out, debug)
+                    mul_map_file, padding, list(explicit_paddings), data_format, list(dilations), out, debug, accumulate)
 
 
 def approx_depthwise_conv2d_with_min_max_vars(input, filter, input_min, input_max, filter_min, filter_max, strides,
