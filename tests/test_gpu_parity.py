@@ -363,6 +363,17 @@ DW_SHAPES = [
     (2, 8, 8, 5, 1, 1, 1, (1, 1), (1, 1), "SAME"),
     (1, 12, 12, 16, 5, 5, 1, (1, 1), (1, 1), "SAME"),
     (1, 12, 12, 16, 3, 3, 1, (1, 2), (1, 1), "SAME"),    # anisotropic stride -> generic kernel
+    # 1024 output pixels and more: the kernel with the per-channel-group expanded table
+    (2, 28, 28, 144, 3, 3, 1, (1, 1), (1, 1), "SAME"),   # 4.5 channel groups, 4 bands of 7 rows
+    (1, 56, 56, 40, 3, 3, 1, (1, 1), (1, 1), "SAME"),    # channel tail of 8
+    (2, 57, 55, 96, 3, 3, 1, (2, 2), (1, 1), "SAME"),    # stride 2, odd sizes: padding before and after
+    (1, 112, 112, 32, 3, 3, 1, (2, 2), (1, 1), "SAME"),  # stride 2, even sizes: padding after only
+    (1, 45, 47, 33, 3, 3, 1, (1, 1), (1, 1), "VALID"),   # 43 output rows: a band of one row at the bottom
+    (1, 80, 40, 7, 3, 3, 3, (2, 2), (1, 1), "VALID"),    # multiplier 3, stride 2
+    (3, 33, 35, 64, 3, 3, 1, (1, 1), (1, 1), "SAME"),
+    (1, 36, 36, 16, 3, 3, 2, (1, 1), (1, 1), "SAME"),    # multiplier 2
+    (8, 56, 56, 144, 3, 3, 1, (1, 1), (1, 1), "SAME"),   # 320 units on 148 CTAs: CTAs whose range crosses a channel group
+    (6, 56, 56, 96, 3, 3, 1, (2, 2), (1, 1), "SAME"),    # the same for stride 2
 ]
 
 

@@ -535,7 +535,10 @@ int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, con
     const int *gate = nullptr;
     const DevQuant *dq = reinterpret_cast<const DevQuant *>(plan + kDevQuantOffset);
 
-    rc = launch_quant(q, ranges_dev, g.K, plan, stream);
+    // the quantisation parameters reach the workspace with the first kernel of the plan check, or - without a
+    // plan - with a kernel of their own
+    if (scheduled) rc = launch_plan(lut_dev, table_uid, g, q, ranges_dev, filter, plan, L, dbg ? dbg->qfilter : nullptr, stream);
+    else rc = launch_quant(q, ranges_dev, g.K, plan, stream);
     if (rc) return rc;
     if (dbg && dbg->qinput) {
         const long long n = (long long)g.N * g.H * g.W * g.C;
@@ -547,8 +550,6 @@ int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, con
         }
     }
     if (scheduled) {
-        rc = launch_plan(lut_dev, table_uid, g, filter, plan, L, dbg ? dbg->qfilter : nullptr, stream);
-        if (rc) return rc;
         rc = launch_dense_sched(g, input, output, plan, L, dbg ? dbg->acc : nullptr, di, stream);
         if (rc) return rc;
         gate = &reinterpret_cast<const PlanHeader *>(plan)->fallback;

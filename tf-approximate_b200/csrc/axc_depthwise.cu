@@ -10,7 +10,9 @@
 // image row and keeps the 3x3 input window in registers, so an input element is read once
 // per output row it touches; the new window columns of four outputs are requested together.  The table lives in shared memory in the two-plane layout of
 // the dense kernel (plane p at 65536*(1+p), byte a*256 + 2*(b&127)).
+#include <cstdlib>
 #include <mutex>
+#include <type_traits>
 
 #include "axc_internal.h"
 
@@ -38,6 +40,12 @@ struct DwParams {
     int runs_per_row, groups;
     long long items;       // N*OH*runs_per_row*groups
     float in_off, in_inv, s1s2, m1, m2, km1m2;
+    // expanded-table kernel only
+    const float *filter;   // [9][OC] fp32
+    float f_off, f_inv;
+    int bands;             // bands of output rows per image
+    int units_per_group;   // N * bands
+    long long units_total; // groups * units_per_group
 };
 
 __device__ __forceinline__ unsigned dw_quantize_u8(float x, float off, float inv)
@@ -303,6 +311,310 @@ __global__ void __launch_bounds__(kDwThreads, 1) depthwise_3x3_kernel(const DwPa
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------------
+// 3x3 depthwise with a per-channel-group expanded table (stride 1 or 2, dilation 1).
+//
+// In the kernels above activation and weight both differ from lane to lane, so the bank of a lookup is random
+// (3.2 wavefronts per lookup measured).  A depthwise lane, however, only ever uses the nine table columns of its
+// own channel.  For a group of 32 channels the CTA therefore expands the table once into
+//     T16[a][lane] = the entries LUT[a][b(lane, tap)] of eight taps, 16 bytes,   T4[a][lane] = the centre tap,
+// (160 KiB of shared memory) and then looks an INPUT pixel up instead of an output tap: one LDS.128 plus one
+// LDS.32 return all nine products of the pixel, which are scattered to the nine outputs it contributes to.  The
+// address is a * 512 + lane * 16: the bank depends on the lane alone, so every quarter warp of the LDS.128 and the
+// whole LDS.32 are conflict-free - 5 wavefronts per 9 table MACs instead of 29.
+//
+// Work: the CTA owns a contiguous range of (channel group, image, band of R output rows) units; it rebuilds the
+// table when the range crosses into the next group.  A warp walks a band from left to right, lane = channel: per
+// input column it loads the (R-1)*S+3 rows of the column (one 128-byte line each), quantises, looks up and adds
+// the products into the accumulators of the (at most) three output columns in flight; a finished output column
+// gets its patch sum - the raw taps added in (ky, kx) order like the reference's im2col
+// (tf2/src/approx_nn_conv_kernels.cpp:272-295) - and is dequantised and stored.
+//
+// Packing of a T16 entry: x = {t00, t02}, y = {t20, t22}, z = {t01, t21}, w = {t10, t12} (low half first), so
+// that under stride 2 a pixel fetches only what its row and column parity can use (8, 4, 4 or 4 bytes).
+// ---------------------------------------------------------------------------------------------------
+constexpr unsigned kTab16Bytes = 256u * 32u * 16u;
+constexpr unsigned kTab4Bytes = 256u * 32u * 4u;
+constexpr unsigned kTabSmem = kTab16Bytes + kTab4Bytes + 512u;
+constexpr long long kTabMinOutputsPerGroup = 32768;
+
+__device__ __forceinline__ unsigned dw_q_u8(float x, float off, float inv)
+{
+    const float v = __fadd_rn(__fmul_rn(__fsub_rn(x, off), inv), 0.5f);
+    unsigned u;
+    asm("cvt.rzi.u8.f32 %0, %1;" : "=r"(u) : "f"(v));     // truncates and saturates to 0..255 (NaN -> 0)
+    return u;
+}
+
+// c + low / high 16-bit half of `a`.  DP: one two-way dot product with the byte vector {1,0} resp. {0,1}
+template <bool DP>
+__device__ __forceinline__ int dw_add_lo(unsigned a, int c)
+{
+    if (!DP) return c + int(a & 0xFFFFu);
+    int d;
+    asm("dp2a.lo.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(0x00000001u), "r"(c));
+    return d;
+}
+template <bool DP>
+__device__ __forceinline__ int dw_add_hi(unsigned a, int c)
+{
+    if (!DP) return c + int(a >> 16);
+    int d;
+    asm("dp2a.lo.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(0x00000100u), "r"(c));
+    return d;
+}
+
+template <int NT>
+__device__ __forceinline__ void dw_build_table(const DwParams &P, int g, unsigned tab16, unsigned tab4, int tid)
+{
+    constexpr int kTabWarps = NT / 32;
+    const int lane = tid & 31;
+    const int oc = g * 32 + lane;
+    unsigned b[9];
+#pragma unroll
+    for (int t = 0; t < 9; ++t) b[t] = oc < P.OC ? dw_q_u8(__ldg(P.filter + (size_t)t * P.OC + oc), P.f_off, P.f_inv) : 0u;
+#pragma unroll 4
+    for (int a = tid >> 5; a < 256; a += kTabWarps) {
+        const uint16_t *row = P.lut + a * 256;
+        unsigned t[9];
+#pragma unroll
+        for (int k = 0; k < 9; ++k) t[k] = __ldg(row + b[k]);
+        const unsigned d16 = tab16 + unsigned(a) * 512u + unsigned(lane) * 16u;
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(d16), "r"(t[0] | (t[2] << 16)), "r"(t[6] | (t[8] << 16)),
+                     "r"(t[1] | (t[7] << 16)), "r"(t[3] | (t[5] << 16)) : "memory");
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(tab4 + unsigned(a) * 128u + unsigned(lane) * 4u), "r"(t[4]) : "memory");
+    }
+}
+
+template <int S, int R, int NT, bool DP>
+__global__ void __launch_bounds__(NT, 1) depthwise_3x3_tab_kernel(const DwParams P)
+{
+    constexpr int IR = (R - 1) * S + 3;
+    constexpr int kTabWarps = NT / 32;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const unsigned dyn0 = (unsigned)__cvta_generic_to_shared(smem_raw);
+    unsigned dyn_size;
+    asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
+    const unsigned tab16 = (dyn0 + 511u) & ~511u;
+    const unsigned tab4 = tab16 + kTab16Bytes;
+    if (tab4 + kTab4Bytes > dyn0 + dyn_size) {
+        if (threadIdx.x == 0) atomicExch(P.status, 1);
+        return;
+    }
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const unsigned lane16 = tab16 + unsigned(lane) * 16u, lane4 = tab4 + unsigned(lane) * 4u;
+    const long long u_begin = P.units_total * blockIdx.x / gridDim.x;
+    const long long u_end = P.units_total * (blockIdx.x + 1) / gridDim.x;
+    const int row_elems = P.W * P.C;                       // elements per input row
+    const int orow_elems = P.OW * P.OC;
+
+    for (long long u = u_begin; u < u_end;) {
+        const int g = int(u / P.units_per_group);
+        const long long g_first = (long long)g * P.units_per_group;
+        const long long g_end = u_end < g_first + P.units_per_group ? u_end : g_first + P.units_per_group;
+        __syncthreads();                                    // every warp is done with the previous group's table
+        dw_build_table<NT>(P, g, tab16, tab4, tid);
+        __syncthreads();
+
+        const int oc = g * 32 + lane;
+        const bool oc_ok = oc < P.OC;
+        const int cin = oc_ok ? oc / P.mult : 0;
+        const float t2 = oc_ok ? __fmul_rn(P.m1, __ldg(P.bsum + oc)) : 0.0f;
+
+        for (long long v = u + warp; v < g_end; v += kTabWarps) {
+            const int w = int(v - g_first);
+            const int n = w / P.bands;
+            const int oy0 = (w - n * P.bands) * R;
+            const int rows_here = P.OH - oy0 < R ? P.OH - oy0 : R;
+            const float *in_n = P.input + (size_t)n * P.H * row_elems + cin;
+            const int out0 = (n * P.OH + oy0) * orow_elems + oc;          // output element (n, oy0, 0, oc)
+            unsigned rowok = 0;                                            // bit i: input row i lies inside the image
+            const int iy0 = oy0 * S - P.ph;
+#pragma unroll
+            for (int i = 0; i < IR; ++i) rowok |= (unsigned(iy0 + i) < unsigned(P.H) ? 1u : 0u) << i;
+            const int in0 = iy0 * row_elems - P.pw * P.C;                  // element offset of (iy0, column rel 0)
+
+            int acc[R][S == 1 ? 3 : 2];
+            float xf[IR][3];
+            float nx[IR];
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int q = 0; q < (S == 1 ? 3 : 2); ++q) acc[r][q] = 0;
+
+            // raw taps of input column `c` (relative: image column c - pw); zeros outside the image
+            auto fetch = [&](int c, float (&dst)[IR]) {
+                const bool colok = oc_ok && unsigned(c - P.pw) < unsigned(P.W);
+                const int off = in0 + c * P.C;
+#pragma unroll
+                for (int i = 0; i < IR; ++i)
+                    dst[i] = (colok && ((rowok >> i) & 1u)) ? __ldg(in_n + (off + i * row_elems)) : 0.0f;
+            };
+            // patch sum, dequantisation and store of output column ox, rows 0..R-1: raw columns in xf slots
+            // (k0, k1, k2) for kx = 0, 1, 2, accumulators in slot sa
+            auto emit = [&](int ox, auto k0c, auto k1c, auto k2c, auto sac) {
+                constexpr int k0 = decltype(k0c)::value, k1 = decltype(k1c)::value, k2 = decltype(k2c)::value;
+                constexpr int sa = decltype(sac)::value;
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    float a = 0.0f;
+#pragma unroll
+                    for (int ky = 0; ky < 3; ++ky) {
+                        a = __fadd_rn(a, xf[r * S + ky][k0]);
+                        a = __fadd_rn(a, xf[r * S + ky][k1]);
+                        a = __fadd_rn(a, xf[r * S + ky][k2]);
+                    }
+                    const int s = acc[r][sa];
+                    acc[r][sa] = 0;
+                    if (oc_ok && r < rows_here) {
+                        const int o = out0 + r * orow_elems + ox * P.OC;
+                        P.output[o] = dw_epilogue(s, a, t2, P);
+                        if (P.acc_out) P.acc_out[o] = s;
+                    }
+                }
+            };
+
+            if constexpr (S == 1) {
+                // input column c serves kx = 0 of output c, kx = 1 of output c - 1, kx = 2 of output c - 2
+                auto column = [&](int c, auto jc) {
+                    constexpr int J = decltype(jc)::value;            // c % 3
+                    constexpr int s0 = J, s1 = (J + 2) % 3, s2 = (J + 1) % 3;
+                    float cur[IR];
+#pragma unroll
+                    for (int i = 0; i < IR; ++i) cur[i] = nx[i];
+                    fetch(c + 1, nx);                                  // next column in flight while this one is used
+#pragma unroll
+                    for (int i = 0; i < IR; ++i) {
+                        xf[i][J] = cur[i];
+                        const unsigned qa = dw_q_u8(cur[i], P.in_off, P.in_inv);
+                        uint4 t;
+                        asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t.x), "=r"(t.y), "=r"(t.z), "=r"(t.w) : "r"(lane16 + qa * 512u));
+                        if (i < R) {                                   // ky = 0 -> output row i
+                            acc[i][s0] = dw_add_lo<DP>(t.x, acc[i][s0]);
+                            acc[i][s1] = dw_add_lo<DP>(t.z, acc[i][s1]);
+                            acc[i][s2] = dw_add_hi<DP>(t.x, acc[i][s2]);
+                        }
+                        if (i >= 1 && i - 1 < R) {                     // ky = 1 -> output row i - 1
+                            unsigned t11;
+                            asm("ld.shared.u32 %0, [%1];" : "=r"(t11) : "r"(lane4 + qa * 128u));
+                            acc[i - 1][s0] = dw_add_lo<DP>(t.w, acc[i - 1][s0]);
+                            acc[i - 1][s1] += int(t11);
+                            acc[i - 1][s2] = dw_add_hi<DP>(t.w, acc[i - 1][s2]);
+                        }
+                        if (i >= 2) {                                  // ky = 2 -> output row i - 2
+                            acc[i - 2][s0] = dw_add_lo<DP>(t.y, acc[i - 2][s0]);
+                            acc[i - 2][s1] = dw_add_hi<DP>(t.z, acc[i - 2][s1]);
+                            acc[i - 2][s2] = dw_add_hi<DP>(t.y, acc[i - 2][s2]);
+                        }
+                    }
+                    if (c >= 2) {
+                        emit(c - 2, std::integral_constant<int, s2>{}, std::integral_constant<int, s1>{},
+                             std::integral_constant<int, s0>{}, std::integral_constant<int, s2>{});
+                    } else {
+                        // columns 0 and 1 also feed the outputs -2 and -1, which do not exist: drop what they got
+#pragma unroll
+                        for (int r = 0; r < R; ++r) acc[r][s2] = 0;
+                    }
+                };
+                fetch(0, nx);
+                const int c_end = P.OW + 2;
+                for (int c = 0; c < c_end; c += 3) {
+                    column(c, std::integral_constant<int, 0>{});
+                    if (c + 1 < c_end) column(c + 1, std::integral_constant<int, 1>{});
+                    if (c + 2 < c_end) column(c + 2, std::integral_constant<int, 2>{});
+                }
+            } else {
+                // even input column 2m: kx = 0 of output m and kx = 2 of output m - 1; odd column 2m + 1: kx = 1 of
+                // output m.  Even input row 2r: ky = 0 of output row r and ky = 2 of row r - 1; odd row 2r + 1: ky = 1.
+                auto even_column = [&](int m, auto jc) {
+                    constexpr int J = decltype(jc)::value;            // m % 2
+                    float cur[IR];
+#pragma unroll
+                    for (int i = 0; i < IR; ++i) cur[i] = nx[i];
+                    fetch(2 * m + 1, nx);
+#pragma unroll
+                    for (int i = 0; i < IR; ++i) {
+                        xf[i][J] = cur[i];
+                        const unsigned qa = dw_q_u8(cur[i], P.in_off, P.in_inv);
+                        if ((i & 1) == 0) {
+                            unsigned tx, ty;
+                            asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(tx), "=r"(ty) : "r"(lane16 + qa * 512u));
+                            if (i / 2 < R) {
+                                acc[i / 2][J] = dw_add_lo<DP>(tx, acc[i / 2][J]);              // t00
+                                acc[i / 2][J ^ 1] = dw_add_hi<DP>(tx, acc[i / 2][J ^ 1]);      // t02
+                            }
+                            if (i >= 2) {
+                                acc[i / 2 - 1][J] = dw_add_lo<DP>(ty, acc[i / 2 - 1][J]);          // t20
+                                acc[i / 2 - 1][J ^ 1] = dw_add_hi<DP>(ty, acc[i / 2 - 1][J ^ 1]);  // t22
+                            }
+                        } else {
+                            unsigned tw;
+                            asm("ld.shared.u32 %0, [%1];" : "=r"(tw) : "r"(lane16 + qa * 512u + 12u));
+                            acc[i / 2][J] = dw_add_lo<DP>(tw, acc[i / 2][J]);                  // t10
+                            acc[i / 2][J ^ 1] = dw_add_hi<DP>(tw, acc[i / 2][J ^ 1]);          // t12
+                        }
+                    }
+                    if (m >= 1) {
+                        emit(m - 1, std::integral_constant<int, J ^ 1>{}, std::integral_constant<int, 2>{},
+                             std::integral_constant<int, J>{}, std::integral_constant<int, J ^ 1>{});
+                    } else {
+                        // column 0 also feeds output -1, which does not exist: drop what it got
+#pragma unroll
+                        for (int r = 0; r < R; ++r) acc[r][J ^ 1] = 0;
+                    }
+                };
+                auto odd_column = [&](int m, auto jc) {
+                    constexpr int J = decltype(jc)::value;
+                    float cur[IR];
+#pragma unroll
+                    for (int i = 0; i < IR; ++i) cur[i] = nx[i];
+                    fetch(2 * m + 2, nx);
+#pragma unroll
+                    for (int i = 0; i < IR; ++i) {
+                        xf[i][2] = cur[i];
+                        const unsigned qa = dw_q_u8(cur[i], P.in_off, P.in_inv);
+                        if ((i & 1) == 0) {
+                            unsigned tz;
+                            asm("ld.shared.u32 %0, [%1];" : "=r"(tz) : "r"(lane16 + qa * 512u + 8u));
+                            if (i / 2 < R) acc[i / 2][J] = dw_add_lo<DP>(tz, acc[i / 2][J]);           // t01
+                            if (i >= 2) acc[i / 2 - 1][J] = dw_add_hi<DP>(tz, acc[i / 2 - 1][J]);      // t21
+                        } else {
+                            unsigned t11;
+                            asm("ld.shared.u32 %0, [%1];" : "=r"(t11) : "r"(lane4 + qa * 128u));
+                            acc[i / 2][J] += int(t11);
+                        }
+                    }
+                };
+                fetch(0, nx);
+                for (int m = 0; m <= P.OW; m += 2) {
+                    even_column(m, std::integral_constant<int, 0>{});
+                    if (m < P.OW) odd_column(m, std::integral_constant<int, 0>{});
+                    if (m + 1 <= P.OW) {
+                        even_column(m + 1, std::integral_constant<int, 1>{});
+                        if (m + 1 < P.OW) odd_column(m + 1, std::integral_constant<int, 1>{});
+                    }
+                }
+            }
+        }
+        u = g_end;
+    }
+}
+
+template <int S, int R, int NT, bool DP>
+int launch_dw_tab(DwParams P, const DeviceInfo &di, cudaStream_t stream)
+{
+    P.bands = (P.OH + R - 1) / R;
+    P.units_per_group = P.N * P.bands;
+    P.units_total = (long long)P.groups * P.units_per_group;
+    AXC_CUDA(cudaFuncSetAttribute(depthwise_3x3_tab_kernel<S, R, NT, DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kTabSmem)));
+    const long long grid = P.units_total < di.sm_count ? P.units_total : di.sm_count;
+    depthwise_3x3_tab_kernel<S, R, NT, DP><<<unsigned(grid), NT, kTabSmem, stream>>>(P);
+    AXC_CUDA(cudaGetLastError());
+    count_launch();
+    return AXC_OK;
+}
+
 template <typename Kern>
 int launch_dw(Kern kern, const DwParams &P, const DeviceInfo &di, cudaStream_t stream)
 {
@@ -365,6 +677,32 @@ int launch_depthwise(const uint16_t *lut_dev, const Geom &g, const Quant &q, con
     }
     const bool small = (long long)g.N * g.H * g.W * g.C < (1ll << 31) && g.M * OC < (1ll << 31) && P.items < (1ll << 31);
     const bool k3 = small && g.KH == 3 && g.KW == 3 && g.dh == 1 && g.dw == 1 && g.sh == g.sw;
+    P.filter = filter; P.f_off = q.f_off; P.f_inv = q.f_inv;
+    P.bands = 0; P.units_per_group = 0; P.units_total = 0;
+    // The expanded-table kernel pays about 74 000 lookups per CTA and channel group for its table: worth it from
+    // some ten thousand outputs per group on.
+    if (k3 && (g.sw == 1 || g.sw == 2) && g.M * 32 >= kTabMinOutputsPerGroup && di.max_smem_optin >= int(kTabSmem)) {
+        static const int variant = getenv("AXC_DW_TAB_VARIANT") ? atoi(getenv("AXC_DW_TAB_VARIANT")) : 0;   // tuning only
+        if (variant >= 0) {
+            if (g.sw == 1) {
+                switch (variant) {
+                case 1: return launch_dw_tab<1, 7, 512, false>(P, di, stream);
+                case 2: return launch_dw_tab<1, 7, 384, true>(P, di, stream);
+                case 3: return launch_dw_tab<1, 4, 512, true>(P, di, stream);
+                case 4: return launch_dw_tab<1, 4, 768, true>(P, di, stream);
+                case 5: return launch_dw_tab<1, 6, 512, true>(P, di, stream);
+                default: return launch_dw_tab<1, 7, 512, true>(P, di, stream);
+                }
+            }
+            switch (variant) {
+            case 1: return launch_dw_tab<2, 4, 512, false>(P, di, stream);
+            case 2: return launch_dw_tab<2, 4, 384, true>(P, di, stream);
+            case 3: return launch_dw_tab<2, 3, 512, true>(P, di, stream);
+            case 4: return launch_dw_tab<2, 2, 768, true>(P, di, stream);
+            default: return launch_dw_tab<2, 4, 512, true>(P, di, stream);
+            }
+        }
+    }
     if (k3 && g.sw == 1) return launch_dw(depthwise_3x3_kernel<1>, P, di, stream);
     if (k3 && g.sw == 2) return launch_dw(depthwise_3x3_kernel<2>, P, di, stream);
     return launch_dw(depthwise_generic_kernel, P, di, stream);

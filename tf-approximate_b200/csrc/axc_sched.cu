@@ -36,6 +36,7 @@ constexpr int kComputeWarps = 8;
 constexpr int kTilePix = 16;
 constexpr int kTapTableMax = 512;
 constexpr int kStepsInSmemMax = 1024;
+constexpr uint32_t kPlanMagic = 0x41584334u;   // "AXC4"
 
 __device__ __forceinline__ unsigned q_u8(float x, float off, float inv)
 {
@@ -96,29 +97,100 @@ __device__ __forceinline__ unsigned lds32(unsigned addr)
 __device__ __forceinline__ int slot_bank(int s) { return ((s & 127) >> 1) & 31; }
 
 // ------------------------------------------------------------------------------------------------
-// plan_check: quantised filter vs. stored copy
+// plan_check: quantisation parameters of the call, quantised filter vs. stored copy, structure of the stored plan
 // ------------------------------------------------------------------------------------------------
-__global__ void plan_check_kernel(const float *__restrict__ filter, long long count, const DevQuant *__restrict__ dq,
-                                  uint8_t *__restrict__ qf, uint8_t *__restrict__ qf_debug, PlanHeader *hdr,
-                                  PlanHeader want)
+// Range nudging on the device, operation by operation as on the host (axc_api.cu var_quant_props).
+__device__ void dev_var_quant(float min_v, float max_v, float *scale, float *inv, float *offset)
 {
+    float s = 0.0f, i = 0.0f, nudged_min = 0.0f;
+    if (min_v != 0.0f || max_v != 0.0f) {
+        s = __fdiv_rn(__fsub_rn(max_v, min_v), 255.0f);
+        const float zp_from_min = __fsub_rn(0.0f, __fdiv_rn(min_v, s));
+        float zp;
+        if (zp_from_min < 0.0f) zp = 0.0f;
+        else if (zp_from_min > 255.0f) zp = 255.0f;
+        else zp = roundf(zp_from_min);                       // half away from zero, like std::round
+        nudged_min = __fmul_rn(__fsub_rn(0.0f, zp), s);      // a true subtraction: +0.0 for zp == 0
+        i = __fdiv_rn(1.0f, s);
+    }
+    *scale = s; *inv = i; *offset = nudged_min;
+}
+
+__device__ DevQuant dev_quant_from_ranges(const float *__restrict__ ranges, int K)
+{
+    float s1, i1, o1, s2, i2, o2;
+    dev_var_quant(ranges[0], ranges[1], &s1, &i1, &o1);
+    dev_var_quant(ranges[2], ranges[3], &s2, &i2, &o2);
+    DevQuant q;
+    q.in_off = o1; q.in_inv = i1; q.f_off = o2; q.f_inv = i2;
+    q.s1s2 = __fmul_rn(s1, s2); q.m1 = o1; q.m2 = o2;
+    q.km1m2 = __fmul_rn(float(K), __fmul_rn(o1, o2));
+    return q;
+}
+
+// A program word is safe to execute when the shared-memory addresses the kernel forms from it stay inside the
+// table planes, the zero words and the activation buffers, and are aligned: plane byte 1 or 2 with an even column
+// byte, or the idle form (plane byte 3, bit 14 set, column byte a multiple of 4 below 128); activation row offset a
+// multiple of 16 and at most 16 * (KC + 7).
+__device__ __forceinline__ bool prog_word_ok(uint32_t w, int KC)
+{
+    const unsigned col = w & 0xFFu, plane = (w >> 16) & 0xFFu, idle = (w >> 14) & 1u;
+    const unsigned rowoff = (w >> 24) | (w & 0x3F00u);
+    const bool lookup_ok = idle ? (plane == 3u && (col & 3u) == 0u && col < 128u) : ((plane == 1u || plane == 2u) && (col & 1u) == 0u);
+    return lookup_ok && (w & 0x8000u) == 0u && (rowoff & 15u) == 0u && rowoff <= 16u * unsigned(KC + 7);
+}
+
+// Every call: (1) block 0 writes the quantisation parameters of the call into the workspace - `host_q`, or derived
+// from the four range scalars in device memory; (2) the filter is quantised and compared with the stored copy;
+// (3) the stored plan is checked structurally - header, step counts within their reserve, every program word that
+// the convolution would execute (prog_word_ok) - so that a buffer whose tail was overwritten by someone else can
+// give wrong numbers at worst, never an access outside shared memory or the workspace: it is rebuilt instead.
+// A plan found wanting gets `dirty` and loses its magic word until plan_build has finished the new one.
+__global__ void plan_check_kernel(const float *__restrict__ filter, long long count, DevQuant host_q,
+                                  const float *__restrict__ ranges, int K, unsigned char *__restrict__ plan, PlanLayout L,
+                                  uint8_t *__restrict__ qf_debug, PlanHeader want)
+{
+    PlanHeader *hdr = reinterpret_cast<PlanHeader *>(plan);
+    uint8_t *qf = plan + L.qf_off;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const float f_off = dq->f_off, f_inv = dq->f_inv;
+    const long long nthreads = (long long)gridDim.x * blockDim.x;
+    const DevQuant q = ranges ? dev_quant_from_ranges(ranges, K) : host_q;
+    const float f_off = q.f_off, f_inv = q.f_inv;
+    bool bad = false;
     if (idx == 0) {
-        const bool same = hdr->magic == want.magic && hdr->K == want.K && hdr->Cout == want.Cout && hdr->G == want.G &&
-                          hdr->NCH == want.NCH && hdr->KC == want.KC && hdr->sqcap == want.sqcap &&
-                          hdr->table_uid == want.table_uid && hdr->f_off_bits == __float_as_uint(f_off) &&
-                          hdr->f_inv_bits == __float_as_uint(f_inv);
-        if (!same) atomicOr(&hdr->dirty, 1);
+        *reinterpret_cast<DevQuant *>(plan + kDevQuantOffset) = q;
+        bad = !(hdr->magic == want.magic && hdr->K == want.K && hdr->Cout == want.Cout && hdr->G == want.G &&
+                hdr->NCH == want.NCH && hdr->KC == want.KC && hdr->sqcap == want.sqcap &&
+                hdr->table_uid == want.table_uid && hdr->f_off_bits == __float_as_uint(f_off) &&
+                hdr->f_inv_bits == __float_as_uint(f_inv));
         hdr->status = 0;
     }
-    if (idx >= count) return;
-    const unsigned b = q_u8(filter[idx], f_off, f_inv);
-    if (qf[idx] != b) {
-        qf[idx] = uint8_t(b);
+    if (idx < count) {
+        const unsigned b = q_u8(filter[idx], f_off, f_inv);
+        if (qf[idx] != b) {
+            qf[idx] = uint8_t(b);
+            bad = true;
+        }
+        if (qf_debug) qf_debug[idx] = uint8_t(b);
+    }
+    // structure of the stored plan
+    const int n_sched = L.G * L.NCH;
+    const int *steps = reinterpret_cast<const int *>(plan + L.steps_off);
+    for (long long e = idx; e < n_sched; e += nthreads) bad |= unsigned(steps[e]) > unsigned(L.sqcap);
+    const uint4 *prog = reinterpret_cast<const uint4 *>(plan + L.prog_off);
+    const long long quads = (long long)n_sched * L.sqcap * 32;
+    for (long long e = idx; e < quads; e += nthreads) {
+        const long long row = e >> 5;
+        const int sc = int(row / L.sqcap), qi = int(row - (long long)sc * L.sqcap);
+        if (unsigned(qi) < unsigned(steps[sc])) {
+            const uint4 w = prog[e];
+            bad |= !(prog_word_ok(w.x, L.KC) && prog_word_ok(w.y, L.KC) && prog_word_ok(w.z, L.KC) && prog_word_ok(w.w, L.KC));
+        }
+    }
+    if (bad) {
+        hdr->magic = 0;
         atomicOr(&hdr->dirty, 1);
     }
-    if (qf_debug) qf_debug[idx] = uint8_t(b);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -139,6 +211,7 @@ __global__ void __launch_bounds__(256) plan_sigma_kernel(const uint8_t *__restri
                                                          PlanHeader want, const DevQuant *__restrict__ dq)
 {
     if (hdr->dirty == 0) return;
+    if (threadIdx.x == 0) hdr->blocks_done = 0;
     extern __shared__ __align__(16) unsigned sigma_smem[];
     __shared__ unsigned hist[256];
     __shared__ int value_at_rank[256];
@@ -313,7 +386,8 @@ __global__ void __launch_bounds__(256) plan_sigma_kernel(const uint8_t *__restri
         sigma[t] = uint8_t(slot);
     }
     if (t == 0) {
-        hdr->magic = want.magic; hdr->K = want.K; hdr->Cout = want.Cout; hdr->G = want.G; hdr->NCH = want.NCH;
+        // the magic word is written by the last block of plan_build: a plan is valid only once it is complete
+        hdr->K = want.K; hdr->Cout = want.Cout; hdr->G = want.G; hdr->NCH = want.NCH;
         hdr->KC = want.KC; hdr->sqcap = want.sqcap; hdr->table_uid = want.table_uid;
         hdr->f_off_bits = __float_as_uint(dq->f_off); hdr->f_inv_bits = __float_as_uint(dq->f_inv);
         hdr->fallback = 0;
@@ -347,6 +421,17 @@ __global__ void __launch_bounds__(32) plan_build_kernel(const float *__restrict_
     const uint8_t *sigma = plan + L.sigma_off;
     const int lane = threadIdx.x;
     const int n_sched = L.G * L.NCH;
+    // the block that finishes last seals the plan
+    auto block_done = [&]() {
+        __syncwarp();
+        if (lane == 0) {
+            __threadfence();
+            if (atomicAdd(&hdr->blocks_done, 1) == int(gridDim.x) - 1) {
+                __threadfence();
+                hdr->magic = kPlanMagic;
+            }
+        }
+    };
 
     if (int(blockIdx.x) >= n_sched) {
         const int rest = int(blockIdx.x) - n_sched;
@@ -375,6 +460,7 @@ __global__ void __launch_bounds__(32) plan_build_kernel(const float *__restrict_
                 reinterpret_cast<float *>(plan + L.bsum_off)[j] = acc;
             }
         }
+        block_done();
         return;
     }
 
@@ -598,6 +684,7 @@ __global__ void __launch_bounds__(32) plan_build_kernel(const float *__restrict_
         reinterpret_cast<int *>(plan + L.steps_off)[blockIdx.x] = (step + 3) >> 2;
         if (overflow) atomicOr(&hdr->fallback, 1);
     }
+    block_done();
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -909,7 +996,8 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
         *pp = prog;
         if (gi < P.g_count) {
             const int sc = (P.g_base + gi) * NCH + c;
-            *nq = steps_in_smem ? int(lds32(sSteps + unsigned(sc) * 4u)) : __ldg(steps_q + sc);
+            const int stored = steps_in_smem ? int(lds32(sSteps + unsigned(sc) * 4u)) : __ldg(steps_q + sc);
+            *nq = min(max(stored, 0), P.L.sqcap);          // never walk beyond the block's reserve
             *pp = prog + (size_t)sc * P.L.sqcap * 32 + lane;
         }
     };
@@ -1091,68 +1179,44 @@ PlanLayout plan_layout(int K, int Cout)
     return L;
 }
 
-// Range nudging on the device, operation by operation as on the host (axc_api.cu var_quant_props).
-__device__ void dev_var_quant(float min_v, float max_v, float *scale, float *inv, float *offset)
+static DevQuant host_dev_quant(const Quant &q, int K)
 {
-    float s = 0.0f, i = 0.0f, nudged_min = 0.0f;
-    if (min_v != 0.0f || max_v != 0.0f) {
-        s = __fdiv_rn(__fsub_rn(max_v, min_v), 255.0f);
-        const float zp_from_min = __fsub_rn(0.0f, __fdiv_rn(min_v, s));
-        float zp;
-        if (zp_from_min < 0.0f) zp = 0.0f;
-        else if (zp_from_min > 255.0f) zp = 255.0f;
-        else zp = roundf(zp_from_min);                       // half away from zero, like std::round
-        nudged_min = __fmul_rn(__fsub_rn(0.0f, zp), s);      // a true subtraction: +0.0 for zp == 0
-        i = __fdiv_rn(1.0f, s);
-    }
-    *scale = s; *inv = i; *offset = nudged_min;
+    DevQuant d;
+    d.in_off = q.in_off; d.in_inv = q.in_inv; d.f_off = q.f_off; d.f_inv = q.f_inv;
+    d.s1s2 = q.s1s2; d.m1 = q.m1; d.m2 = q.m2;
+    volatile float kf = float(K);
+    volatile float t3 = kf * q.m1m2;
+    d.km1m2 = t3;
+    return d;
 }
 
-__global__ void quant_from_ranges_kernel(const float *__restrict__ ranges, int K, DevQuant *out)
+__global__ void quant_store_kernel(DevQuant host_q, const float *__restrict__ ranges, int K, DevQuant *out)
 {
-    float s1, i1, o1, s2, i2, o2;
-    dev_var_quant(ranges[0], ranges[1], &s1, &i1, &o1);
-    dev_var_quant(ranges[2], ranges[3], &s2, &i2, &o2);
-    DevQuant q;
-    q.in_off = o1; q.in_inv = i1; q.f_off = o2; q.f_inv = i2;
-    q.s1s2 = __fmul_rn(s1, s2); q.m1 = o1; q.m2 = o2;
-    q.km1m2 = __fmul_rn(float(K), __fmul_rn(o1, o2));
-    *out = q;
+    *out = ranges ? dev_quant_from_ranges(ranges, K) : host_q;
 }
 
-__global__ void quant_store_kernel(DevQuant q, DevQuant *out) { *out = q; }
-
+// For calls that do not go through launch_plan (common-K kernel only).
 int launch_quant(const Quant &q, const float *ranges_dev, int K, unsigned char *plan, cudaStream_t stream)
 {
-    DevQuant *dst = reinterpret_cast<DevQuant *>(plan + kDevQuantOffset);
-    if (ranges_dev) {
-        quant_from_ranges_kernel<<<1, 1, 0, stream>>>(ranges_dev, K, dst);
-    } else {
-        DevQuant d;
-        d.in_off = q.in_off; d.in_inv = q.in_inv; d.f_off = q.f_off; d.f_inv = q.f_inv;
-        d.s1s2 = q.s1s2; d.m1 = q.m1; d.m2 = q.m2;
-        volatile float kf = float(K);
-        volatile float t3 = kf * q.m1m2;
-        d.km1m2 = t3;
-        quant_store_kernel<<<1, 1, 0, stream>>>(d, dst);
-    }
+    quant_store_kernel<<<1, 1, 0, stream>>>(host_dev_quant(q, K), ranges_dev, K, reinterpret_cast<DevQuant *>(plan + kDevQuantOffset));
     AXC_CUDA(cudaGetLastError());
     count_launch();
     return AXC_OK;
 }
 
-int launch_plan(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const float *filter,
-                unsigned char *plan, const PlanLayout &L, uint8_t *qf_debug, cudaStream_t stream)
+int launch_plan(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const Quant &q, const float *ranges_dev,
+                const float *filter, unsigned char *plan, const PlanLayout &L, uint8_t *qf_debug, cudaStream_t stream)
 {
     PlanHeader want = {};
-    want.magic = 0x41584333u;  // "AXC3"
+    want.magic = kPlanMagic;
     want.K = g.K; want.Cout = g.Cout; want.G = L.G; want.NCH = L.NCH; want.KC = L.KC; want.sqcap = L.sqcap;
     want.table_uid = table_uid;
     PlanHeader *hdr = reinterpret_cast<PlanHeader *>(plan);
     AXC_CUDA(cudaMemsetAsync(&hdr->dirty, 0, sizeof(int), stream));
     const long long count = (long long)g.K * g.Cout;
     const DevQuant *dq = reinterpret_cast<const DevQuant *>(plan + kDevQuantOffset);
-    plan_check_kernel<<<unsigned((count + 255) / 256), 256, 0, stream>>>(filter, count, dq, plan + L.qf_off, qf_debug, hdr, want);
+    plan_check_kernel<<<unsigned((count + 255) / 256), 256, 0, stream>>>(filter, count, host_dev_quant(q, g.K), ranges_dev, g.K, plan, L,
+                                                                         qf_debug, want);
     AXC_CUDA(cudaGetLastError());
     {
         // the local search of plan_sigma_kernel needs 640 bytes of shared memory per schedule block
@@ -1271,7 +1335,7 @@ int plan_info(const void *workspace, int32_t out4[4], cudaStream_t stream)
     PlanHeader h;
     AXC_CUDA(cudaMemcpy(&h, workspace, sizeof(h), cudaMemcpyDeviceToHost));
     out4[0] = h.dirty; out4[1] = h.fallback; out4[2] = h.status; out4[3] = 0;
-    if (h.magic == 0x41584333u && h.G > 0 && h.NCH > 0 && h.G * h.NCH <= 65536) {
+    if (h.magic == kPlanMagic && h.G > 0 && h.NCH > 0 && h.G * h.NCH <= 65536) {
         const PlanLayout L = plan_layout(h.K, h.Cout);
         std::vector<int> steps(size_t(h.G) * h.NCH);
         AXC_CUDA(cudaMemcpy(steps.data(), static_cast<const unsigned char *>(workspace) + L.steps_off,

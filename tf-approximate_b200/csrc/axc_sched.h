@@ -22,7 +22,8 @@ struct PlanHeader {
     int dirty;      // set by plan_check when the stored plan does not belong to this filter / table
     int fallback;   // set when a schedule did not fit: the common-K kernel serves the call
     int status;     // 0 fine; 2 shared-memory layout check failed
-    int pad[3];
+    int blocks_done;   // plan_build blocks that have finished: the last one writes `magic`
+    int pad[2];
 };
 
 // Quantisation parameters of a call as the kernels read them.  Filled from host values, or on the device from
@@ -51,10 +52,11 @@ __host__ __device__ inline bool plan_group_dual(int g, int G, int Cout, int K)
 
 // Writes the DevQuant block of `plan`: from the host values `q`, or - when ranges_dev is given - on the device
 // from {in_min, in_max, f_min, f_max} read there (same arithmetic as the host: tf2/src/approx_ops_types.h:29-49,135-197).
+// launch_plan does the same as part of its first kernel; launch_quant is for calls that skip the plan.
 int launch_quant(const Quant &q, const float *ranges_dev, int K, unsigned char *plan, cudaStream_t stream);
 
-int launch_plan(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const float *filter,
-                unsigned char *plan, const PlanLayout &L, uint8_t *qf_debug, cudaStream_t stream);
+int launch_plan(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const Quant &q, const float *ranges_dev,
+                const float *filter, unsigned char *plan, const PlanLayout &L, uint8_t *qf_debug, cudaStream_t stream);
 
 int launch_dense_sched(const Geom &g, const float *input, float *output,
                        const unsigned char *plan, const PlanLayout &L, int32_t *acc_out, const DeviceInfo &di,
