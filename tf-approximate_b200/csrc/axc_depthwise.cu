@@ -45,7 +45,7 @@ struct DwParams {
     float f_off, f_inv;
     int bands;             // bands of output rows per image
     int units_per_group;   // N * bands
-    long long units_total; // groups * units_per_group
+    int wave, sets;        // CTAs per set (= channel groups served at a time) and sets: grid = wave * sets
 };
 
 __device__ __forceinline__ unsigned dw_quantize_u8(float x, float off, float inv)
@@ -387,7 +387,15 @@ __device__ __forceinline__ void dw_build_table(const DwParams &P, int g, unsigne
     }
 }
 
-template <int S, int R, int NT, bool DP>
+// base + a * b for an unsigned 32-bit a * b and a 64-bit base: one instruction (IMAD.WIDE)
+__device__ __forceinline__ const char *dw_ptr_mad(const char *base, unsigned a, unsigned b)
+{
+    unsigned long long r;
+    asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(r) : "r"(a), "r"(b), "l"((unsigned long long)base));
+    return reinterpret_cast<const char *>(r);
+}
+
+template <int S, int R, int NT, bool DP, bool DBG>
 __global__ void __launch_bounds__(NT, 1) depthwise_3x3_tab_kernel(const DwParams P)
 {
     constexpr int IR = (R - 1) * S + 3;
@@ -404,15 +412,18 @@ __global__ void __launch_bounds__(NT, 1) depthwise_3x3_tab_kernel(const DwParams
     }
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const unsigned lane16 = tab16 + unsigned(lane) * 16u, lane4 = tab4 + unsigned(lane) * 4u;
-    const long long u_begin = P.units_total * blockIdx.x / gridDim.x;
-    const long long u_end = P.units_total * (blockIdx.x + 1) / gridDim.x;
-    const int row_elems = P.W * P.C;                       // elements per input row
-    const int orow_elems = P.OW * P.OC;
+    // CTAs work in sets of `wave` = min(groups, CTAs) members: the members of a set take different channel groups of
+    // the same range of bands at the same time, so that the 128-byte pieces of a pixel that the groups read lie
+    // close together in time as well as in memory.  With more groups than CTAs a member takes several groups in turn.
+    const int wave = P.wave, set = int(blockIdx.x) / wave, slot = int(blockIdx.x) - set * wave;
+    const int w_begin = int((long long)P.units_per_group * set / P.sets);
+    const int w_end = int((long long)P.units_per_group * (set + 1) / P.sets);
+    const unsigned row_bytes = unsigned(P.W) * unsigned(P.C) * 4u;        // the launcher keeps IR rows below 2^32 bytes
+    const unsigned orow_bytes = unsigned(P.OW) * unsigned(P.OC) * 4u;
+    const unsigned pix_bytes = unsigned(P.C) * 4u, opix_bytes = unsigned(P.OC) * 4u;
+    const float in_off = P.in_off, in_inv = P.in_inv;
 
-    for (long long u = u_begin; u < u_end;) {
-        const int g = int(u / P.units_per_group);
-        const long long g_first = (long long)g * P.units_per_group;
-        const long long g_end = u_end < g_first + P.units_per_group ? u_end : g_first + P.units_per_group;
+    for (int g = slot; g < P.groups; g += wave) {
         __syncthreads();                                    // every warp is done with the previous group's table
         dw_build_table<NT>(P, g, tab16, tab4, tid);
         __syncthreads();
@@ -422,40 +433,48 @@ __global__ void __launch_bounds__(NT, 1) depthwise_3x3_tab_kernel(const DwParams
         const int cin = oc_ok ? oc / P.mult : 0;
         const float t2 = oc_ok ? __fmul_rn(P.m1, __ldg(P.bsum + oc)) : 0.0f;
 
-        for (long long v = u + warp; v < g_end; v += kTabWarps) {
-            const int w = int(v - g_first);
+        for (int w = w_begin + warp; w < w_end; w += kTabWarps) {
             const int n = w / P.bands;
             const int oy0 = (w - n * P.bands) * R;
-            const int rows_here = P.OH - oy0 < R ? P.OH - oy0 : R;
-            const float *in_n = P.input + (size_t)n * P.H * row_elems + cin;
-            const int out0 = (n * P.OH + oy0) * orow_elems + oc;          // output element (n, oy0, 0, oc)
-            unsigned rowok = 0;                                            // bit i: input row i lies inside the image
+            const int rows_here = oc_ok ? (P.OH - oy0 < R ? P.OH - oy0 : R) : 0;      // rows this lane stores
             const int iy0 = oy0 * S - P.ph;
-#pragma unroll
-            for (int i = 0; i < IR; ++i) rowok |= (unsigned(iy0 + i) < unsigned(P.H) ? 1u : 0u) << i;
-            const int in0 = iy0 * row_elems - P.pw * P.C;                  // element offset of (iy0, column rel 0)
+            // input rows lo <= i < hi of the band lie inside the image (lo is 0 or 1)
+            const int lo = iy0 < 0 ? -iy0 : 0;
+            const int hi = P.H - iy0 < IR ? P.H - iy0 : IR;
+            // byte pointers: input element (n, iy0, image column -pw, cin); output element (n, oy0, 0, oc)
+            const char *in0 = reinterpret_cast<const char *>(P.input + ((long long)n * P.H + iy0) * (long long)(P.W * P.C) -
+                                                             (long long)P.pw * P.C + cin);
+            const long long o0 = ((long long)n * P.OH + oy0) * (long long)(P.OW * P.OC) + (oc_ok ? oc : 0);
+            const char *out0 = reinterpret_cast<const char *>(P.output + o0);
+            const char *acc0 = DBG ? reinterpret_cast<const char *>(P.acc_out + o0) : nullptr;
 
             int acc[R][S == 1 ? 3 : 2];
-            float xf[IR][3];
-            float nx[IR];
-#pragma unroll
-            for (int r = 0; r < R; ++r)
-#pragma unroll
-                for (int q = 0; q < (S == 1 ? 3 : 2); ++q) acc[r][q] = 0;
+            float xf[IR][3];      // raw taps of the columns in flight: S == 1 ring slot = column % 3; S == 2: 0 / 1 = even
+                                  // columns (m % 2), 2 = odd column
+            float nx[IR];         // raw taps of the column being fetched
 
             // raw taps of input column `c` (relative: image column c - pw); zeros outside the image
-            auto fetch = [&](int c, float (&dst)[IR]) {
-                const bool colok = oc_ok && unsigned(c - P.pw) < unsigned(P.W);
-                const int off = in0 + c * P.C;
+            auto fetch = [&](int c) {
+                if (unsigned(c - P.pw) < unsigned(P.W)) {          // the same for all lanes
+                    const char *colp = dw_ptr_mad(in0, unsigned(c), pix_bytes);
 #pragma unroll
-                for (int i = 0; i < IR; ++i)
-                    dst[i] = (colok && ((rowok >> i) & 1u)) ? __ldg(in_n + (off + i * row_elems)) : 0.0f;
+                    for (int i = 0; i < IR; ++i) {
+                        float x = 0.0f;
+                        if (i >= lo && i < hi) x = __ldg(reinterpret_cast<const float *>(dw_ptr_mad(colp, unsigned(i), row_bytes)));
+                        nx[i] = x;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < IR; ++i) nx[i] = 0.0f;
+                }
             };
             // patch sum, dequantisation and store of output column ox, rows 0..R-1: raw columns in xf slots
-            // (k0, k1, k2) for kx = 0, 1, 2, accumulators in slot sa
+            // (k0, k1, k2) for kx = 0, 1, 2, integer sums in slot sa
             auto emit = [&](int ox, auto k0c, auto k1c, auto k2c, auto sac) {
                 constexpr int k0 = decltype(k0c)::value, k1 = decltype(k1c)::value, k2 = decltype(k2c)::value;
                 constexpr int sa = decltype(sac)::value;
+                const char *outp = dw_ptr_mad(out0, unsigned(ox), opix_bytes);
+                const char *accp = DBG ? dw_ptr_mad(acc0, unsigned(ox), opix_bytes) : nullptr;
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
                     float a = 0.0f;
@@ -465,33 +484,34 @@ __global__ void __launch_bounds__(NT, 1) depthwise_3x3_tab_kernel(const DwParams
                         a = __fadd_rn(a, xf[r * S + ky][k1]);
                         a = __fadd_rn(a, xf[r * S + ky][k2]);
                     }
-                    const int s = acc[r][sa];
-                    acc[r][sa] = 0;
-                    if (oc_ok && r < rows_here) {
-                        const int o = out0 + r * orow_elems + ox * P.OC;
-                        P.output[o] = dw_epilogue(s, a, t2, P);
-                        if (P.acc_out) P.acc_out[o] = s;
+                    const float y = dw_epilogue(acc[r][sa], a, t2, P);
+                    if (r < rows_here) {
+                        asm volatile("st.global.f32 [%0], %1;" ::"l"(dw_ptr_mad(outp, unsigned(r), orow_bytes)), "f"(y) : "memory");
+                        if (DBG) asm volatile("st.global.s32 [%0], %1;" ::"l"(dw_ptr_mad(accp, unsigned(r), orow_bytes)), "r"(acc[r][sa]) : "memory");
                     }
                 }
             };
+            using I0 = std::integral_constant<int, 0>;
+            using I1 = std::integral_constant<int, 1>;
+            using I2 = std::integral_constant<int, 2>;
 
             if constexpr (S == 1) {
-                // input column c serves kx = 0 of output c, kx = 1 of output c - 1, kx = 2 of output c - 2
+                // Input column c serves kx = 0 of output c, kx = 1 of output c - 1, kx = 2 of output c - 2.  The first
+                // product an output receives (ky = 0, kx = 0) initialises its sum, so no slot is ever cleared; what
+                // columns 0 and 1 add to the slots of the non-existent outputs -2 and -1 is overwritten that way.
                 auto column = [&](int c, auto jc) {
                     constexpr int J = decltype(jc)::value;            // c % 3
                     constexpr int s0 = J, s1 = (J + 2) % 3, s2 = (J + 1) % 3;
-                    float cur[IR];
 #pragma unroll
-                    for (int i = 0; i < IR; ++i) cur[i] = nx[i];
-                    fetch(c + 1, nx);                                  // next column in flight while this one is used
+                    for (int i = 0; i < IR; ++i) xf[i][J] = nx[i];
+                    fetch(c + 1);                                      // next column in flight while this one is used
 #pragma unroll
                     for (int i = 0; i < IR; ++i) {
-                        xf[i][J] = cur[i];
-                        const unsigned qa = dw_q_u8(cur[i], P.in_off, P.in_inv);
+                        const unsigned qa = dw_q_u8(xf[i][J], in_off, in_inv);
                         uint4 t;
                         asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t.x), "=r"(t.y), "=r"(t.z), "=r"(t.w) : "r"(lane16 + qa * 512u));
                         if (i < R) {                                   // ky = 0 -> output row i
-                            acc[i][s0] = dw_add_lo<DP>(t.x, acc[i][s0]);
+                            acc[i][s0] = dw_add_lo<DP>(t.x, 0);
                             acc[i][s1] = dw_add_lo<DP>(t.z, acc[i][s1]);
                             acc[i][s2] = dw_add_hi<DP>(t.x, acc[i][s2]);
                         }
@@ -508,72 +528,58 @@ __global__ void __launch_bounds__(NT, 1) depthwise_3x3_tab_kernel(const DwParams
                             acc[i - 2][s2] = dw_add_hi<DP>(t.y, acc[i - 2][s2]);
                         }
                     }
-                    if (c >= 2) {
-                        emit(c - 2, std::integral_constant<int, s2>{}, std::integral_constant<int, s1>{},
-                             std::integral_constant<int, s0>{}, std::integral_constant<int, s2>{});
-                    } else {
-                        // columns 0 and 1 also feed the outputs -2 and -1, which do not exist: drop what they got
-#pragma unroll
-                        for (int r = 0; r < R; ++r) acc[r][s2] = 0;
-                    }
+                    if (c >= 2) emit(c - 2, std::integral_constant<int, s2>{}, std::integral_constant<int, s1>{},
+                                     std::integral_constant<int, s0>{}, std::integral_constant<int, s2>{});
                 };
-                fetch(0, nx);
+#pragma unroll
+                for (int r = 0; r < R; ++r) { acc[r][1] = 0; acc[r][2] = 0; }
+                fetch(0);
                 const int c_end = P.OW + 2;
                 for (int c = 0; c < c_end; c += 3) {
-                    column(c, std::integral_constant<int, 0>{});
-                    if (c + 1 < c_end) column(c + 1, std::integral_constant<int, 1>{});
-                    if (c + 2 < c_end) column(c + 2, std::integral_constant<int, 2>{});
+                    column(c, I0{});
+                    if (c + 1 < c_end) column(c + 1, I1{});
+                    if (c + 2 < c_end) column(c + 2, I2{});
                 }
             } else {
                 // even input column 2m: kx = 0 of output m and kx = 2 of output m - 1; odd column 2m + 1: kx = 1 of
                 // output m.  Even input row 2r: ky = 0 of output row r and ky = 2 of row r - 1; odd row 2r + 1: ky = 1.
                 auto even_column = [&](int m, auto jc) {
                     constexpr int J = decltype(jc)::value;            // m % 2
-                    float cur[IR];
 #pragma unroll
-                    for (int i = 0; i < IR; ++i) cur[i] = nx[i];
-                    fetch(2 * m + 1, nx);
+                    for (int i = 0; i < IR; ++i) xf[i][J] = nx[i];
+                    fetch(2 * m + 1);
 #pragma unroll
                     for (int i = 0; i < IR; ++i) {
-                        xf[i][J] = cur[i];
-                        const unsigned qa = dw_q_u8(cur[i], P.in_off, P.in_inv);
+                        const unsigned qa = dw_q_u8(xf[i][J], in_off, in_inv);
                         if ((i & 1) == 0) {
                             unsigned tx, ty;
                             asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(tx), "=r"(ty) : "r"(lane16 + qa * 512u));
                             if (i / 2 < R) {
-                                acc[i / 2][J] = dw_add_lo<DP>(tx, acc[i / 2][J]);              // t00
-                                acc[i / 2][J ^ 1] = dw_add_hi<DP>(tx, acc[i / 2][J ^ 1]);      // t02
+                                acc[i / 2][J] = dw_add_lo<DP>(tx, 0);                                  // t00 starts the sum
+                                acc[i / 2][J ^ 1] = dw_add_hi<DP>(tx, acc[i / 2][J ^ 1]);              // t02
                             }
                             if (i >= 2) {
-                                acc[i / 2 - 1][J] = dw_add_lo<DP>(ty, acc[i / 2 - 1][J]);          // t20
-                                acc[i / 2 - 1][J ^ 1] = dw_add_hi<DP>(ty, acc[i / 2 - 1][J ^ 1]);  // t22
+                                acc[i / 2 - 1][J] = dw_add_lo<DP>(ty, acc[i / 2 - 1][J]);              // t20
+                                acc[i / 2 - 1][J ^ 1] = dw_add_hi<DP>(ty, acc[i / 2 - 1][J ^ 1]);      // t22
                             }
                         } else {
                             unsigned tw;
                             asm("ld.shared.u32 %0, [%1];" : "=r"(tw) : "r"(lane16 + qa * 512u + 12u));
-                            acc[i / 2][J] = dw_add_lo<DP>(tw, acc[i / 2][J]);                  // t10
-                            acc[i / 2][J ^ 1] = dw_add_hi<DP>(tw, acc[i / 2][J ^ 1]);          // t12
+                            acc[i / 2][J] = dw_add_lo<DP>(tw, acc[i / 2][J]);                          // t10
+                            acc[i / 2][J ^ 1] = dw_add_hi<DP>(tw, acc[i / 2][J ^ 1]);                  // t12
                         }
                     }
-                    if (m >= 1) {
-                        emit(m - 1, std::integral_constant<int, J ^ 1>{}, std::integral_constant<int, 2>{},
-                             std::integral_constant<int, J>{}, std::integral_constant<int, J ^ 1>{});
-                    } else {
-                        // column 0 also feeds output -1, which does not exist: drop what it got
-#pragma unroll
-                        for (int r = 0; r < R; ++r) acc[r][J ^ 1] = 0;
-                    }
+                    if (m >= 1) emit(m - 1, std::integral_constant<int, J ^ 1>{}, I2{}, std::integral_constant<int, J>{},
+                                     std::integral_constant<int, J ^ 1>{});
                 };
                 auto odd_column = [&](int m, auto jc) {
                     constexpr int J = decltype(jc)::value;
-                    float cur[IR];
 #pragma unroll
-                    for (int i = 0; i < IR; ++i) cur[i] = nx[i];
-                    fetch(2 * m + 2, nx);
+                    for (int i = 0; i < IR; ++i) xf[i][2] = nx[i];
+                    fetch(2 * m + 2);
 #pragma unroll
                     for (int i = 0; i < IR; ++i) {
-                        xf[i][2] = cur[i];
-                        const unsigned qa = dw_q_u8(cur[i], P.in_off, P.in_inv);
+                        const unsigned qa = dw_q_u8(xf[i][2], in_off, in_inv);
                         if ((i & 1) == 0) {
                             unsigned tz;
                             asm("ld.shared.u32 %0, [%1];" : "=r"(tz) : "r"(lane16 + qa * 512u + 8u));
@@ -586,33 +592,42 @@ __global__ void __launch_bounds__(NT, 1) depthwise_3x3_tab_kernel(const DwParams
                         }
                     }
                 };
-                fetch(0, nx);
+#pragma unroll
+                for (int r = 0; r < R; ++r) acc[r][1] = 0;    // fed by column 0 for the output -1; output 1 initialises it
+                fetch(0);
                 for (int m = 0; m <= P.OW; m += 2) {
-                    even_column(m, std::integral_constant<int, 0>{});
-                    if (m < P.OW) odd_column(m, std::integral_constant<int, 0>{});
+                    even_column(m, I0{});
+                    if (m < P.OW) odd_column(m, I0{});
                     if (m + 1 <= P.OW) {
-                        even_column(m + 1, std::integral_constant<int, 1>{});
-                        if (m + 1 < P.OW) odd_column(m + 1, std::integral_constant<int, 1>{});
+                        even_column(m + 1, I1{});
+                        if (m + 1 < P.OW) odd_column(m + 1, I1{});
                     }
                 }
             }
         }
-        u = g_end;
     }
 }
 
-template <int S, int R, int NT, bool DP>
-int launch_dw_tab(DwParams P, const DeviceInfo &di, cudaStream_t stream)
+template <int S, int R, int NT, bool DP, bool DBG>
+int launch_dw_tab_variant(DwParams P, const DeviceInfo &di, cudaStream_t stream)
 {
     P.bands = (P.OH + R - 1) / R;
     P.units_per_group = P.N * P.bands;
-    P.units_total = (long long)P.groups * P.units_per_group;
-    AXC_CUDA(cudaFuncSetAttribute(depthwise_3x3_tab_kernel<S, R, NT, DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kTabSmem)));
-    const long long grid = P.units_total < di.sm_count ? P.units_total : di.sm_count;
-    depthwise_3x3_tab_kernel<S, R, NT, DP><<<unsigned(grid), NT, kTabSmem, stream>>>(P);
+    P.wave = P.groups < di.sm_count ? P.groups : di.sm_count;
+    P.sets = di.sm_count / P.wave;
+    if (P.sets > P.units_per_group) P.sets = P.units_per_group;
+    AXC_CUDA(cudaFuncSetAttribute(depthwise_3x3_tab_kernel<S, R, NT, DP, DBG>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kTabSmem)));
+    depthwise_3x3_tab_kernel<S, R, NT, DP, DBG><<<unsigned(P.wave * P.sets), NT, kTabSmem, stream>>>(P);
     AXC_CUDA(cudaGetLastError());
     count_launch();
     return AXC_OK;
+}
+
+template <int S, int R, int NT, bool DP>
+int launch_dw_tab(const DwParams &P, const DeviceInfo &di, cudaStream_t stream)
+{
+    if (P.acc_out) return launch_dw_tab_variant<S, R, NT, DP, true>(P, di, stream);
+    return launch_dw_tab_variant<S, R, NT, DP, false>(P, di, stream);
 }
 
 template <typename Kern>
@@ -678,10 +693,11 @@ int launch_depthwise(const uint16_t *lut_dev, const Geom &g, const Quant &q, con
     const bool small = (long long)g.N * g.H * g.W * g.C < (1ll << 31) && g.M * OC < (1ll << 31) && P.items < (1ll << 31);
     const bool k3 = small && g.KH == 3 && g.KW == 3 && g.dh == 1 && g.dw == 1 && g.sh == g.sw;
     P.filter = filter; P.f_off = q.f_off; P.f_inv = q.f_inv;
-    P.bands = 0; P.units_per_group = 0; P.units_total = 0;
+    P.bands = 0; P.units_per_group = 0; P.wave = 0; P.sets = 0;
     // The expanded-table kernel pays about 74 000 lookups per CTA and channel group for its table: worth it from
     // some ten thousand outputs per group on.
-    if (k3 && (g.sw == 1 || g.sw == 2) && g.M * 32 >= kTabMinOutputsPerGroup && di.max_smem_optin >= int(kTabSmem)) {
+    if (k3 && (g.sw == 1 || g.sw == 2) && g.M * 32 >= kTabMinOutputsPerGroup && di.max_smem_optin >= int(kTabSmem) &&
+        (long long)g.W * g.C * 4 * 16 < (1ll << 32) && (long long)g.OW * OC * 4 * 8 < (1ll << 32)) {
         static const int variant = getenv("AXC_DW_TAB_VARIANT") ? atoi(getenv("AXC_DW_TAB_VARIANT")) : 0;   // tuning only
         if (variant >= 0) {
             if (g.sw == 1) {
