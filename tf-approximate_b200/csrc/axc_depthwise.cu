@@ -10,6 +10,8 @@
 // image row and keeps the 3x3 input window in registers, so an input element is read once
 // per output row it touches; the new window columns of four outputs are requested together.  The table lives in shared memory in the two-plane layout of
 // the dense kernel (plane p at 65536*(1+p), byte a*256 + 2*(b&127)).
+#include <cuda.h>
+
 #include <cstdlib>
 #include <mutex>
 #include <type_traits>
@@ -46,6 +48,7 @@ struct DwParams {
     int bands;             // bands of output rows per image
     int units_per_group;   // N * bands
     int wave, sets;        // CTAs per set (= channel groups served at a time) and sets: grid = wave * sets
+    int chan_box;          // channels per TMA box: min(32, C)
 };
 
 __device__ __forceinline__ unsigned dw_quantize_u8(float x, float off, float inv)
@@ -337,6 +340,10 @@ __global__ void __launch_bounds__(kDwThreads, 1) depthwise_3x3_kernel(const DwPa
 constexpr unsigned kTab16Bytes = 256u * 32u * 16u;
 constexpr unsigned kTab4Bytes = 256u * 32u * 4u;
 constexpr unsigned kTabSmem = kTab16Bytes + kTab4Bytes + 512u;
+#ifndef AXC_DW_PF
+#define AXC_DW_PF 3
+#endif
+constexpr int kTmaL2Ahead = 6;     // columns ahead of the copy in flight that are prefetched into L2
 constexpr long long kTabMinOutputsPerGroup = 32768;
 
 __device__ __forceinline__ unsigned dw_q_u8(float x, float off, float inv)
@@ -395,22 +402,68 @@ __device__ __forceinline__ const char *dw_ptr_mad(const char *base, unsigned a, 
     return reinterpret_cast<const char *>(r);
 }
 
-template <int S, int R, int NT, bool DP, bool DBG>
-__global__ void __launch_bounds__(NT, 1) depthwise_3x3_tab_kernel(const DwParams P)
+// ---- TMA helpers: every column of a band (IR rows x 32 channels) is one tiled bulk copy into a stage buffer of the
+// warp; rows, columns and channels outside the tensor arrive as zeros, which is exactly the padding rule ----------
+__device__ __forceinline__ void dw_mbar_init(unsigned bar)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void dw_tma_column(unsigned dst, const CUtensorMap *tmap, unsigned bar, unsigned bytes, int x, int col, int row, int n)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+                 ::"r"(dst), "l"(tmap), "r"(x), "r"(col), "r"(row), "r"(n), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void dw_tma_prefetch_l2(const CUtensorMap *tmap, int x, int col, int row, int n)
+{
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(tmap), "r"(x), "r"(col), "r"(row), "r"(n) : "memory");
+}
+// Waits for the phase `parity` of the barrier, at most about a second; false if the copy never arrived.
+__device__ __forceinline__ bool dw_mbar_wait(unsigned bar, unsigned parity)
+{
+    for (int it = 0; it < (1 << 20); ++it) {
+        unsigned done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+template <int S, int R, int NT, bool DP, bool DBG, bool TMA>
+__device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const CUtensorMap *tmap)
 {
     constexpr int IR = (R - 1) * S + 3;
     constexpr int kTabWarps = NT / 32;
+    constexpr int STAGES = S == 1 ? 3 : 2;          // stage of a column = its index % STAGES: a compile-time slot
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const unsigned dyn0 = (unsigned)__cvta_generic_to_shared(smem_raw);
     unsigned dyn_size;
     asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
     const unsigned tab16 = (dyn0 + 511u) & ~511u;
     const unsigned tab4 = tab16 + kTab16Bytes;
-    if (tab4 + kTab4Bytes > dyn0 + dyn_size) {
+    const unsigned box_bytes = unsigned(IR) * unsigned(P.chan_box) * 4u;               // what one copy delivers
+    const unsigned stage_bytes = (box_bytes + 127u) & ~127u;                           // stages start on 128-byte boundaries
+    const unsigned stages0 = tab4 + kTab4Bytes;                                        // [warp][stage][row][channel]
+    const unsigned bars0 = stages0 + (TMA ? unsigned(kTabWarps * STAGES) * stage_bytes : 0u);   // [warp][stage] mbarriers
+    if (bars0 + (TMA ? unsigned(kTabWarps * STAGES) * 8u : 0u) > dyn0 + dyn_size) {
         if (threadIdx.x == 0) atomicExch(P.status, 1);
         return;
     }
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const unsigned my_stage0 = stages0 + unsigned(warp * STAGES) * stage_bytes;
+    const unsigned my_bar0 = bars0 + unsigned(warp * STAGES) * 8u;
+    unsigned phase = 0;                 // bit s: parity the next wait on stage s expects
+    bool failed = false;                // a copy did not arrive in time: status 3, no further waits
+    if (TMA) {
+        if (lane == 0) {
+#pragma unroll
+            for (int st = 0; st < STAGES; ++st) dw_mbar_init(my_bar0 + st * 8u);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __syncwarp();
+    }
     const unsigned lane16 = tab16 + unsigned(lane) * 16u, lane4 = tab4 + unsigned(lane) * 4u;
     // CTAs work in sets of `wave` = min(groups, CTAs) members: the members of a set take different channel groups of
     // the same range of bands at the same time, so that the 128-byte pieces of a pixel that the groups read lie
@@ -422,6 +475,7 @@ __global__ void __launch_bounds__(NT, 1) depthwise_3x3_tab_kernel(const DwParams
     const unsigned orow_bytes = unsigned(P.OW) * unsigned(P.OC) * 4u;
     const unsigned pix_bytes = unsigned(P.C) * 4u, opix_bytes = unsigned(P.OC) * 4u;
     const float in_off = P.in_off, in_inv = P.in_inv;
+    constexpr int PF = AXC_DW_PF;
 
     for (int g = slot; g < P.groups; g += wave) {
         __syncthreads();                                    // every warp is done with the previous group's table
@@ -451,7 +505,35 @@ __global__ void __launch_bounds__(NT, 1) depthwise_3x3_tab_kernel(const DwParams
             int acc[R][S == 1 ? 3 : 2];
             float xf[IR][3];      // raw taps of the columns in flight: S == 1 ring slot = column % 3; S == 2: 0 / 1 = even
                                   // columns (m % 2), 2 = odd column
-            float nx[IR];         // raw taps of the column being fetched
+            float nx[IR];         // raw taps of the column being fetched (plain loads only)
+            const int ncols = S == 1 ? P.OW + 2 : 2 * P.OW + 1;                   // input columns of the band
+            const unsigned lane_off = (oc_ok ? unsigned(lane) : 0u) * 4u;
+
+            // TMA: column `c` into stage `st`, issued by lane 0 after the whole warp has consumed the stage
+            auto tma_issue = [&](int c, int st) {
+                __syncwarp();
+                if (lane == 0 && c < ncols) {
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    dw_tma_column(my_stage0 + unsigned(st) * stage_bytes, tmap, my_bar0 + unsigned(st) * 8u, box_bytes, g * 32,
+                                  c - P.pw, iy0, n);
+                    if (c + kTmaL2Ahead < ncols) dw_tma_prefetch_l2(tmap, g * 32, c + kTmaL2Ahead - P.pw, iy0, n);
+                }
+            };
+            // TMA: raw taps of the column in stage `st` into xf slot `slot`
+            auto tma_take = [&](auto stc, auto slotc) {
+                constexpr int st = decltype(stc)::value, slot = decltype(slotc)::value;
+                if (!failed) {
+                    if (!dw_mbar_wait(my_bar0 + st * 8u, (phase >> st) & 1u)) {
+                        failed = true;
+                        atomicExch(P.status, 3);
+                    }
+                    phase ^= 1u << st;
+                }
+                const unsigned a = my_stage0 + unsigned(st) * stage_bytes + lane_off;
+#pragma unroll
+                for (int i = 0; i < IR; ++i)
+                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(xf[i][slot]) : "r"(a + unsigned(i) * unsigned(P.chan_box) * 4u));
+            };
 
             // raw taps of input column `c` (relative: image column c - pw); zeros outside the image
             auto fetch = [&](int c) {
@@ -462,6 +544,12 @@ __global__ void __launch_bounds__(NT, 1) depthwise_3x3_tab_kernel(const DwParams
                         float x = 0.0f;
                         if (i >= lo && i < hi) x = __ldg(reinterpret_cast<const float *>(dw_ptr_mad(colp, unsigned(i), row_bytes)));
                         nx[i] = x;
+                    }
+                    if (PF > 0 && unsigned(c + PF - P.pw) < unsigned(P.W)) {
+                        const char *pfp = colp + PF * pix_bytes;
+#pragma unroll
+                        for (int i = 0; i < IR; ++i)
+                            if (i >= lo && i < hi) asm volatile("prefetch.global.L2 [%0];" ::"l"(dw_ptr_mad(pfp, unsigned(i), row_bytes)));
                     }
                 } else {
 #pragma unroll
@@ -502,9 +590,13 @@ __global__ void __launch_bounds__(NT, 1) depthwise_3x3_tab_kernel(const DwParams
                 auto column = [&](int c, auto jc) {
                     constexpr int J = decltype(jc)::value;            // c % 3
                     constexpr int s0 = J, s1 = (J + 2) % 3, s2 = (J + 1) % 3;
+                    if (TMA) {
+                        tma_take(std::integral_constant<int, J>{}, std::integral_constant<int, J>{});
+                    } else {
 #pragma unroll
-                    for (int i = 0; i < IR; ++i) xf[i][J] = nx[i];
-                    fetch(c + 1);                                      // next column in flight while this one is used
+                        for (int i = 0; i < IR; ++i) xf[i][J] = nx[i];
+                        fetch(c + 1);                                  // next column in flight while this one is used
+                    }
 #pragma unroll
                     for (int i = 0; i < IR; ++i) {
                         const unsigned qa = dw_q_u8(xf[i][J], in_off, in_inv);
@@ -528,12 +620,18 @@ __global__ void __launch_bounds__(NT, 1) depthwise_3x3_tab_kernel(const DwParams
                             acc[i - 2][s2] = dw_add_hi<DP>(t.y, acc[i - 2][s2]);
                         }
                     }
+                    if (TMA) tma_issue(c + STAGES, J);                 // the stage is free: every lane has used its taps
                     if (c >= 2) emit(c - 2, std::integral_constant<int, s2>{}, std::integral_constant<int, s1>{},
                                      std::integral_constant<int, s0>{}, std::integral_constant<int, s2>{});
                 };
 #pragma unroll
                 for (int r = 0; r < R; ++r) { acc[r][1] = 0; acc[r][2] = 0; }
-                fetch(0);
+                if (TMA) {
+#pragma unroll
+                    for (int st = 0; st < STAGES; ++st) tma_issue(st, st);
+                } else {
+                    fetch(0);
+                }
                 const int c_end = P.OW + 2;
                 for (int c = 0; c < c_end; c += 3) {
                     column(c, I0{});
@@ -545,9 +643,13 @@ __global__ void __launch_bounds__(NT, 1) depthwise_3x3_tab_kernel(const DwParams
                 // output m.  Even input row 2r: ky = 0 of output row r and ky = 2 of row r - 1; odd row 2r + 1: ky = 1.
                 auto even_column = [&](int m, auto jc) {
                     constexpr int J = decltype(jc)::value;            // m % 2
+                    if (TMA) {
+                        tma_take(I0{}, std::integral_constant<int, J>{});
+                    } else {
 #pragma unroll
-                    for (int i = 0; i < IR; ++i) xf[i][J] = nx[i];
-                    fetch(2 * m + 1);
+                        for (int i = 0; i < IR; ++i) xf[i][J] = nx[i];
+                        fetch(2 * m + 1);
+                    }
 #pragma unroll
                     for (int i = 0; i < IR; ++i) {
                         const unsigned qa = dw_q_u8(xf[i][J], in_off, in_inv);
@@ -569,14 +671,19 @@ __global__ void __launch_bounds__(NT, 1) depthwise_3x3_tab_kernel(const DwParams
                             acc[i / 2][J ^ 1] = dw_add_hi<DP>(tw, acc[i / 2][J ^ 1]);                  // t12
                         }
                     }
+                    if (TMA) tma_issue(2 * m + STAGES, 0);
                     if (m >= 1) emit(m - 1, std::integral_constant<int, J ^ 1>{}, I2{}, std::integral_constant<int, J>{},
                                      std::integral_constant<int, J ^ 1>{});
                 };
                 auto odd_column = [&](int m, auto jc) {
                     constexpr int J = decltype(jc)::value;
+                    if (TMA) {
+                        tma_take(I1{}, I2{});
+                    } else {
 #pragma unroll
-                    for (int i = 0; i < IR; ++i) xf[i][2] = nx[i];
-                    fetch(2 * m + 2);
+                        for (int i = 0; i < IR; ++i) xf[i][2] = nx[i];
+                        fetch(2 * m + 2);
+                    }
 #pragma unroll
                     for (int i = 0; i < IR; ++i) {
                         const unsigned qa = dw_q_u8(xf[i][2], in_off, in_inv);
@@ -591,10 +698,16 @@ __global__ void __launch_bounds__(NT, 1) depthwise_3x3_tab_kernel(const DwParams
                             acc[i / 2][J] += int(t11);
                         }
                     }
+                    if (TMA) tma_issue(2 * m + 1 + STAGES, 1);
                 };
 #pragma unroll
                 for (int r = 0; r < R; ++r) acc[r][1] = 0;    // fed by column 0 for the output -1; output 1 initialises it
-                fetch(0);
+                if (TMA) {
+#pragma unroll
+                    for (int st = 0; st < STAGES; ++st) tma_issue(st, st);
+                } else {
+                    fetch(0);
+                }
                 for (int m = 0; m <= P.OW; m += 2) {
                     even_column(m, I0{});
                     if (m < P.OW) odd_column(m, I0{});
@@ -609,13 +722,64 @@ __global__ void __launch_bounds__(NT, 1) depthwise_3x3_tab_kernel(const DwParams
 }
 
 template <int S, int R, int NT, bool DP, bool DBG>
+__global__ void __launch_bounds__(NT, 1) depthwise_3x3_tab_kernel(const DwParams P)
+{
+    depthwise_3x3_tab_body<S, R, NT, DP, DBG, false>(P, nullptr);
+}
+
+template <int S, int R, int NT, bool DP, bool DBG>
+__global__ void __launch_bounds__(NT, 1) depthwise_3x3_tma_kernel(const DwParams P, const __grid_constant__ CUtensorMap tmap)
+{
+    depthwise_3x3_tab_body<S, R, NT, DP, DBG, true>(P, &tmap);
+}
+
+// Tiled tensor map of the NHWC input for boxes of (chan_box channels, 1 column, rows, 1 image); false when the
+// tensor does not meet TMA's alignment rules (16-byte base and strides) or the driver entry point is missing.
+bool dw_make_tensor_map(const DwParams &P, int rows, CUtensorMap *out)
+{
+    typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static encode_fn encode = []() -> encode_fn {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<encode_fn>(fn);
+    }();
+    if (!encode || P.C % 4 != 0 || (reinterpret_cast<uintptr_t>(P.input) & 15u) != 0) return false;
+    const cuuint64_t dims[4] = {cuuint64_t(P.C), cuuint64_t(P.W), cuuint64_t(P.H), cuuint64_t(P.N)};
+    const cuuint64_t strides[3] = {cuuint64_t(P.C) * 4, cuuint64_t(P.W) * P.C * 4, cuuint64_t(P.H) * P.W * P.C * 4};
+    const cuuint32_t box[4] = {cuuint32_t(P.chan_box), 1, cuuint32_t(rows), 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(P.input), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int S, int R, int NT, bool DP, bool DBG>
 int launch_dw_tab_variant(DwParams P, const DeviceInfo &di, cudaStream_t stream)
 {
+    constexpr int IR = (R - 1) * S + 3;
+    constexpr int STAGES = S == 1 ? 3 : 2;
     P.bands = (P.OH + R - 1) / R;
     P.units_per_group = P.N * P.bands;
     P.wave = P.groups < di.sm_count ? P.groups : di.sm_count;
     P.sets = di.sm_count / P.wave;
     if (P.sets > P.units_per_group) P.sets = P.units_per_group;
+    P.chan_box = P.C < 32 ? P.C : 32;
+    // Input columns by TMA where the tensor allows it (and the channel multiplier is 1, so that a lane's input
+    // channel is its output channel); plain loads otherwise.
+    CUtensorMap tmap;
+    const unsigned tma_smem = kTabSmem + unsigned(NT / 32 * STAGES) * (((unsigned(IR) * unsigned(P.chan_box) * 4u + 127u) & ~127u) + 8u);
+    static const bool no_tma = getenv("AXC_DW_NO_TMA") != nullptr;   // tuning only
+    if (!no_tma && P.mult == 1 && tma_smem <= unsigned(di.max_smem_optin) && dw_make_tensor_map(P, IR, &tmap)) {
+        AXC_CUDA(cudaFuncSetAttribute(depthwise_3x3_tma_kernel<S, R, NT, DP, DBG>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tma_smem)));
+        depthwise_3x3_tma_kernel<S, R, NT, DP, DBG><<<unsigned(P.wave * P.sets), NT, tma_smem, stream>>>(P, tmap);
+        AXC_CUDA(cudaGetLastError());
+        count_launch();
+        return AXC_OK;
+    }
     AXC_CUDA(cudaFuncSetAttribute(depthwise_3x3_tab_kernel<S, R, NT, DP, DBG>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kTabSmem)));
     depthwise_3x3_tab_kernel<S, R, NT, DP, DBG><<<unsigned(P.wave * P.sets), NT, kTabSmem, stream>>>(P);
     AXC_CUDA(cudaGetLastError());
@@ -693,7 +857,7 @@ int launch_depthwise(const uint16_t *lut_dev, const Geom &g, const Quant &q, con
     const bool small = (long long)g.N * g.H * g.W * g.C < (1ll << 31) && g.M * OC < (1ll << 31) && P.items < (1ll << 31);
     const bool k3 = small && g.KH == 3 && g.KW == 3 && g.dh == 1 && g.dw == 1 && g.sh == g.sw;
     P.filter = filter; P.f_off = q.f_off; P.f_inv = q.f_inv;
-    P.bands = 0; P.units_per_group = 0; P.wave = 0; P.sets = 0;
+    P.bands = 0; P.units_per_group = 0; P.wave = 0; P.sets = 0; P.chan_box = 32;
     // The expanded-table kernel pays about 74 000 lookups per CTA and channel group for its table: worth it from
     // some ten thousand outputs per group on.
     if (k3 && (g.sw == 1 || g.sw == 2) && g.M * 32 >= kTabMinOutputsPerGroup && di.max_smem_optin >= int(kTabSmem) &&
