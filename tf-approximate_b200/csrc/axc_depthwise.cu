@@ -12,7 +12,6 @@
 // the dense kernel (plane p at 65536*(1+p), byte a*256 + 2*(b&127)).
 #include <cuda.h>
 
-#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -48,7 +47,6 @@ struct DwParams {
     int bands;             // bands of output rows per image
     int units_per_group;   // N * bands
     int wave, sets;        // CTAs per set (= channel groups served at a time) and sets: grid = wave * sets
-    int chan_box;          // channels per TMA box: min(32, C)
 };
 
 __device__ __forceinline__ unsigned dw_quantize_u8(float x, float off, float inv)
@@ -340,9 +338,7 @@ __global__ void __launch_bounds__(kDwThreads, 1) depthwise_3x3_kernel(const DwPa
 constexpr unsigned kTab16Bytes = 256u * 32u * 16u;
 constexpr unsigned kTab4Bytes = 256u * 32u * 4u;
 constexpr unsigned kTabSmem = kTab16Bytes + kTab4Bytes + 512u;
-#ifndef AXC_DW_PF
-#define AXC_DW_PF 3
-#endif
+constexpr int kPlainL2Ahead = 3;   // the same for the kernel that fetches with plain loads
 constexpr int kTmaL2Ahead = 6;     // columns ahead of the copy in flight that are prefetched into L2
 constexpr long long kTabMinOutputsPerGroup = 32768;
 
@@ -354,19 +350,16 @@ __device__ __forceinline__ unsigned dw_q_u8(float x, float off, float inv)
     return u;
 }
 
-// c + low / high 16-bit half of `a`.  DP: one two-way dot product with the byte vector {1,0} resp. {0,1}
-template <bool DP>
+// c + low / high 16-bit half of `a`: one two-way dot product with the byte vector {1,0} resp. {0,1} (measured no
+// slower than mask / shift + add, and one instruction instead of two)
 __device__ __forceinline__ int dw_add_lo(unsigned a, int c)
 {
-    if (!DP) return c + int(a & 0xFFFFu);
     int d;
     asm("dp2a.lo.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(0x00000001u), "r"(c));
     return d;
 }
-template <bool DP>
 __device__ __forceinline__ int dw_add_hi(unsigned a, int c)
 {
-    if (!DP) return c + int(a >> 16);
     int d;
     asm("dp2a.lo.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(0x00000100u), "r"(c));
     return d;
@@ -430,7 +423,7 @@ __device__ __forceinline__ bool dw_mbar_wait(unsigned bar, unsigned parity)
     return false;
 }
 
-template <int S, int R, int NT, bool DP, bool DBG, bool TMA>
+template <int S, int R, int NT, bool DBG, bool TMA>
 __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const CUtensorMap *tmap)
 {
     constexpr int IR = (R - 1) * S + 3;
@@ -442,8 +435,8 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
     asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
     const unsigned tab16 = (dyn0 + 511u) & ~511u;
     const unsigned tab4 = tab16 + kTab16Bytes;
-    const unsigned box_bytes = unsigned(IR) * unsigned(P.chan_box) * 4u;               // what one copy delivers
-    const unsigned stage_bytes = (box_bytes + 127u) & ~127u;                           // stages start on 128-byte boundaries
+    constexpr unsigned box_bytes = unsigned(IR) * 128u;        // what one copy delivers: IR rows of 32 channels
+    constexpr unsigned stage_bytes = box_bytes;                // a multiple of 128 bytes, as the copy's destination must be
     const unsigned stages0 = tab4 + kTab4Bytes;                                        // [warp][stage][row][channel]
     const unsigned bars0 = stages0 + (TMA ? unsigned(kTabWarps * STAGES) * stage_bytes : 0u);   // [warp][stage] mbarriers
     if (bars0 + (TMA ? unsigned(kTabWarps * STAGES) * 8u : 0u) > dyn0 + dyn_size) {
@@ -474,8 +467,8 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
     const unsigned row_bytes = unsigned(P.W) * unsigned(P.C) * 4u;        // the launcher keeps IR rows below 2^32 bytes
     const unsigned orow_bytes = unsigned(P.OW) * unsigned(P.OC) * 4u;
     const unsigned pix_bytes = unsigned(P.C) * 4u, opix_bytes = unsigned(P.OC) * 4u;
-    const float in_off = P.in_off, in_inv = P.in_inv;
-    constexpr int PF = AXC_DW_PF;
+    const float in_off = P.in_off, in_inv = P.in_inv, s1s2 = P.s1s2, m2 = P.m2, km1m2 = P.km1m2;
+    constexpr int PF = kPlainL2Ahead;
 
     for (int g = slot; g < P.groups; g += wave) {
         __syncthreads();                                    // every warp is done with the previous group's table
@@ -507,7 +500,7 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
                                   // columns (m % 2), 2 = odd column
             float nx[IR];         // raw taps of the column being fetched (plain loads only)
             const int ncols = S == 1 ? P.OW + 2 : 2 * P.OW + 1;                   // input columns of the band
-            const unsigned lane_off = (oc_ok ? unsigned(lane) : 0u) * 4u;
+            const unsigned lane_off = unsigned(lane) * 4u;
 
             // TMA: column `c` into stage `st`, issued by lane 0 after the whole warp has consumed the stage
             auto tma_issue = [&](int c, int st) {
@@ -532,7 +525,7 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
                 const unsigned a = my_stage0 + unsigned(st) * stage_bytes + lane_off;
 #pragma unroll
                 for (int i = 0; i < IR; ++i)
-                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(xf[i][slot]) : "r"(a + unsigned(i) * unsigned(P.chan_box) * 4u));
+                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(xf[i][slot]) : "r"(a + unsigned(i) * 128u));
             };
 
             // raw taps of input column `c` (relative: image column c - pw); zeros outside the image
@@ -565,18 +558,25 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
                 const char *accp = DBG ? dw_ptr_mad(acc0, unsigned(ox), opix_bytes) : nullptr;
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
-                    float a = 0.0f;
+                    // 0 + x00 of the reference's running sum is x00 up to the sign of a zero, which cannot reach the output
+                    float a = xf[r * S][k0];
+                    a = __fadd_rn(a, xf[r * S][k1]);
+                    a = __fadd_rn(a, xf[r * S][k2]);
 #pragma unroll
-                    for (int ky = 0; ky < 3; ++ky) {
+                    for (int ky = 1; ky < 3; ++ky) {
                         a = __fadd_rn(a, xf[r * S + ky][k0]);
                         a = __fadd_rn(a, xf[r * S + ky][k1]);
                         a = __fadd_rn(a, xf[r * S + ky][k2]);
                     }
-                    const float y = dw_epilogue(acc[r][sa], a, t2, P);
-                    if (r < rows_here) {
-                        asm volatile("st.global.f32 [%0], %1;" ::"l"(dw_ptr_mad(outp, unsigned(r), orow_bytes)), "f"(y) : "memory");
-                        if (DBG) asm volatile("st.global.s32 [%0], %1;" ::"l"(dw_ptr_mad(accp, unsigned(r), orow_bytes)), "r"(acc[r][sa]) : "memory");
-                    }
+                    const float t0 = __fmul_rn(float(acc[r][sa]), s1s2);
+                    const float t1 = __fmul_rn(m2, a);
+                    const float y = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), km1m2);
+                    // predicated stores (no branch): rows_here is 0 for a lane without a channel
+                    asm volatile("{\n\t.reg .pred p;\n\tsetp.gt.s32 p, %2, %3;\n\t@p st.global.f32 [%0], %1;\n\t}"
+                                 ::"l"(dw_ptr_mad(outp, unsigned(r), orow_bytes)), "f"(y), "r"(rows_here), "r"(r) : "memory");
+                    if (DBG)
+                        asm volatile("{\n\t.reg .pred p;\n\tsetp.gt.s32 p, %2, %3;\n\t@p st.global.s32 [%0], %1;\n\t}"
+                                     ::"l"(dw_ptr_mad(accp, unsigned(r), orow_bytes)), "r"(acc[r][sa]), "r"(rows_here), "r"(r) : "memory");
                 }
             };
             using I0 = std::integral_constant<int, 0>;
@@ -603,21 +603,21 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
                         uint4 t;
                         asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t.x), "=r"(t.y), "=r"(t.z), "=r"(t.w) : "r"(lane16 + qa * 512u));
                         if (i < R) {                                   // ky = 0 -> output row i
-                            acc[i][s0] = dw_add_lo<DP>(t.x, 0);
-                            acc[i][s1] = dw_add_lo<DP>(t.z, acc[i][s1]);
-                            acc[i][s2] = dw_add_hi<DP>(t.x, acc[i][s2]);
+                            acc[i][s0] = dw_add_lo(t.x, 0);
+                            acc[i][s1] = dw_add_lo(t.z, acc[i][s1]);
+                            acc[i][s2] = dw_add_hi(t.x, acc[i][s2]);
                         }
                         if (i >= 1 && i - 1 < R) {                     // ky = 1 -> output row i - 1
                             unsigned t11;
                             asm("ld.shared.u32 %0, [%1];" : "=r"(t11) : "r"(lane4 + qa * 128u));
-                            acc[i - 1][s0] = dw_add_lo<DP>(t.w, acc[i - 1][s0]);
+                            acc[i - 1][s0] = dw_add_lo(t.w, acc[i - 1][s0]);
                             acc[i - 1][s1] += int(t11);
-                            acc[i - 1][s2] = dw_add_hi<DP>(t.w, acc[i - 1][s2]);
+                            acc[i - 1][s2] = dw_add_hi(t.w, acc[i - 1][s2]);
                         }
                         if (i >= 2) {                                  // ky = 2 -> output row i - 2
-                            acc[i - 2][s0] = dw_add_lo<DP>(t.y, acc[i - 2][s0]);
-                            acc[i - 2][s1] = dw_add_hi<DP>(t.z, acc[i - 2][s1]);
-                            acc[i - 2][s2] = dw_add_hi<DP>(t.y, acc[i - 2][s2]);
+                            acc[i - 2][s0] = dw_add_lo(t.y, acc[i - 2][s0]);
+                            acc[i - 2][s1] = dw_add_hi(t.z, acc[i - 2][s1]);
+                            acc[i - 2][s2] = dw_add_hi(t.y, acc[i - 2][s2]);
                         }
                     }
                     if (TMA) tma_issue(c + STAGES, J);                 // the stage is free: every lane has used its taps
@@ -657,18 +657,18 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
                             unsigned tx, ty;
                             asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(tx), "=r"(ty) : "r"(lane16 + qa * 512u));
                             if (i / 2 < R) {
-                                acc[i / 2][J] = dw_add_lo<DP>(tx, 0);                                  // t00 starts the sum
-                                acc[i / 2][J ^ 1] = dw_add_hi<DP>(tx, acc[i / 2][J ^ 1]);              // t02
+                                acc[i / 2][J] = dw_add_lo(tx, 0);                                  // t00 starts the sum
+                                acc[i / 2][J ^ 1] = dw_add_hi(tx, acc[i / 2][J ^ 1]);              // t02
                             }
                             if (i >= 2) {
-                                acc[i / 2 - 1][J] = dw_add_lo<DP>(ty, acc[i / 2 - 1][J]);              // t20
-                                acc[i / 2 - 1][J ^ 1] = dw_add_hi<DP>(ty, acc[i / 2 - 1][J ^ 1]);      // t22
+                                acc[i / 2 - 1][J] = dw_add_lo(ty, acc[i / 2 - 1][J]);              // t20
+                                acc[i / 2 - 1][J ^ 1] = dw_add_hi(ty, acc[i / 2 - 1][J ^ 1]);      // t22
                             }
                         } else {
                             unsigned tw;
                             asm("ld.shared.u32 %0, [%1];" : "=r"(tw) : "r"(lane16 + qa * 512u + 12u));
-                            acc[i / 2][J] = dw_add_lo<DP>(tw, acc[i / 2][J]);                          // t10
-                            acc[i / 2][J ^ 1] = dw_add_hi<DP>(tw, acc[i / 2][J ^ 1]);                  // t12
+                            acc[i / 2][J] = dw_add_lo(tw, acc[i / 2][J]);                          // t10
+                            acc[i / 2][J ^ 1] = dw_add_hi(tw, acc[i / 2][J ^ 1]);                  // t12
                         }
                     }
                     if (TMA) tma_issue(2 * m + STAGES, 0);
@@ -690,8 +690,8 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
                         if ((i & 1) == 0) {
                             unsigned tz;
                             asm("ld.shared.u32 %0, [%1];" : "=r"(tz) : "r"(lane16 + qa * 512u + 8u));
-                            if (i / 2 < R) acc[i / 2][J] = dw_add_lo<DP>(tz, acc[i / 2][J]);           // t01
-                            if (i >= 2) acc[i / 2 - 1][J] = dw_add_hi<DP>(tz, acc[i / 2 - 1][J]);      // t21
+                            if (i / 2 < R) acc[i / 2][J] = dw_add_lo(tz, acc[i / 2][J]);           // t01
+                            if (i >= 2) acc[i / 2 - 1][J] = dw_add_hi(tz, acc[i / 2 - 1][J]);      // t21
                         } else {
                             unsigned t11;
                             asm("ld.shared.u32 %0, [%1];" : "=r"(t11) : "r"(lane4 + qa * 128u));
@@ -721,19 +721,19 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
     }
 }
 
-template <int S, int R, int NT, bool DP, bool DBG>
+template <int S, int R, int NT, bool DBG>
 __global__ void __launch_bounds__(NT, 1) depthwise_3x3_tab_kernel(const DwParams P)
 {
-    depthwise_3x3_tab_body<S, R, NT, DP, DBG, false>(P, nullptr);
+    depthwise_3x3_tab_body<S, R, NT, DBG, false>(P, nullptr);
 }
 
-template <int S, int R, int NT, bool DP, bool DBG>
+template <int S, int R, int NT, bool DBG>
 __global__ void __launch_bounds__(NT, 1) depthwise_3x3_tma_kernel(const DwParams P, const __grid_constant__ CUtensorMap tmap)
 {
-    depthwise_3x3_tab_body<S, R, NT, DP, DBG, true>(P, &tmap);
+    depthwise_3x3_tab_body<S, R, NT, DBG, true>(P, &tmap);
 }
 
-// Tiled tensor map of the NHWC input for boxes of (chan_box channels, 1 column, rows, 1 image); false when the
+// Tiled tensor map of the NHWC input for boxes of (32 channels, 1 column, rows, 1 image); false when the
 // tensor does not meet TMA's alignment rules (16-byte base and strides) or the driver entry point is missing.
 bool dw_make_tensor_map(const DwParams &P, int rows, CUtensorMap *out)
 {
@@ -750,14 +750,14 @@ bool dw_make_tensor_map(const DwParams &P, int rows, CUtensorMap *out)
     if (!encode || P.C % 4 != 0 || (reinterpret_cast<uintptr_t>(P.input) & 15u) != 0) return false;
     const cuuint64_t dims[4] = {cuuint64_t(P.C), cuuint64_t(P.W), cuuint64_t(P.H), cuuint64_t(P.N)};
     const cuuint64_t strides[3] = {cuuint64_t(P.C) * 4, cuuint64_t(P.W) * P.C * 4, cuuint64_t(P.H) * P.W * P.C * 4};
-    const cuuint32_t box[4] = {cuuint32_t(P.chan_box), 1, cuuint32_t(rows), 1};
+    const cuuint32_t box[4] = {32, 1, cuuint32_t(rows), 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     return encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(P.input), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int S, int R, int NT, bool DP, bool DBG>
+template <int S, int R, int NT, bool DBG>
 int launch_dw_tab_variant(DwParams P, const DeviceInfo &di, cudaStream_t stream)
 {
     constexpr int IR = (R - 1) * S + 3;
@@ -767,31 +767,29 @@ int launch_dw_tab_variant(DwParams P, const DeviceInfo &di, cudaStream_t stream)
     P.wave = P.groups < di.sm_count ? P.groups : di.sm_count;
     P.sets = di.sm_count / P.wave;
     if (P.sets > P.units_per_group) P.sets = P.units_per_group;
-    P.chan_box = P.C < 32 ? P.C : 32;
-    // Input columns by TMA where the tensor allows it (and the channel multiplier is 1, so that a lane's input
-    // channel is its output channel); plain loads otherwise.
+    // Input columns by TMA where the tensor allows it (at least 32 channels, and a channel multiplier of 1, so that
+    // a lane's input channel is its output channel); plain loads otherwise.
     CUtensorMap tmap;
-    const unsigned tma_smem = kTabSmem + unsigned(NT / 32 * STAGES) * (((unsigned(IR) * unsigned(P.chan_box) * 4u + 127u) & ~127u) + 8u);
-    static const bool no_tma = getenv("AXC_DW_NO_TMA") != nullptr;   // tuning only
-    if (!no_tma && P.mult == 1 && tma_smem <= unsigned(di.max_smem_optin) && dw_make_tensor_map(P, IR, &tmap)) {
-        AXC_CUDA(cudaFuncSetAttribute(depthwise_3x3_tma_kernel<S, R, NT, DP, DBG>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tma_smem)));
-        depthwise_3x3_tma_kernel<S, R, NT, DP, DBG><<<unsigned(P.wave * P.sets), NT, tma_smem, stream>>>(P, tmap);
+    const unsigned tma_smem = kTabSmem + unsigned(NT / 32 * STAGES) * (unsigned(IR) * 128u + 8u);
+    if (P.mult == 1 && P.C >= 32 && tma_smem <= unsigned(di.max_smem_optin) && dw_make_tensor_map(P, IR, &tmap)) {
+        AXC_CUDA(cudaFuncSetAttribute(depthwise_3x3_tma_kernel<S, R, NT, DBG>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tma_smem)));
+        depthwise_3x3_tma_kernel<S, R, NT, DBG><<<unsigned(P.wave * P.sets), NT, tma_smem, stream>>>(P, tmap);
         AXC_CUDA(cudaGetLastError());
         count_launch();
         return AXC_OK;
     }
-    AXC_CUDA(cudaFuncSetAttribute(depthwise_3x3_tab_kernel<S, R, NT, DP, DBG>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kTabSmem)));
-    depthwise_3x3_tab_kernel<S, R, NT, DP, DBG><<<unsigned(P.wave * P.sets), NT, kTabSmem, stream>>>(P);
+    AXC_CUDA(cudaFuncSetAttribute(depthwise_3x3_tab_kernel<S, R, NT, DBG>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kTabSmem)));
+    depthwise_3x3_tab_kernel<S, R, NT, DBG><<<unsigned(P.wave * P.sets), NT, kTabSmem, stream>>>(P);
     AXC_CUDA(cudaGetLastError());
     count_launch();
     return AXC_OK;
 }
 
-template <int S, int R, int NT, bool DP>
+template <int S, int R, int NT>
 int launch_dw_tab(const DwParams &P, const DeviceInfo &di, cudaStream_t stream)
 {
-    if (P.acc_out) return launch_dw_tab_variant<S, R, NT, DP, true>(P, di, stream);
-    return launch_dw_tab_variant<S, R, NT, DP, false>(P, di, stream);
+    if (P.acc_out) return launch_dw_tab_variant<S, R, NT, true>(P, di, stream);
+    return launch_dw_tab_variant<S, R, NT, false>(P, di, stream);
 }
 
 template <typename Kern>
@@ -857,31 +855,13 @@ int launch_depthwise(const uint16_t *lut_dev, const Geom &g, const Quant &q, con
     const bool small = (long long)g.N * g.H * g.W * g.C < (1ll << 31) && g.M * OC < (1ll << 31) && P.items < (1ll << 31);
     const bool k3 = small && g.KH == 3 && g.KW == 3 && g.dh == 1 && g.dw == 1 && g.sh == g.sw;
     P.filter = filter; P.f_off = q.f_off; P.f_inv = q.f_inv;
-    P.bands = 0; P.units_per_group = 0; P.wave = 0; P.sets = 0; P.chan_box = 32;
+    P.bands = 0; P.units_per_group = 0; P.wave = 0; P.sets = 0;
     // The expanded-table kernel pays about 74 000 lookups per CTA and channel group for its table: worth it from
     // some ten thousand outputs per group on.
     if (k3 && (g.sw == 1 || g.sw == 2) && g.M * 32 >= kTabMinOutputsPerGroup && di.max_smem_optin >= int(kTabSmem) &&
         (long long)g.W * g.C * 4 * 16 < (1ll << 32) && (long long)g.OW * OC * 4 * 8 < (1ll << 32)) {
-        static const int variant = getenv("AXC_DW_TAB_VARIANT") ? atoi(getenv("AXC_DW_TAB_VARIANT")) : 0;   // tuning only
-        if (variant >= 0) {
-            if (g.sw == 1) {
-                switch (variant) {
-                case 1: return launch_dw_tab<1, 7, 512, false>(P, di, stream);
-                case 2: return launch_dw_tab<1, 7, 384, true>(P, di, stream);
-                case 3: return launch_dw_tab<1, 4, 512, true>(P, di, stream);
-                case 4: return launch_dw_tab<1, 4, 768, true>(P, di, stream);
-                case 5: return launch_dw_tab<1, 6, 512, true>(P, di, stream);
-                default: return launch_dw_tab<1, 7, 512, true>(P, di, stream);
-                }
-            }
-            switch (variant) {
-            case 1: return launch_dw_tab<2, 4, 512, false>(P, di, stream);
-            case 2: return launch_dw_tab<2, 4, 384, true>(P, di, stream);
-            case 3: return launch_dw_tab<2, 3, 512, true>(P, di, stream);
-            case 4: return launch_dw_tab<2, 2, 768, true>(P, di, stream);
-            default: return launch_dw_tab<2, 4, 512, true>(P, di, stream);
-            }
-        }
+        if (g.sw == 1) return launch_dw_tab<1, 7, 512>(P, di, stream);
+        return launch_dw_tab<2, 4, 512>(P, di, stream);
     }
     if (k3 && g.sw == 1) return launch_dw(depthwise_3x3_kernel<1>, P, di, stream);
     if (k3 && g.sw == 2) return launch_dw(depthwise_3x3_kernel<2>, P, di, stream);
