@@ -25,32 +25,40 @@ if ROOT not in sys.path:
 
 import numpy as np  # noqa: E402
 
-CFG_INDEX = 4          # seeds follow 1000+cfg (input), 2000+100*cfg+layer (filters)
 SM_COUNT = 148
 LOOKUPS_PER_CLK_PER_SM = 32   # one 32-bit shared-memory bank transaction per lane per clock
 NCU_DRAM_OVER_ALGORITHMIC = (205.0 + 162.1) / 411.2
 
 
-# name -> (description for `config.workload`, default batch per GPU, input description)
+# name -> (description for `config.workload`, default batch per GPU, input description, configuration number)
+# Seeds follow the configuration number: 1000+cfg (input), 2000+100*cfg+layer (filters), 3000+100*cfg+layer (tables).
 WORKLOADS = {
     "resnet50": ("resnet50_approx_conv (BASELINE config 4): ImageNet-shaped ResNet-50 v1.5, 53 table "
                  "convolutions, truncated truth table, random He-init filters, frozen per-layer ranges",
-                 256, "224x224x3 fp32 NHWC"),
+                 256, "224x224x3 fp32 NHWC", 4),
     "resnet20": ("resnet20_approx_conv (BASELINE config 3): CIFAR-shaped ResNet-20, 3x3 table convolutions with "
-                 "16/32/64 channels, truncated truth table, random He-init filters, frozen per-layer ranges",
-                 1024, "32x32x3 fp32 NHWC"),
+                 "16/32/64 channels, a seeded noisy truth table per layer, random He-init filters, frozen per-layer "
+                 "ranges", 1024, "32x32x3 fp32 NHWC", 3),
     "mobilenet_stack": ("mobilenet_stack_approx_conv (BASELINE config 5): 3x3 depthwise + 1x1 pointwise table "
-                        "convolutions, 32-384 channels at 112/56/28/14, truncated truth table, random He-init "
-                        "filters, frozen per-layer ranges", 512, "112x112x32 fp32 NHWC"),
+                        "convolutions, 32-384 channels at 112/56/28/14, seeded noisy truth table, random He-init "
+                        "filters, frozen per-layer ranges", 512, "112x112x32 fp32 NHWC", 5),
 }
 
 
 def build_params(kind):
+    """(network, filters, truth tables: one for all layers or one per layer, configuration number)."""
     from tf_approximate_b200 import workloads as W
     import tf_approximate_b200 as ax
+    cfg = WORKLOADS[kind][3]
     net = W.Network(kind)
-    filters = W.make_filters(net.convs, 2000 + 100 * CFG_INDEX)
-    return net, filters, ax.truncated_table()
+    filters = W.make_filters(net.convs, 2000 + 100 * cfg)
+    if kind == "resnet50":
+        tables = [ax.truncated_table()]
+    elif kind == "resnet20":
+        tables = [ax.noisy_table(3000 + 100 * cfg + i) for i in range(len(net.convs))]
+    else:
+        tables = [ax.noisy_table(3000 + 100 * cfg)]
+    return net, filters, tables, cfg
 
 
 # ------------------------------------------------------------------------------------------------
@@ -63,36 +71,36 @@ def _cpu_worker(args):
     from tf_approximate_b200 import workloads as W
     from oracle import oracle as O
     import tf_approximate_b200 as ax
-    net, filters, lut = build_params(kind)
+    net, filters, tables, _ = build_params(kind)
     x = W.make_input(1, net.hw, net.in_channels, seed)
-    use_ref = O.ref_available()
-    tmp = None
+    # the reference's kernels have no depthwise path: such a workload is timed with the restatement
+    use_ref = O.ref_available() and not any(spec.depthwise for spec, _ in net.convs)
+    tmps, ops = [], []
     if use_ref:
-        tmp = tempfile.NamedTemporaryFile(suffix=".bin", delete=False)
-        tmp.close()
-        ax.write_table(tmp.name, lut)
-        op = O.RefOp(tmp.name)
-    conv_time = [0.0]
+        for lut in tables:
+            tmp = tempfile.NamedTemporaryFile(suffix=".bin", delete=False)
+            tmp.close()
+            ax.write_table(tmp.name, lut)
+            tmps.append(tmp.name)
+            ops.append(O.RefOp(tmp.name))
 
     def conv(spec, table_index, xx, f, lo, hi, flo, fhi):
         lo, hi = float(xx.min()), float(xx.max())   # per-call range: a single image calibrates itself
         d = O.desc(xx.shape[0], xx.shape[1], xx.shape[2], xx.shape[3], f.shape[0], f.shape[1], f.shape[3],
                    (spec.stride, spec.stride), (1, 1), "SAME")
-        t0 = time.perf_counter()
+        if spec.depthwise:
+            return O.depthwise_conv2d(d, tables[table_index], xx, f, lo, hi, flo, fhi, nthreads=1)["out_ref"]
         if use_ref:
-            y = op.conv2d(d, xx, f, lo, hi, flo, fhi)
-        else:
-            y = O.conv2d(d, lut, xx, f, lo, hi, flo, fhi, want=("out_ref",), nthreads=1)["out_ref"]
-        conv_time[0] += time.perf_counter() - t0
-        return y
+            return ops[table_index].conv2d(d, xx, f, lo, hi, flo, fhi)
+        return O.conv2d(d, tables[table_index], xx, f, lo, hi, flo, fhi, want=("out_ref",), nthreads=1)["out_ref"]
 
-    runner = W.CpuRunner(net, filters, [(0.0, 0.0)] * len(filters), conv)
+    runner = W.CpuRunner(net, filters, [(0.0, 0.0)] * len(filters), conv, shared_table=len(tables) == 1)
     t0 = time.perf_counter()
     runner.forward(x)
     dt = time.perf_counter() - t0
-    if tmp is not None:
+    for op, name in zip(ops, tmps):
         op.close()
-        os.unlink(tmp.name)
+        os.unlink(name)
     return dt, net.macs_per_image(), "reference" if use_ref else "port"
 
 
@@ -103,15 +111,15 @@ def run_cpu(kind, steps, warmup, workers=None):
     times, macs, impl_kind = [], 0, "port"
     with ctx.Pool(workers) as pool:
         for s in range(warmup + steps):
-            res = pool.map(_cpu_worker, [(kind, 1000 + CFG_INDEX + 17 * i) for i in range(workers)])
+            res = pool.map(_cpu_worker, [(kind, 1000 + WORKLOADS[kind][3] + 17 * i) for i in range(workers)])
             if s >= warmup:
                 times.append(max(r[0] for r in res))   # the workers run side by side: slowest forward pass
             macs = sum(r[1] for r in res)
             impl_kind = res[0][2]
     sec = sum(times) / len(times)
     return {"value": macs / sec, "unit": "LUT-MAC/s", "cores": workers, "kind": impl_kind,
-            "sample": "%d images of the same ResNet-50 forward per step, one per process (the reference's "
-                      "kernels are single-threaded)" % workers,
+            "sample": "%d images of the same %s forward per step, one per process (the reference's "
+                      "kernels are single-threaded)" % (workers, kind),
             "seconds_per_step": sec, "images_per_s": workers / sec, "macs_per_step": macs}
 
 
@@ -188,10 +196,10 @@ def run_gpu(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    net, filters, lut = build_params(args.workload)
+    net, filters, tables, cfg = build_params(args.workload)
     batch = args.batch if args.batch else WORKLOADS[args.workload][1]
-    runner = W.GpuRunner(net, [lut], filters, dev)
-    x_host = torch.from_numpy(W.make_input(batch, net.hw, net.in_channels, 1000 + CFG_INDEX + rank)).pin_memory()
+    runner = W.GpuRunner(net, tables, filters, dev)
+    x_host = torch.from_numpy(W.make_input(batch, net.hw, net.in_channels, 1000 + cfg + rank)).pin_memory()
     x = x_host.to(dev)
 
     # Frozen per-layer input ranges: calibrated on rank 0's batch, identical on every rank, so that
@@ -272,12 +280,43 @@ def run_gpu(args):
     f1.record(main)
     barrier()
     ms_e2e = f0.elapsed_time(f1)
+
+    # ---- timed region 3 (N > 1): ONE batch of the workload's size cut into contiguous slabs, one per GPU ------
+    # ("batch 256 sharded across 1/2/4/8 GPUs"): the same seeded global batch on every rank, rank r keeps
+    # parallel.shard_batch(x).  Then, separately timed and never inside the convolution timing, the optional
+    # all-gather of the final output over NCCL.
+    ms_strong, ms_gather, gather_bytes, shard = ms_total, 0.0, 0, batch
+    if world > 1:
+        x_glob = torch.from_numpy(W.make_input(batch, net.hw, net.in_channels, 1000 + cfg))
+        x_s = parallel.shard_batch(x_glob, world, rank).to(dev)
+        shard = int(x_s.shape[0])
+        del x_glob
+        for _ in range(max(args.warmup, 3)):
+            y_s = runner.forward(x_s)
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        g0.record()
+        for _ in range(args.steps):
+            y_s = runner.forward(x_s)
+        g1.record()
+        barrier()
+        ms_strong = g0.elapsed_time(g1)
+        y_all = parallel.gather_outputs(y_s)          # warm-up of the collective (communicator set-up)
+        h0, h1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        h0.record()
+        for _ in range(args.steps):
+            y_all = parallel.gather_outputs(y_s)
+        h1.record()
+        barrier()
+        ms_gather = h0.elapsed_time(h1)
+        gather_bytes = y_all.numel() * 4
     clocks = sampler.stop() if rank == 0 else None
 
-    t = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
+    t = torch.tensor([ms_total, ms_e2e, ms_strong, ms_gather], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, ms_e2e = float(t[0]), float(t[1])
+    ms_total, ms_e2e, ms_strong, ms_gather = float(t[0]), float(t[1]), float(t[2]), float(t[3])
 
     if rank != 0:
         if world > 1:
@@ -299,6 +338,9 @@ def run_gpu(args):
     sm_mhz = clocks["sm_mhz"] or 1965.0
     achieved = dense_macs / (dense_ms * 1e-3)
     peak = SM_COUNT * LOOKUPS_PER_CLK_PER_SM * sm_mhz * 1e6
+    # the same peak measured on this GPU: conflict-free 16-bit shared-memory loads per clock and SM (one short kernel)
+    measured_per_clk = ax.measure_lookup_peak(dev)
+    peak_measured = SM_COUNT * measured_per_clk * sm_mhz * 1e6
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -306,8 +348,8 @@ def run_gpu(args):
         pass
     hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
     # DRAM bytes per launch: ncu on the single 3x3 layer N=256, 56x56x64->64 read 205.0 MB and wrote 162.1 MB
-    # against 411.2 MB algorithmic (profiles/dense_kernel_cfg2_3x3_64to64.md); the whole step is too large to
-    # capture, so the measured ratio is applied to the average algorithmic bytes of a launch here.
+    # against 411.2 MB algorithmic; the whole step is too large to capture, so the measured ratio is applied to
+    # the average algorithmic bytes of a launch here.
     traffic = NCU_DRAM_OVER_ALGORITHMIC * io_bytes / dense_launches
     slowest = sorted(per_layer.items(), key=lambda kv: -kv[1])[:3]
     roofline = {
@@ -316,6 +358,10 @@ def run_gpu(args):
         "achieved": achieved / 1e9, "peak": peak / 1e9, "unit": "GLUT-MAC/s", "frac": achieved / peak,
         "peak_basis": "148 SMs x 32 shared-memory lookups/clk x %.0f MHz (median SM clock sampled during this run); "
                       "%.0f GLUT-MAC/s at the 1965 MHz maximum" % (sm_mhz, SM_COUNT * 32 * 1965e6 / 1e9),
+        "peak_measured": peak_measured / 1e9, "frac_of_measured": achieved / peak_measured,
+        "peak_measured_basis": "%.2f conflict-free 16-bit shared-memory loads per clock and SM, measured in this run "
+                               "by axc_measure_lookup_peak (512 threads per SM, 16 independent loads per thread and "
+                               "iteration), x 148 SMs x the sampled clock" % measured_per_clk,
         "units_per_launch": dense_macs / dense_launches, "ms_per_launch": dense_ms / dense_launches,
         "traffic": traffic, "traffic_unit": "bytes per launch (scaled from an ncu capture of one layer)",
         "hbm": {"algorithmic_bytes_per_step": io_bytes, "achieved_gbs": io_bytes / (dense_ms * 1e-3) / 1e9,
@@ -346,6 +392,17 @@ def run_gpu(args):
                    "l2": "not flushed: every layer's input and output are larger than the 126 MB L2"},
         "images_per_s": batch * world / (ms_step * 1e-3),
         "conv_only_lut_macs_per_s_rank0": achieved,
+        "strong_bs%d" % batch: {
+            "what": "one batch of %d images cut into contiguous slabs of %d per GPU (parallel.shard_batch), same "
+                    "frozen ranges, no collective in the step" % (batch, shard),
+            "scaling": "strong", "global_batch": batch, "batch_per_gpu": shard,
+            "ms_per_step": ms_strong / args.steps,
+            "value": net.macs_per_image() * batch / (ms_strong / args.steps * 1e-3), "unit": "LUT-MAC/s",
+            "images_per_s": batch / (ms_strong / args.steps * 1e-3),
+            "output_gather": None if world == 1 else {
+                "what": "all-gather of the final layer's output over NCCL (parallel.gather_outputs), timed on its own",
+                "ms": ms_gather / args.steps, "bytes_gathered_per_rank": gather_bytes,
+                "algbw_gbs": gather_bytes / (ms_gather / args.steps * 1e-3) / 1e9}},
         "e2e": {"value": macs_step / (ms_e2e_step * 1e-3), "unit": "LUT-MAC/s", "ms_per_step": ms_e2e_step,
                 "images_per_s": batch * world / (ms_e2e_step * 1e-3),
                 "h2d_bytes_per_step": in_bytes * world, "d2h_bytes_per_step": out_bytes * world},

@@ -181,6 +181,13 @@ const char *axc_status_string(int status);
 int axc_last_cuda_error(void);
 /* Number of kernels this library has launched in the calling process (monotonic). */
 uint64_t axc_launch_count(void);
+/* Measures what one SM sustains in conflict-free 16-bit shared-memory loads - the operation a table MAC of the
+ * dense kernels costs (the reference does the same lookup through a texture fetch,
+ * tf2/src/cuda/approx_nn_conv_kernels.cu:471-472) - in lookups per clock and SM; 32 by the construction of the
+ * hardware.  One short kernel on every SM, then a blocking read-back.  `scratch`: device memory, 256-byte aligned,
+ * at least 256 + 8 * (number of SMs) bytes.  Diagnostics for roofline reports; no counterpart in the reference. */
+int axc_measure_lookup_peak(int device, void *scratch, size_t scratch_bytes, void *stream,
+                            double *lookups_per_clk_per_sm);
 
 #ifdef __cplusplus
 }

@@ -13,7 +13,7 @@ SYMBOLS = [
     "axc_conv2d_workspace_bytes", "axc_depthwise_conv2d_workspace_bytes", "axc_conv2d_plan_info",
     "axc_conv2d_forward", "axc_conv2d_forward_device_ranges", "axc_depthwise_conv2d_forward",
     "axc_depthwise_conv2d_forward_noalloc",
-    "axc_quant_props", "axc_status_string", "axc_last_cuda_error", "axc_launch_count",
+    "axc_quant_props", "axc_status_string", "axc_last_cuda_error", "axc_launch_count", "axc_measure_lookup_peak",
 ]
 
 
@@ -65,5 +65,6 @@ def load():
     L.axc_status_string.restype = C.c_char_p
     L.axc_last_cuda_error.restype = C.c_int
     L.axc_launch_count.restype = C.c_uint64
+    L.axc_measure_lookup_peak.argtypes = [C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.POINTER(C.c_double)]
     _lib = L
     return L

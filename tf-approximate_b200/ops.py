@@ -251,3 +251,14 @@ def approx_depthwise_conv2d_with_min_max_vars(input, filter, input_min, input_ma
 def launch_count():
     """Kernels launched by libaxconv in this process so far."""
     return int(_lib.load().axc_launch_count())
+
+
+def measure_lookup_peak(device=None):
+    """Conflict-free 16-bit shared-memory loads one SM sustains, in lookups per clock (32 by construction)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    scratch = torch.zeros(8192, dtype=torch.uint8, device=dev)
+    out = C.c_double()
+    st = _lib.load().axc_measure_lookup_peak(dev.index or 0, scratch.data_ptr(), scratch.numel(),
+                                             C.c_void_p(torch.cuda.current_stream(dev).cuda_stream), C.byref(out))
+    raise_for_status(st, "lookup peak", _cuda_detail() if st == 100 else "")
+    return float(out.value)
