@@ -92,8 +92,10 @@ void axc_table_destroy(axc_table *table);
 /* Host copy of the 65536 entries (owned by the table). */
 int axc_table_host_data(const axc_table *table, const uint16_t **out);
 /* Uploads the 128 KiB replica for `device` if it is not there yet (blocking, once per
- * device).  axc_*_forward does this lazily; call it first to keep the upload out of a
- * timed or captured region. */
+ * device) and, on the first use of a device by this library, runs a one-thread probe kernel that records where a
+ * CTA's shared-memory window starts and ends there (the kernels place the table at fixed window addresses; a device
+ * whose window does not fit makes every forward call return AXC_INTERNAL instead of launching).  axc_*_forward
+ * does both lazily; call this first to keep them out of a timed or captured region. */
 int axc_table_ensure_device(axc_table *table, int device);
 
 /* ---- geometry: ComputeApproxConv2DDimensions (tf2/src/approx_nn_conv_ops.cpp:311-404) */
@@ -170,6 +172,14 @@ int axc_depthwise_conv2d_forward_noalloc(axc_table *table, const axc_conv_desc *
                                          const float *input, const float *filter,
                                          float in_min, float in_max, float f_min, float f_max,
                                          float *output, int device, void *stream);
+
+/* Status word the depthwise kernels leave in their scratch: 0 = fine, 1 = a kernel found its shared-memory layout
+ * broken and returned without writing the output, 3 = a bulk copy into shared memory did not arrive within its
+ * time limit.  `workspace` = the buffer of the forward call, or NULL for the built-in scratch of
+ * axc_depthwise_conv2d_forward_noalloc.  Blocks until `stream` is idle.  The forward calls themselves are
+ * asynchronous: AXC_OK from them means that the launches were accepted; what the kernels found is read here and, for
+ * the dense op, with axc_conv2d_plan_info.  No counterpart in the reference, which never checks a CUDA result. */
+int axc_depthwise_conv2d_status(const axc_conv_desc *desc, const void *workspace, int32_t *status, int device, void *stream);
 
 /* ---- quantisation parameters: Nudge + UpdateVarQuantProps
  *      (tf2/src/approx_ops_types.h:29-49, 135-152).  out3 = {scale, 1/scale, nudged_min}. */

@@ -32,9 +32,14 @@ class Quant(C.Structure):
                 ("s1s2", C.c_float), ("m1", C.c_float), ("m2", C.c_float), ("m1m2", C.c_float)]
 
 
-def build(ref_root="/root/reference"):
+def reference_root():
+    """Where the reference checkout lies: $AXC_REFERENCE_ROOT, else a directory `reference` beside the repository."""
+    return os.environ.get("AXC_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+
+
+def build(ref_root=None):
     """Compile the checker libraries (gcc only; seconds)."""
-    subprocess.run(["make", "-C", _HERE, "REF=" + ref_root], check=True, stdout=subprocess.DEVNULL)
+    subprocess.run(["make", "-C", _HERE, "REF=" + (ref_root or reference_root())], check=True, stdout=subprocess.DEVNULL)
 
 
 _lib = None

@@ -340,7 +340,8 @@ def run_depthwise(ax, lut, x, f, mm, stride, dil, pad):
         torch.from_numpy(x).cuda(), torch.from_numpy(f).cuda(), *mm, strides=[1, stride[0], stride[1], 1],
         num_bits=8, mul_map_file=ax.Table(array=lut), padding=pad, dilations=[1, dil[0], dil[1], 1], debug=True)
     torch.cuda.synchronize()
-    return y.cpu().numpy(), {k: v.cpu().numpy() for k, v in dbg.items()}
+    assert dbg["status"] == 0
+    return y.cpu().numpy(), {k: v.cpu().numpy() for k, v in dbg.items() if k != "status"}
 
 
 @pytest.mark.parametrize("case", cases.DEPTHWISE_CASES, ids=[c[0] for c in cases.DEPTHWISE_CASES])

@@ -18,7 +18,7 @@ import cases
 from oracle import oracle as O
 
 GDIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
-REF_ROOT = os.environ.get("AXC_REFERENCE_ROOT", "/root/reference")
+REF_ROOT = O.reference_root()
 
 
 @pytest.mark.parametrize("case", cases.DENSE_CASES, ids=[c[0] for c in cases.DENSE_CASES])

@@ -56,6 +56,8 @@ def test_noalloc_depthwise_matches_workspace_entry_point(built):
                                                     got.data_ptr(), 0, stream)
         assert st == 0, L.axc_status_string(st)
         torch.cuda.synchronize()
+        word = C.c_int32(-1)
+        assert L.axc_depthwise_conv2d_status(C.byref(d), None, C.byref(word), 0, stream) == 0 and word.value == 0
         if call > 0:   # the first call on a device may load the module that holds the array; later ones must not move the needle
             assert torch.cuda.mem_get_info(dev)[0] == free_before, "the entry point allocated device memory"
         # integer table sums and tap-order fp32 sums: the two entry points agree bit for bit

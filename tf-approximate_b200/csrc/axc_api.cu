@@ -234,6 +234,16 @@ const uint16_t *table_device_ptr_if_resident(axc_table *t, int device)
     return t->dev[size_t(device)];
 }
 
+__global__ void layout_probe_kernel(unsigned *out2)
+{
+    extern __shared__ __align__(16) unsigned char probe_smem[];
+    unsigned size;
+    asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(size));
+    out2[0] = (unsigned)__cvta_generic_to_shared(probe_smem);
+    out2[1] = out2[0] + size;
+}
+static __device__ unsigned g_layout_probe[2];
+
 int device_info(int device, DeviceInfo *out)
 {
     static std::mutex mu;
@@ -247,7 +257,26 @@ int device_info(int device, DeviceInfo *out)
     DeviceInfo di;
     AXC_CUDA(cudaDeviceGetAttribute(&di.sm_count, cudaDevAttrMultiProcessorCount, device));
     AXC_CUDA(cudaDeviceGetAttribute(&di.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
-    if (cache.size() <= size_t(device)) cache.resize(size_t(device) + 1, DeviceInfo{0, 0});
+    {
+        // where the dynamic shared memory of a CTA really starts and ends on this device and driver
+        int prev = 0;
+        AXC_CUDA(cudaGetDevice(&prev));
+        if (prev != device) AXC_CUDA(cudaSetDevice(device));
+        unsigned *sym = nullptr;
+        unsigned host2[2] = {0, 0};
+        cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void **>(&sym), g_layout_probe);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(layout_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin);
+        if (e == cudaSuccess) {
+            layout_probe_kernel<<<1, 1, size_t(di.max_smem_optin)>>>(sym);
+            e = cudaGetLastError();
+        }
+        if (e == cudaSuccess) e = cudaMemcpy(host2, sym, sizeof(host2), cudaMemcpyDeviceToHost);
+        if (prev != device) cudaSetDevice(prev);
+        if (e != cudaSuccess) return cuda_failed(e);
+        di.smem_base = host2[0];
+        di.smem_end = host2[1];
+    }
+    if (cache.size() <= size_t(device)) cache.resize(size_t(device) + 1, DeviceInfo{0, 0, 0, 0});
     cache[size_t(device)] = di;
     *out = di;
     return AXC_OK;
@@ -368,7 +397,9 @@ int axc_table_ensure_device(axc_table *t, int device)
     if (!t) return AXC_INVALID_ARGUMENT;
     int status = AXC_OK;
     axc::table_device_ptr(t, device, &status);
-    return status;
+    if (status) return status;
+    axc::DeviceInfo di;
+    return axc::device_info(device, &di);     // the one-time shared-memory probe of the device happens here, too
 }
 
 int axc_conv2d_output_dims(const axc_conv_desc *desc, int64_t out4[4])
@@ -447,6 +478,15 @@ int axc_conv2d_plan_info(const void *workspace, int32_t out4[4], int device, voi
     const int rc = axc::plan_info(workspace, out4, cudaStream_t(stream));
     if (prev != device) cudaSetDevice(prev);
     return rc;
+}
+
+int axc_depthwise_conv2d_status(const axc_conv_desc *desc, const void *workspace, int32_t *status, int device, void *stream)
+{
+    if (!status) return AXC_INVALID_ARGUMENT;
+    axc::Geom g;
+    int rc = axc::resolve_geometry(desc, true, &g);
+    if (rc) return rc;
+    return axc::depthwise_status(g, workspace, status, device, cudaStream_t(stream));
 }
 
 int axc_quant_props(float min_value, float max_value, float out3[3])

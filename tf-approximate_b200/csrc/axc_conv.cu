@@ -521,7 +521,10 @@ int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, con
     DeviceInfo di;
     int rc = device_info(device, &di);
     if (rc) return rc;
-    if (di.max_smem_optin < 232448) return AXC_INTERNAL;   // the kernels are laid out for the 227 KiB of sm_100
+    // The kernels are laid out for the 227 KiB of sm_100 and address the table by absolute window addresses: refuse
+    // to launch where the probed window of this device does not start early enough or does not reach 228 KiB
+    // (a kernel that found its layout broken would leave the output unwritten).
+    if (di.max_smem_optin < 232448 || di.smem_base > 2048u || di.smem_end < 233472u) return AXC_INTERNAL;
     // the scheduled kernel divides by C and KW with 40-bit reciprocals, exact while K * max(C, KW) < 2^40; it
     // lets every lane walk K in an order of its own, so a sum that has to be taken in K order is not its job
     const bool scheduled = !ref_order && dense_variant() == 0 && (long long)g.K * (g.C > g.KW ? g.C : g.KW) < (1ll << 40);

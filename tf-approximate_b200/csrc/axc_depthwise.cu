@@ -813,7 +813,8 @@ int launch_depthwise(const uint16_t *lut_dev, const Geom &g, const Quant &q, con
     DeviceInfo di;
     int rc = device_info(device, &di);
     if (rc) return rc;
-    if (di.max_smem_optin < int(kSmemEnd)) return AXC_INTERNAL;
+    // the register-window and generic kernels keep the table at the window addresses 64 KiB .. 192 KiB
+    if (di.max_smem_optin < int(kSmemEnd) || di.smem_base > kLutBase || di.smem_end < kSmemEnd) return AXC_INTERNAL;
     const int OC = g.C * g.Cout;
     const Workspace ws = depthwise_workspace(g.K, g.C, g.Cout);
     unsigned char *wsb = static_cast<unsigned char *>(workspace);
@@ -896,6 +897,29 @@ int static_scratch_address(int device, void **out)
 }
 
 }  // namespace
+
+int depthwise_status(const Geom &g, const void *workspace, int32_t *status, int device, cudaStream_t stream)
+{
+    const Workspace ws = depthwise_workspace(g.K, g.C, g.Cout);
+    int prev = 0;
+    AXC_CUDA(cudaGetDevice(&prev));
+    if (prev != device) AXC_CUDA(cudaSetDevice(device));
+    int rc = AXC_OK;
+    const void *base = workspace;
+    if (!base) {
+        if (ws.total > kStaticScratchBytes) rc = AXC_INVALID_ARGUMENT;
+        void *p = nullptr;
+        if (rc == AXC_OK) rc = static_scratch_address(device, &p);
+        base = p;
+    }
+    cudaError_t e = cudaSuccess;
+    if (rc == AXC_OK) e = cudaStreamSynchronize(stream);
+    if (rc == AXC_OK && e == cudaSuccess)
+        e = cudaMemcpy(status, static_cast<const unsigned char *>(base) + ws.status_off, sizeof(int32_t), cudaMemcpyDeviceToHost);
+    if (prev != device) cudaSetDevice(prev);
+    if (e != cudaSuccess) return cuda_failed(e);
+    return rc;
+}
 
 }  // namespace axc
 

@@ -60,8 +60,15 @@ bool table_sum_fits_int32(const axc_table *t, long long K);
 struct DeviceInfo {
     int sm_count;
     int max_smem_optin;
+    // Shared-memory window of a CTA launched with max_smem_optin bytes of dynamic shared memory, as a probe kernel
+    // saw it on this device: address of the first dynamic byte and the byte after the last.  The dense kernels place
+    // the table planes at fixed window addresses (64 KiB and 128 KiB) and need the window to reach 228 KiB.
+    unsigned smem_base, smem_end;
 };
+// Attributes of `device` (cached).  The first call for a device launches a one-thread probe kernel and waits for it.
 int device_info(int device, DeviceInfo *out);
+// Status word of the depthwise scratch of this shape (0 = fine); workspace == NULL: the built-in scratch.
+int depthwise_status(const Geom &g, const void *workspace, int32_t *status, int device, cudaStream_t stream);
 
 // ---- workspace layout (dense) ---------------------------------------------------------
 //   [0, prog_bytes)            kernel-layout filter program: uint4 per (l/4, j)

@@ -1118,9 +1118,9 @@ int launch_sched_variant(SchedParams P, const DeviceInfo &di, cudaStream_t strea
 }
 
 // Activation buffers that fit beside the table (the kernel repeats this computation with the real window base).
-int buffers_that_fit(const SchedParams &P, int NT)
+int buffers_that_fit(const SchedParams &P, int NT, unsigned smem_base)
 {
-    unsigned cur = 1024u;                                     // first byte after the driver's reserved kilobyte
+    unsigned cur = (smem_base + 15u) & ~15u;                  // first dynamic byte of the window, as probed on this device
     cur += unsigned(NT) * kTilePix * 16u;
     cur += 3u * unsigned(NT) * kTilePix * 4u;
     if (!P.vec_ok && P.K <= kTapTableMax) cur += unsigned(P.K) * 8u;
@@ -1266,8 +1266,8 @@ int launch_dense_sched(const Geom &g, const float *input, float *output,
         // pixel tiles per consumer warp: as many as the shared-memory budget allows (two sets of buffers)
         const int slots = (kComputeWarps / gw) * (P.dual ? 2 : 1);   // pixel tiles in flight per unit of NTW
         int ntw = 4;
-        while (ntw > 1 && buffers_that_fit(P, slots * ntw) < 2 * slots * ntw) ntw >>= 1;
-        if (buffers_that_fit(P, slots * ntw) < 2 * slots * ntw) return AXC_INTERNAL;
+        while (ntw > 1 && buffers_that_fit(P, slots * ntw, di.smem_base) < 2 * slots * ntw) ntw >>= 1;
+        if (buffers_that_fit(P, slots * ntw, di.smem_base) < 2 * slots * ntw) return AXC_INTERNAL;
         // Tile groups are handed out round-robin to one CTA per SM, so a launch takes ceil(groups / SMs) rounds.
         // Choose between one launch (any admissible number of tiles per warp) and a main launch of whole rounds
         // followed by a tail launch with smaller tile groups for the pixels that are left; estimate: a round

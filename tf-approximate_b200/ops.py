@@ -214,9 +214,14 @@ def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_
     if debug:
         if not depthwise:
             info = (C.c_int32 * 4)()
-            raise_for_status(L.axc_conv2d_plan_info(ws.data_ptr(), info, dev.index or 0, C.c_void_p(stream)), "plan info")
+            raise_for_status(L.axc_conv2d_plan_info(ws.data_ptr(), info, dev_index, C.c_void_p(stream)), "plan info")
             dbg_t["plan"] = {"rebuilt": int(info[0]), "fallback": int(info[1]), "status": int(info[2]),
                              "steps_per_mille": int(info[3])}
+        else:
+            word = C.c_int32(-1)
+            raise_for_status(L.axc_depthwise_conv2d_status(C.byref(d), ws.data_ptr(), C.byref(word), dev_index,
+                                                           C.c_void_p(stream)), "depthwise status")
+            dbg_t["status"] = int(word.value)
         return out, dbg_t
     return out
 
