@@ -173,6 +173,28 @@ int axc_depthwise_conv2d_forward_noalloc(axc_table *table, const axc_conv_desc *
                                          float in_min, float in_max, float f_min, float f_max,
                                          float *output, int device, void *stream);
 
+/* ---- quantised operands in, int32 sums out: the contract of the reference's first-generation op AxConv2D
+ *      (registration tf1/axqconv/axqconv.cc:66-94, arithmetic :197-263) ------------------------------------------
+ * qinput [n,h,w,c] and qfilter [kh,kw,c,cout] are uint8 codes; every product of the integer convolution is
+ * LUT[a][b], and the int32 result carries the reference's zero-point corrections
+ *     output = sum_l ( LUT[a_l][b_l] - a_l*filter_offset - b_l*input_offset + input_offset*filter_offset ),
+ * a tap outside the image counting as a_l = input_offset.  With both offsets 0 the output is the plain table sum.
+ * Offsets must lie in 0..255 (axc_quantized_zero_point gives the reference's value for a float range).  As in the
+ * reference op the strides must be equal and the dilation 1 (AXC_INVALID_ARGUMENT otherwise, :305-326); shapes on
+ * which the reference functor would place the window differently from TensorFlow's padding rule (stride larger
+ * than the window by two or more, :153-163) return AXC_UNIMPLEMENTED.  The table sums are computed by the kernels
+ * of axc_conv2d_forward; the workspace additionally holds an fp32 image of both operands. */
+int axc_qconv2d_workspace_bytes(const axc_conv_desc *desc, size_t *bytes);
+int axc_qconv2d_forward(axc_table *table, const axc_conv_desc *desc, const uint8_t *qinput, const uint8_t *qfilter,
+                        int32_t input_offset, int32_t filter_offset, int32_t *output, void *workspace,
+                        size_t workspace_bytes, int device, void *stream);
+/* The uint8 code of the real value 0 in [range_min, range_max]: FloatToQuantizedUnclamped<quint8>(0.0f, ...)
+ * (tf1/axqconv/quantization_utils.h:49-64; the op's offsets, tf1/axqconv/axqconv.cc:365-368). */
+int axc_quantized_zero_point(float range_min, float range_max, int32_t *offset);
+/* out2 = {min_output, max_output} of the op: QuantizationRangeForMultiplication<quint8, quint8, qint32>
+ * (tf1/axqconv/quantization_utils.h:116-140, tf1/axqconv/axqconv.cc:429-441). */
+int axc_quantized_output_range(float min_a, float max_a, float min_b, float max_b, float out2[2]);
+
 /* Status word the depthwise kernels leave in their scratch: 0 = fine, 1 = a kernel found its shared-memory layout
  * broken and returned without writing the output, 3 = a bulk copy into shared memory did not arrive within its
  * time limit.  `workspace` = the buffer of the forward call, or NULL for the built-in scratch of

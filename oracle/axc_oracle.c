@@ -451,6 +451,84 @@ int axo_conv2d_direct(const axo_conv_desc *d, const uint16_t *lut, const float *
 }
 
 /*
+ * First-generation op AxConv2D: quantised uint8 operands in, int32 sums out.
+ * Restates ReferenceConvFunctor::operator() of tf1/axqconv/axqconv.cc:132-263
+ * loop for loop: window origin from the functor's own offsets (:153-163), a tap
+ * outside the image counts as input_offset (:203-214), every product is a table
+ * entry (:232) and carries the zero-point terms (:241-246); offset_output = 0,
+ * mult_output = 1, shift_output = 0 (:369-371) leave the total as the output.
+ * Pin: the functor needs TensorFlow's quantised types to compile, so it is not
+ * built here; for the exact-product table the result must equal the integer
+ * convolution sum (a - input_offset) * (b - filter_offset), which the tests check.
+ */
+int axo_qconv2d(const axo_conv_desc *d, const uint16_t *lut, const uint8_t *qin, const uint8_t *qf, int input_offset,
+                int filter_offset, int32_t *out)
+{
+    int oh, ow, ph, pw;
+    int rc = axo_out_dims(d, &oh, &ow, &ph, &pw);
+    if (rc)
+        return rc;
+    if (d->dil_h != 1 || d->dil_w != 1 || d->stride_h != d->stride_w)
+        return AXO_INVALID_ARGUMENT;
+    const int stride = d->stride_h;
+    int left, top;
+    if (d->padding == AXO_PAD_VALID) {
+        left = ((ow - 1) * stride + d->kw - d->w + 1) / 2;
+        top = ((oh - 1) * stride + d->kh - d->h + 1) / 2;
+    } else {
+        left = ((ow - 1) * stride + d->kw - d->w) / 2;
+        top = ((oh - 1) * stride + d->kh - d->h) / 2;
+    }
+    const int C = d->c, F = d->cout;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int b = 0; b < d->n; ++b)
+        for (int oy = 0; oy < oh; ++oy)
+            for (int ox = 0; ox < ow; ++ox)
+                for (int oc = 0; oc < F; ++oc) {
+                    const int x0 = ox * stride - left;
+                    const int y0 = oy * stride - top;
+                    int32_t total = 0;
+                    for (int fy = 0; fy < d->kh; ++fy)
+                        for (int fx = 0; fx < d->kw; ++fx)
+                            for (int ic = 0; ic < C; ++ic) {
+                                const int ix = x0 + fx, iy = y0 + fy;
+                                int32_t a = input_offset;
+                                if (ix >= 0 && ix < d->w && iy >= 0 && iy < d->h)
+                                    a = qin[(((size_t)b * d->h + iy) * d->w + ix) * C + ic];
+                                const int32_t w = qf[(((size_t)fy * d->kw + fx) * C + ic) * F + oc];
+                                const int32_t axm = lut[(a << 8) | w];
+                                total += axm - a * filter_offset - w * input_offset + input_offset * filter_offset;
+                            }
+                    out[(((size_t)b * oh + oy) * ow + ox) * F + oc] = total;
+                }
+    return AXO_OK;
+}
+
+/* FloatToQuantizedUnclamped<quint8>(0.0f, min, max), tf1/axqconv/quantization_utils.h:49-64. */
+int32_t axo_quantized_zero_point(float range_min, float range_max)
+{
+    if (range_min == range_max)
+        return 0;
+    const int64_t number_of_steps = (int64_t)1 << 8;
+    const double range_adjust = (number_of_steps / (number_of_steps - 1.0));
+    const double range = ((range_max - range_min) * range_adjust);
+    const double range_scale = (number_of_steps / range);
+    int64_t quantized = (int64_t)(round(0.0f * range_scale) - round(range_min * range_scale));
+    return (int32_t)quantized;
+}
+
+/* QuantizationRangeForMultiplication<quint8, quint8, qint32>, tf1/axqconv/quantization_utils.h:116-140. */
+void axo_quantized_output_range(float min_a, float max_a, float min_b, float max_b, float *min_c, float *max_c)
+{
+    const float a_level = (max_a - min_a) / (int64_t)(255 - 0);
+    const float b_level = (max_b - min_b) / (int64_t)(255 - 0);
+    const int64_t c_highest = 2147483647ll, c_lowest = -2147483647ll - 1;
+    const float c_level = a_level * b_level;
+    *min_c = c_level * c_lowest;
+    *max_c = c_level * c_highest;
+}
+
+/*
  * Depthwise variant (no reference counterpart; the reference rejects grouped
  * shapes, tf2/src/approx_nn_conv_ops.cpp:229-232).  Filter [KH,KW,C,mult]
  * (TensorFlow DepthwiseConv2dNative layout), output channel c*mult+m.

@@ -72,6 +72,12 @@ def lib():
         L.axo_depthwise_conv2d.argtypes = [C.POINTER(ConvDesc), C.POINTER(C.c_uint16), C.POINTER(C.c_float),
                                            C.POINTER(C.c_float)] + [C.c_float] * 4 + \
                                           [C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_int32), C.c_int]
+        L.axo_qconv2d.argtypes = [C.POINTER(ConvDesc), C.POINTER(C.c_uint16), C.POINTER(C.c_uint8), C.POINTER(C.c_uint8),
+                                  C.c_int, C.c_int, C.POINTER(C.c_int32)]
+        L.axo_quantized_zero_point.argtypes = [C.c_float, C.c_float]
+        L.axo_quantized_zero_point.restype = C.c_int32
+        L.axo_quantized_output_range.argtypes = [C.c_float] * 4 + [C.POINTER(C.c_float)] * 2
+        L.axo_quantized_output_range.restype = None
         L.axo_max_threads.restype = C.c_int
         _lib = L
     return _lib
@@ -155,6 +161,30 @@ def conv2d_direct(d, lut, x, f, in_min, in_max, f_min, f_max):
     if rc:
         raise ValueError("axo_conv2d_direct status %d" % rc)
     return out
+
+
+def qconv2d(d, lut, qin, qf, input_offset, filter_offset):
+    """The first-generation op's integer functor (tf1/axqconv/axqconv.cc:132-263): uint8 in, int32 out."""
+    oh, ow, _, _ = out_dims(d)
+    qin = np.ascontiguousarray(qin, np.uint8)
+    qf = np.ascontiguousarray(qf, np.uint8)
+    lut = np.ascontiguousarray(lut, np.uint16)
+    out = np.zeros((d.n, oh, ow, d.cout), np.int32)
+    rc = lib().axo_qconv2d(C.byref(d), _ptr(lut, C.c_uint16), _ptr(qin, C.c_uint8), _ptr(qf, C.c_uint8),
+                           int(input_offset), int(filter_offset), _ptr(out, C.c_int32))
+    if rc:
+        raise ValueError("axo_qconv2d status %d" % rc)
+    return out
+
+
+def quantized_zero_point(range_min, range_max):
+    return int(lib().axo_quantized_zero_point(range_min, range_max))
+
+
+def quantized_output_range(min_a, max_a, min_b, max_b):
+    lo, hi = C.c_float(), C.c_float()
+    lib().axo_quantized_output_range(min_a, max_a, min_b, max_b, C.byref(lo), C.byref(hi))
+    return lo.value, hi.value
 
 
 def depthwise_conv2d(d, lut, x, f, in_min, in_max, f_min, f_max, nthreads=0):

@@ -1,0 +1,121 @@
+"""The quantised entry point (uint8 operands in, int32 sums out) - the contract of the reference's first-generation
+op AxConv2D (tf1/axqconv/axqconv.cc:66-94, 132-263) - and the table-less op ApproxConv2D
+(tf2/src/approx_nn_ops.cpp:24-36).
+
+CPU part: the checker's restatement of the integer functor against the plain integer convolution it must equal
+with the exact-product table, and the library's host arithmetic for offsets and output range against the checker's
+restatement of tf1/axqconv/quantization_utils.h.  GPU part: the CUDA path through the C ABI against the checker,
+bit for bit."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import cases
+from oracle import oracle as O
+
+
+def _int_conv(qin, qf, off_in, off_f, stride, pad):
+    """sum (a - off_in) * (b - off_f) with zero contribution outside the image, TensorFlow window placement."""
+    import torch
+    n, h, w, c = qin.shape
+    kh, kw, _, co = qf.shape
+    d = O.desc(n, h, w, c, kh, kw, co, (stride, stride), (1, 1), pad)
+    oh, ow, ph, pw = O.out_dims(d)
+    a = torch.from_numpy(qin.astype(np.float64) - off_in).permute(0, 3, 1, 2)
+    b = torch.from_numpy(qf.astype(np.float64) - off_f).permute(3, 2, 0, 1)
+    need_h = max((oh - 1) * stride + kh - h, 0)
+    need_w = max((ow - 1) * stride + kw - w, 0)
+    a = torch.nn.functional.pad(a, (pw, need_w - pw, ph, need_h - ph))
+    return torch.nn.functional.conv2d(a, b, stride=stride).permute(0, 2, 3, 1).numpy().astype(np.int64)
+
+
+QSHAPES = [
+    # n, h, w, c, kh, kw, cout, stride, padding, (min_in, max_in), (min_f, max_f)
+    (2, 9, 11, 5, 3, 3, 7, 1, "SAME", (-1.0, 1.0), (-0.4, 0.6)),
+    (1, 12, 12, 16, 3, 3, 40, 2, "SAME", (0.0, 6.0), (-0.5, 0.5)),      # input offset 0
+    (2, 8, 8, 64, 1, 1, 96, 1, "VALID", (-2.0, 2.0), (-1.0, 1.0)),
+    (1, 14, 14, 8, 5, 5, 33, 1, "VALID", (-1.0, 3.0), (-0.3, 0.1)),
+    (1, 21, 19, 3, 7, 7, 64, 2, "SAME", (-1.0, 1.0), (-0.2, 0.2)),
+]
+
+
+def _operands(shape, seed):
+    n, h, w, c, kh, kw, co = shape[:7]
+    rng = np.random.Generator(np.random.PCG64(seed))
+    return rng.integers(0, 256, (n, h, w, c), dtype=np.uint8), rng.integers(0, 256, (kh, kw, c, co), dtype=np.uint8)
+
+
+@pytest.mark.parametrize("shape", QSHAPES, ids=["-".join(str(v) for v in s[:9]) for s in QSHAPES])
+def test_checker_functor_equals_integer_convolution_with_exact_table(built, shape):
+    n, h, w, c, kh, kw, co, stride, pad, rin, rf = shape
+    qin, qf = _operands(shape, 5)
+    off_in, off_f = O.quantized_zero_point(*rin), O.quantized_zero_point(*rf)
+    got = O.qconv2d(O.desc(n, h, w, c, kh, kw, co, (stride, stride), (1, 1), pad), O.exact_table(), qin, qf, off_in, off_f)
+    assert np.array_equal(got.astype(np.int64), _int_conv(qin, qf, off_in, off_f, stride, pad))
+
+
+def test_offsets_and_output_range_match_checker(built):
+    from tf_approximate_b200 import _lib
+    L = _lib.load()
+    rng = np.random.Generator(np.random.PCG64(6))
+    ranges = [(-1.0, 1.0), (0.0, 6.0), (0.0, 0.0), (-3.5, 0.25), (1e-3, 2e-3)] + \
+             [tuple(sorted(rng.normal(0, 3, 2).astype(np.float32).tolist())) for _ in range(200)]
+    for lo, hi in ranges:
+        o = C.c_int32(-1)
+        assert L.axc_quantized_zero_point(lo, hi, C.byref(o)) == 0
+        assert o.value == O.quantized_zero_point(lo, hi), (lo, hi)
+        r = (C.c_float * 2)()
+        assert L.axc_quantized_output_range(lo, hi, -0.5, 0.75, r) == 0
+        want = O.quantized_output_range(lo, hi, -0.5, 0.75)
+        assert np.float32(r[0]).view(np.uint32) == np.float32(want[0]).view(np.uint32)
+        assert np.float32(r[1]).view(np.uint32) == np.float32(want[1]).view(np.uint32)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", QSHAPES, ids=["-".join(str(v) for v in s[:9]) for s in QSHAPES])
+def test_ax_conv2d_matches_checker(built, shape):
+    import torch
+    import tf_approximate_b200 as ax
+    n, h, w, c, kh, kw, co, stride, pad, rin, rf = shape
+    qin, qf = _operands(shape, 7)
+    lut = cases.make_table(("noisy", 61))
+    y, lo, hi = ax.ax_conv2d(torch.from_numpy(qin).cuda(), torch.from_numpy(qf).cuda(), rin[0], rin[1], rf[0], rf[1],
+                             [1, stride, stride, 1], pad, table=ax.Table(array=lut))
+    torch.cuda.synchronize()
+    off_in, off_f = O.quantized_zero_point(*rin), O.quantized_zero_point(*rf)
+    want = O.qconv2d(O.desc(n, h, w, c, kh, kw, co, (stride, stride), (1, 1), pad), lut, qin, qf, off_in, off_f)
+    assert np.array_equal(y.cpu().numpy(), want)
+    assert (lo, hi) == O.quantized_output_range(rin[0], rin[1], rf[0], rf[1])
+
+
+@pytest.mark.gpu
+def test_ax_conv2d_refuses_what_the_reference_refuses(built):
+    import torch
+    import tf_approximate_b200 as ax
+    x = torch.zeros((1, 20, 20, 4), dtype=torch.uint8, device="cuda")
+    f = torch.zeros((3, 3, 4, 8), dtype=torch.uint8, device="cuda")
+    with pytest.raises(ax.InvalidArgumentError):          # unequal strides (tf1/axqconv/axqconv.cc:309-313)
+        ax.ax_conv2d(x, f, -1, 1, -1, 1, [1, 1, 2, 1], "SAME")
+    with pytest.raises(ax.InvalidArgumentError):          # dilation (:320-323)
+        ax.ax_conv2d(x, f, -1, 1, -1, 1, [1, 1, 1, 1], "SAME", dilations=[1, 2, 2, 1])
+    x21 = torch.zeros((1, 21, 21, 4), dtype=torch.uint8, device="cuda")
+    with pytest.raises(ax.UnimplementedError):            # stride 8 over a 3x3 window on 21 pixels: the functor would start
+        ax.ax_conv2d(x21, f, -1, 1, -1, 1, [1, 8, 8, 1], "SAME")   # the window at +1 (:153-163), TensorFlow's padding rule at 0
+
+
+@pytest.mark.gpu
+def test_table_less_op_is_the_exact_product_table_with_data_ranges(built):
+    import torch
+    import tf_approximate_b200 as ax
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.rand((2, 16, 16, 24), device="cuda", generator=g) * 3 - 1
+    f = torch.randn((3, 3, 24, 40), device="cuda", generator=g) * 0.2
+    y = ax.approx_conv2d(x, f, [1, 1, 1, 1], "SAME")
+    want = ax.approx_conv2d_with_min_max_vars(x, f, float(x.min()), float(x.max()), float(f.min()), float(f.max()),
+                                              [1, 1, 1, 1], 8, "", "SAME")
+    assert torch.equal(y.view(torch.int32), want.view(torch.int32))
+    # and it is an 8-bit convolution: close to the float convolution, not equal to it
+    ref = torch.nn.functional.conv2d(x.permute(0, 3, 1, 2).double(), f.permute(3, 2, 0, 1).double(), padding=1).permute(0, 2, 3, 1)
+    err = float((y.double() - ref).abs().max() / ref.abs().max())
+    assert 0 < err < 0.05

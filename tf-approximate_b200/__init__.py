@@ -13,5 +13,6 @@ from .errors import InvalidArgumentError, UnimplementedError, InternalError, Cud
 from .tables import (exact_table, truncated_table, noisy_table, write_table, read_table,  # noqa: F401
                      table_from_function, table_from_c_source, table_report, validate_table_file)
 from .ops import (approx_conv2d_with_min_max_vars, approx_depthwise_conv2d_with_min_max_vars,  # noqa: F401
+                  ax_conv2d, approx_conv2d,
                   conv2d_output_shape, launch_count, measure_lookup_peak, Table)
 from .layers import FakeApproxConv2D, fake_quant_with_min_max_vars  # noqa: F401

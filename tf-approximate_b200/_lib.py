@@ -14,6 +14,7 @@ SYMBOLS = [
     "axc_conv2d_forward", "axc_conv2d_forward_device_ranges", "axc_depthwise_conv2d_forward",
     "axc_depthwise_conv2d_forward_noalloc", "axc_depthwise_conv2d_status",
     "axc_quant_props", "axc_status_string", "axc_last_cuda_error", "axc_launch_count", "axc_measure_lookup_peak",
+    "axc_qconv2d_workspace_bytes", "axc_qconv2d_forward", "axc_quantized_zero_point", "axc_quantized_output_range",
 ]
 
 
@@ -61,6 +62,11 @@ def load():
     L.axc_depthwise_conv2d_forward_noalloc.argtypes = [C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.c_float,
                                                        C.c_float, C.c_float, C.c_float, C.c_void_p, C.c_int, C.c_void_p]
     L.axc_depthwise_conv2d_status.argtypes = [C.POINTER(ConvDesc), C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_void_p]
+    L.axc_qconv2d_workspace_bytes.argtypes = [C.POINTER(ConvDesc), C.POINTER(C.c_size_t)]
+    L.axc_qconv2d_forward.argtypes = [C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p,
+                                      C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]
+    L.axc_quantized_zero_point.argtypes = [C.c_float, C.c_float, C.POINTER(C.c_int32)]
+    L.axc_quantized_output_range.argtypes = [C.c_float, C.c_float, C.c_float, C.c_float, C.POINTER(C.c_float)]
     L.axc_quant_props.argtypes = [C.c_float, C.c_float, C.POINTER(C.c_float)]
     L.axc_status_string.argtypes = [C.c_int]
     L.axc_status_string.restype = C.c_char_p

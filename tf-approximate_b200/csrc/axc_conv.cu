@@ -40,7 +40,7 @@ constexpr uint32_t kProgPadN = 0x00010000u;   // any valid table address; result
 struct DenseParams {
     const uint16_t *lut;
     const float *input;
-    float *output;
+    float *output;         // may be NULL: only the integer sums are wanted (acc_out)
     const uint4 *prog;     // [ceil(K/4)][Cout] filter-program quads
     const float *bsum;     // [Cout]
     int32_t *acc_out;      // optional [M][Cout]
@@ -476,7 +476,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
                     const float t0 = __fmul_rn(total, Q.s1s2);
                     const float t1 = __fmul_rn(Q.m2, a_sum);
                     const float o = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), Q.km1m2);
-                    P.output[p * P.Cout + j] = o;
+                    if (P.output) P.output[p * P.Cout + j] = o;
                     if (P.acc_out) P.acc_out[p * P.Cout + j] = REF ? __float2int_rz(total) : acc[i];
                 }
             }

@@ -1089,7 +1089,7 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
                     if (live && pix < P.M) {
                         const float t0 = __fmul_rn(float(acc[i][x]), Q.s1s2);
                         const float t1 = __fmul_rn(Q.m2, a_sum);
-                        P.output[pix * P.Cout + j] = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), Q.km1m2);
+                        if (P.output) P.output[pix * P.Cout + j] = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), Q.km1m2);
                         if (P.acc_out) P.acc_out[pix * P.Cout + j] = acc[i][x];
                     }
                     acc[i][x] = 0;

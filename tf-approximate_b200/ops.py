@@ -253,6 +253,54 @@ def approx_depthwise_conv2d_with_min_max_vars(input, filter, input_min, input_ma
                     mul_map_file, padding, list(explicit_paddings), data_format, list(dilations), out, debug)
 
 
+def ax_conv2d(input, filter, min_input, max_input, min_filter, max_filter, strides, padding, table="",
+              dilations=(1, 1, 1, 1), out=None):
+    """Mirror of the reference's first-generation op `AxConv2D` (tf1/axqconv/axqconv.cc:66-94): quantised uint8
+    input [N,H,W,C] and filter [KH,KW,C,Cout] with their float ranges in; returns (output int32 [N,OH,OW,Cout],
+    min_output, max_output).  `table` stands for the op's AxMult attribute: a `Table` or a table file ('' = exact
+    products).  The offsets are the codes of 0.0 in the two ranges (:365-368); the int32 output is the table sum
+    with the functor's zero-point terms (:241-246)."""
+    L = _lib.load()
+    if input.dtype != torch.uint8 or filter.dtype != torch.uint8 or not input.is_cuda or not filter.is_cuda:
+        raise InvalidArgumentError("input and filter must be uint8 CUDA tensors")
+    tab = _table_for(table, 8)
+    d = _desc(input.shape, filter.shape, strides, padding, "NHWC", list(dilations), [])
+    dims = (C.c_int64 * 4)()
+    raise_for_status(L.axc_conv2d_output_dims(C.byref(d), dims), "AxConv2D")
+    oshape = tuple(int(v) for v in dims)
+    dev = input.device
+    x, f = input.contiguous(), filter.contiguous()
+    if out is None:
+        out = torch.empty(oshape, dtype=torch.int32, device=dev)
+    off_in, off_f = C.c_int32(), C.c_int32()
+    raise_for_status(L.axc_quantized_zero_point(float(min_input), float(max_input), C.byref(off_in)), "input offset")
+    raise_for_status(L.axc_quantized_zero_point(float(min_filter), float(max_filter), C.byref(off_f)), "filter offset")
+    wsz = C.c_size_t()
+    raise_for_status(L.axc_qconv2d_workspace_bytes(C.byref(d), C.byref(wsz)), "workspace size")
+    ws = _workspace(dev, wsz.value, (f.data_ptr(), tuple(f.shape), id(tab), "q"))
+    dev_index = dev.index if dev.index is not None else torch.cuda.current_device()
+    st = L.axc_qconv2d_forward(tab.handle, C.byref(d), x.data_ptr(), f.data_ptr(), off_in.value, off_f.value,
+                               out.data_ptr(), ws.data_ptr(), ws.numel(), dev_index,
+                               C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    raise_for_status(st, "AxConv2D", _cuda_detail() if st == 100 else "")
+    rng = (C.c_float * 2)()
+    raise_for_status(L.axc_quantized_output_range(float(min_input), float(max_input), float(min_filter), float(max_filter), rng),
+                     "output range")
+    return out, float(rng[0]), float(rng[1])
+
+
+def approx_conv2d(input, filter, strides, padding, explicit_paddings=(), data_format="NHWC", dilations=(1, 1, 1, 1),
+                  name=None, out=None):
+    """The op the reference registers without a table and without range inputs, `ApproxConv2D`
+    (tf2/src/approx_nn_ops.cpp:24-36).  There it is an fp32 convolution; here it is served by the same table path
+    with the exact-product table and the ranges of the data - an 8-bit quantised convolution whose products are
+    exact.  The four ranges are reduced on the device and consumed there (no host round trip)."""
+    in_min, in_max = torch.aminmax(input)
+    f_min, f_max = torch.aminmax(filter)
+    return _forward(False, input, filter, in_min, in_max, f_min, f_max, strides, 8, "", padding, list(explicit_paddings),
+                    data_format, list(dilations), out, False)
+
+
 def launch_count():
     """Kernels launched by libaxconv in this process so far."""
     return int(_lib.load().axc_launch_count())
