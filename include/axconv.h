@@ -51,6 +51,12 @@ enum { AXC_FORMAT_NHWC = 0, AXC_FORMAT_NCHW = 1 };
  *   the call, since both give the same bits; otherwise a kernel that walks K in order does (about half the
  *   speed).  Depthwise calls ignore the field (K = kh*kw never rounds). */
 enum { AXC_ACCUM_EXACT_I32 = 0, AXC_ACCUM_REFERENCE_F32 = 1 };
+/* Whether the dense op prepares a per-filter lookup plan (kept in the workspace, built in 3-90 ms, reused while the
+ * filter is unchanged) or serves the call without one.
+ * AXC_PLAN_KEEP (default): inference - the plan makes every table lookup conflict-free (about 1.8 x the speed).
+ * AXC_PLAN_NONE: filters that change from call to call (training steps): the kernel that walks K in order serves
+ *   the call, nothing is prepared and nothing has to be rebuilt.  Same results bit for bit. */
+enum { AXC_PLAN_KEEP = 0, AXC_PLAN_NONE = 1 };
 
 /* Geometry of one call: what ApproxConv2DParameters + ApproxConv2DDimensions carry
  * (tf2/src/approx_nn_conv_ops.h:36-98, filled at tf2/src/approx_nn_conv_ops.cpp:254-404).
@@ -65,6 +71,7 @@ typedef struct {
     int32_t padding;      /* AXC_PADDING_*  */
     int32_t data_format;  /* AXC_FORMAT_*   */
     int32_t accumulate;   /* AXC_ACCUM_*: 0 = exact int32 sum (default), 1 = the reference's fp32 running total */
+    int32_t plan;         /* AXC_PLAN_*: 0 = keep a lookup plan per filter (default), 1 = none (changing filters) */
 } axc_conv_desc;
 
 /* Optional taps into the integer pipeline, for parity checks (device pointers, any may be
@@ -202,6 +209,18 @@ int axc_quantized_output_range(float min_a, float max_a, float min_b, float max_
  * asynchronous: AXC_OK from them means that the launches were accepted; what the kernels found is read here and, for
  * the dense op, with axc_conv2d_plan_info.  No counterpart in the reference, which never checks a CUDA result. */
 int axc_depthwise_conv2d_status(const axc_conv_desc *desc, const void *workspace, int32_t *status, int device, void *stream);
+
+/* ---- the steps that precede the op in the reference's Keras wrapper, on the device
+ *      (tf2/python/keras/layers/fake_approx_convolutional.py:233-242: reduce_min / reduce_max of the tensor, then
+ *      FakeQuantWithMinMaxVars) --------------------------------------------------------------------------------- */
+/* range2 (device, two floats) = {min, max} over the `count` floats at x: one reduction kernel (plus a two-thread
+ * kernel that resets range2).  NaNs are skipped.  count == 0 leaves {+inf, -inf}.  Write input and filter ranges
+ * into the two halves of one four-float buffer and hand it to axc_conv2d_forward_device_ranges. */
+int axc_tensor_range(const float *x, size_t count, float *range2, int device, void *stream);
+/* out[i] = x[i] clamped to the nudged range and snapped to its 256-level grid: the forward of TensorFlow's
+ * FakeQuantWithMinMaxVars with num_bits = 8, with the range read from device memory (range2 = {min, max}); the
+ * nudging is the op's own (tf2/src/approx_ops_types.h:29-49), operation by operation.  out may equal x. */
+int axc_fake_quant(const float *x, size_t count, const float *range2, float *out, int device, void *stream);
 
 /* ---- quantisation parameters: Nudge + UpdateVarQuantProps
  *      (tf2/src/approx_ops_types.h:29-49, 135-152).  out3 = {scale, 1/scale, nudged_min}. */

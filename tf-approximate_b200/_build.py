@@ -6,7 +6,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libaxconv.so")
-SOURCES = ["axc_api.cu", "axc_conv.cu", "axc_sched.cu", "axc_depthwise.cu", "axc_probe.cu", "axc_qconv.cu"]
+SOURCES = ["axc_api.cu", "axc_conv.cu", "axc_sched.cu", "axc_depthwise.cu", "axc_probe.cu", "axc_qconv.cu", "axc_prologue.cu"]
 
 
 def needs_build():

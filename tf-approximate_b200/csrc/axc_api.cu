@@ -143,6 +143,8 @@ int resolve_geometry(const axc_conv_desc *d, bool depthwise, Geom *g)
     if (d->c != d->filter_c) return AXC_UNIMPLEMENTED;  // grouped convolution
     if (d->accumulate != AXC_ACCUM_EXACT_I32 && d->accumulate != AXC_ACCUM_REFERENCE_F32) return AXC_INVALID_ARGUMENT;
     g->accum = d->accumulate;
+    if (d->plan != AXC_PLAN_KEEP && d->plan != AXC_PLAN_NONE) return AXC_INVALID_ARGUMENT;
+    g->plan = d->plan;
 
     g->N = d->n; g->H = d->h; g->W = d->w; g->C = d->c;
     g->KH = d->kh; g->KW = d->kw; g->Cout = d->cout;

@@ -527,7 +527,7 @@ int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, con
     if (di.max_smem_optin < 232448 || di.smem_base > 2048u || di.smem_end < 233472u) return AXC_INTERNAL;
     // the scheduled kernel divides by C and KW with 40-bit reciprocals, exact while K * max(C, KW) < 2^40; it
     // lets every lane walk K in an order of its own, so a sum that has to be taken in K order is not its job
-    const bool scheduled = !ref_order && dense_variant() == 0 && (long long)g.K * (g.C > g.KW ? g.C : g.KW) < (1ll << 40);
+    const bool scheduled = !ref_order && g.plan == AXC_PLAN_KEEP && dense_variant() == 0 && (long long)g.K * (g.C > g.KW ? g.C : g.KW) < (1ll << 40);
     const PlanLayout L = plan_layout(g.K, g.Cout);
     const Workspace ws = dense_workspace(g.K, g.Cout);
     unsigned char *plan = static_cast<unsigned char *>(workspace);

@@ -25,6 +25,7 @@ struct Geom {
     int K;             // dense: KH*KW*C; depthwise: KH*KW
     long long M;       // N*OH*OW
     int accum;         // AXC_ACCUM_*
+    int plan;          // AXC_PLAN_*
 };
 
 void var_quant_props(float min_v, float max_v, float *scale, float *inv, float *offset);

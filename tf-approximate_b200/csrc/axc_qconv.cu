@@ -155,6 +155,7 @@ extern "C" int axc_qconv2d_forward(axc_table *table, const axc_conv_desc *desc, 
         axc_debug_out taps = {nullptr, nullptr, output};
         Geom ge = g;
         ge.accum = AXC_ACCUM_EXACT_I32;
+        ge.plan = g.plan;
         rc = launch_dense(lut, table_uid(table), ge, q, nullptr, xin, xf, nullptr, ws, &taps, device, s, false);
     }
     if (e == cudaSuccess && rc == AXC_OK && (input_offset != 0 || filter_offset != 0)) {

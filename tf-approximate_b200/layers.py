@@ -4,6 +4,7 @@ input and kernel, the table convolution, then bias and activation; the backward 
 convolution's (the reference registers `conv2d_backprop_input/filter` as the gradient, :264-302)."""
 import torch
 
+from . import ops
 from .ops import approx_conv2d_with_min_max_vars
 
 
@@ -44,13 +45,27 @@ def fake_quant_with_min_max_vars(x, min_v, max_v, num_bits=8):
     return torch.where(zero_range, torch.zeros_like(x), q * scale + nmin)
 
 
+class _FakeQuantFn(torch.autograd.Function):
+    """Fake quantisation with a device-resident range (one kernel); straight-through gradient - every element lies
+    inside its own tensor's range, where TensorFlow's fake-quant gradient is the identity."""
+
+    @staticmethod
+    def forward(ctx, x, range2):
+        return ops.fake_quant_device_range(x, range2)
+
+    @staticmethod
+    def backward(ctx, grad):
+        return grad, None
+
+
 class _ApproxConvFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, mins_maxs, strides, padding, mul_map_file, num_bits, dilations):
+    def forward(ctx, x, w, ranges, strides, padding, mul_map_file, num_bits, dilations, plan, workspace):
         ctx.save_for_backward(x, w)
         ctx.cfg = (strides, padding, dilations)
-        return approx_conv2d_with_min_max_vars(x, w, *mins_maxs, strides=strides, num_bits=num_bits,
-                                               mul_map_file=mul_map_file, padding=padding, dilations=dilations)
+        return approx_conv2d_with_min_max_vars(x, w, None, None, None, None, strides=strides, num_bits=num_bits,
+                                               mul_map_file=mul_map_file, padding=padding, dilations=dilations,
+                                               plan=plan, workspace=workspace, ranges=ranges)
 
     @staticmethod
     def backward(ctx, grad):
@@ -70,7 +85,7 @@ class _ApproxConvFn(torch.autograd.Function):
                 xp = xc
             y = torch.nn.functional.conv2d(xp, wc, stride=(sh, sw), dilation=(dh, dw))
             gx, gw = torch.autograd.grad(y, (xc, wc), grad.permute(0, 3, 1, 2))
-        return gx.permute(0, 2, 3, 1), gw.permute(2, 3, 1, 0), None, None, None, None, None, None
+        return gx.permute(0, 2, 3, 1), gw.permute(2, 3, 1, 0), None, None, None, None, None, None, None, None
 
 
 class FakeApproxConv2D(torch.nn.Module):
@@ -92,19 +107,50 @@ class FakeApproxConv2D(torch.nn.Module):
         limit = (6.0 / (fan_in + fan_out)) ** 0.5  # glorot_uniform, the Keras default
         self.kernel = torch.nn.Parameter(torch.empty(ks[0], ks[1], in_channels, filters).uniform_(-limit, limit))
         self.bias = torch.nn.Parameter(torch.zeros(filters)) if use_bias else None
+        # owned by the layer, like the op instance's state in the reference: the four range scalars and the op's
+        # workspace (the lookup plan of the kernel lives there between calls)
+        self._ranges = None
+        self._workspace = None
+
+    def _own_buffers(self, inputs, strides4, dilations4):
+        dev = inputs.device
+        if self._ranges is None or self._ranges.device != dev:
+            self._ranges = torch.empty(4, dtype=torch.float32, device=dev)
+            self._workspace = None
+        need = ops.workspace_bytes(inputs.shape, self.kernel.shape, strides4, self.padding, dilations4)
+        if self._workspace is None or self._workspace.numel() < need:
+            self._workspace = torch.zeros(need, dtype=torch.uint8, device=dev)
+        return self._ranges, self._workspace
+
+    def plan_info(self):
+        """{rebuilt in the last call, fallback, status, steps per mille} of the lookup plan in the layer's workspace
+        (blocks until the current stream is idle)."""
+        import ctypes as C
+        from . import _lib
+        if self._workspace is None:
+            return None
+        info = (C.c_int32 * 4)()
+        dev = self._workspace.device
+        st = _lib.load().axc_conv2d_plan_info(self._workspace.data_ptr(), info, dev.index or 0,
+                                              C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+        ops.raise_for_status(st, "plan info")
+        return {"rebuilt": int(info[0]), "fallback": int(info[1]), "status": int(info[2]), "steps_per_mille": int(info[3])}
 
     def forward(self, inputs):
-        # per-batch ranges stay on the device: 0-d tensors, consumed by the op without a host round trip
-        input_min, input_max = torch.aminmax(inputs.detach())
-        q_in = fake_quant_with_min_max_vars(inputs, input_min, input_max, self.num_bits)
-        k_min, k_max = torch.aminmax(self.kernel.detach())
-        q_k = fake_quant_with_min_max_vars(self.kernel, k_min, k_max, self.num_bits)
-        # straight-through estimator for the fake-quant steps, as TF's fake-quant gradient inside the range
-        q_in = inputs + (q_in - inputs).detach()
-        q_k = self.kernel + (q_k - self.kernel).detach()
-        y = _ApproxConvFn.apply(q_in, q_k, (input_min, input_max, k_min, k_max),
-                                (1, self.strides[0], self.strides[1], 1), self.padding, self.mul_map_file,
-                                self.num_bits, (1, self.dilation_rate[0], self.dilation_rate[1], 1))
+        if self.num_bits != 8:
+            raise ops.InvalidArgumentError("only num_bits == 8 is supported")
+        strides4 = (1, self.strides[0], self.strides[1], 1)
+        dilations4 = (1, self.dilation_rate[0], self.dilation_rate[1], 1)
+        ranges, workspace = self._own_buffers(inputs, strides4, dilations4)
+        # per-batch ranges: one reduction kernel each, written where the op reads them - no host round trip
+        ops.tensor_range(inputs.detach(), ranges[0:2])
+        ops.tensor_range(self.kernel.detach(), ranges[2:4])
+        q_in = _FakeQuantFn.apply(inputs, ranges[0:2])
+        q_k = _FakeQuantFn.apply(self.kernel, ranges[2:4])
+        # while the weights are being trained they change every step: no lookup plan then (nothing to rebuild)
+        plan = "none" if (self.training and self.kernel.requires_grad) else "keep"
+        y = _ApproxConvFn.apply(q_in, q_k, ranges, strides4, self.padding, self.mul_map_file, self.num_bits, dilations4,
+                                plan, workspace)
         if self.bias is not None:
             y = y + self.bias
         if self.activation is not None:

@@ -18,6 +18,7 @@ from .errors import InvalidArgumentError, raise_for_status
 _PADDING = {"SAME": 0, "VALID": 1, "EXPLICIT": 2}
 _FORMAT = {"NHWC": 0, "NCHW": 1}
 _ACCUMULATE = {"exact": 0, "reference": 1}
+_PLAN = {"keep": 0, "none": 1}
 
 
 class Table:
@@ -95,9 +96,12 @@ def _scalar(v):
     return float(v)
 
 
-def _desc(input_shape, filter_shape, strides, padding, data_format, dilations, explicit_paddings, accumulate="exact"):
+def _desc(input_shape, filter_shape, strides, padding, data_format, dilations, explicit_paddings, accumulate="exact",
+          plan="keep"):
     if accumulate not in _ACCUMULATE:
         raise InvalidArgumentError("accumulate must be 'exact' or 'reference'")
+    if plan not in _PLAN:
+        raise InvalidArgumentError("plan must be 'keep' or 'none'")
     if len(input_shape) != 4:
         raise InvalidArgumentError("input must be 4-dimensional %s" % (tuple(input_shape),))
     if len(filter_shape) != 4:
@@ -122,7 +126,7 @@ def _desc(input_shape, filter_shape, strides, padding, data_format, dilations, e
     return _lib.ConvDesc(int(input_shape[n_i]), int(input_shape[h_i]), int(input_shape[w_i]), int(input_shape[c_i]),
                          int(filter_shape[0]), int(filter_shape[1]), int(filter_shape[2]), int(filter_shape[3]),
                          int(strides[h_i]), int(strides[w_i]), int(dilations[h_i]), int(dilations[w_i]),
-                         _PADDING[pad], _FORMAT[data_format], _ACCUMULATE[accumulate])
+                         _PADDING[pad], _FORMAT[data_format], _ACCUMULATE[accumulate], _PLAN[plan])
 
 
 def conv2d_output_shape(input_shape, filter_shape, strides, padding, data_format="NHWC", dilations=(1, 1, 1, 1),
@@ -137,28 +141,47 @@ def conv2d_output_shape(input_shape, filter_shape, strides, padding, data_format
 
 
 _ws_cache = collections.OrderedDict()
+_ws_lock = threading.Lock()
 _WS_CACHE_ENTRIES = 256
+_WS_CACHE_BYTES = 1 << 30
 
 
 def _workspace(device, nbytes, key):
-    """Per-filter workspace.  The library keeps the prepared filter (quantised copy, lookup schedule, filter
-    sums) in it and re-uses that preparation while the filter values it was built from are unchanged, so
-    every (device, filter storage, shape, table) gets its own buffer, the way the reference's op instance
-    owns its table (tf2/src/approx_ops_types.h:222).  The buffer belongs to one stream at a time."""
-    key = (device.index,) + key
-    buf = _ws_cache.get(key)
-    if buf is None or buf.numel() < nbytes:
-        buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
-        _ws_cache[key] = buf
-        while len(_ws_cache) > _WS_CACHE_ENTRIES:
-            _ws_cache.popitem(last=False)
-    else:
-        _ws_cache.move_to_end(key)
-    return buf
+    """Per-filter workspace for callers that do not bring their own (`workspace=`).  The library keeps the
+    prepared filter (quantised copy, lookup schedule, filter sums) in it and re-uses that preparation while the
+    filter values it was built from are unchanged, so every (device, stream, filter storage, shape, table) gets
+    its own buffer, the way the reference's op instance owns its table (tf2/src/approx_ops_types.h:222).  A buffer
+    serves one stream at a time, hence the stream in the key.  The cache is bounded in entries and in bytes; a
+    caller whose filter tensor is a temporary (a new address every call) should own the buffer instead, as
+    `layers.FakeApproxConv2D` does."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream) + key
+    with _ws_lock:
+        buf = _ws_cache.get(key)
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+            _ws_cache[key] = buf
+            total = sum(b.numel() for b in _ws_cache.values())
+            while len(_ws_cache) > 1 and (len(_ws_cache) > _WS_CACHE_ENTRIES or total > _WS_CACHE_BYTES):
+                _, old = _ws_cache.popitem(last=False)
+                total -= old.numel()
+        else:
+            _ws_cache.move_to_end(key)
+        return buf
+
+
+def workspace_bytes(input_shape, filter_shape, strides, padding, dilations=(1, 1, 1, 1), depthwise=False):
+    """Bytes of device scratch a forward call of this shape needs (axc_conv2d_workspace_bytes)."""
+    L = _lib.load()
+    d = _desc(input_shape, filter_shape, strides, padding, "NHWC", list(dilations), [])
+    wsz = C.c_size_t()
+    fn = L.axc_depthwise_conv2d_workspace_bytes if depthwise else L.axc_conv2d_workspace_bytes
+    raise_for_status(fn(C.byref(d), C.byref(wsz)), "workspace size")
+    return int(wsz.value)
 
 
 def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
-             mul_map_file, padding, explicit_paddings, data_format, dilations, out, debug, accumulate="exact"):
+             mul_map_file, padding, explicit_paddings, data_format, dilations, out, debug, accumulate="exact",
+             plan="keep", workspace=None, ranges=None):
     L = _lib.load()
     if not isinstance(input, torch.Tensor) or not isinstance(filter, torch.Tensor):
         raise InvalidArgumentError("input and filter must be torch tensors")
@@ -169,7 +192,7 @@ def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_
     if filter.device != input.device:
         raise InvalidArgumentError("input and filter are on different devices")
     table = _table_for(mul_map_file, num_bits)
-    d = _desc(input.shape, filter.shape, strides, padding, data_format, dilations, explicit_paddings, accumulate)
+    d = _desc(input.shape, filter.shape, strides, padding, data_format, dilations, explicit_paddings, accumulate, plan)
     dims = (C.c_int64 * 4)()
     dims_fn = L.axc_depthwise_conv2d_output_dims if depthwise else L.axc_conv2d_output_dims
     raise_for_status(dims_fn(C.byref(d), dims), "ApproxConv2D")
@@ -184,7 +207,14 @@ def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_
     wsz = C.c_size_t()
     ws_fn = L.axc_depthwise_conv2d_workspace_bytes if depthwise else L.axc_conv2d_workspace_bytes
     raise_for_status(ws_fn(C.byref(d), C.byref(wsz)), "workspace size")
-    ws = _workspace(dev, wsz.value, (f.data_ptr(), tuple(f.shape), id(table), depthwise))
+    if workspace is not None:
+        if (workspace.dtype != torch.uint8 or workspace.device != dev or not workspace.is_contiguous()
+                or workspace.numel() < wsz.value or workspace.data_ptr() % 256):
+            raise InvalidArgumentError("workspace must be a contiguous uint8 tensor on the input's device, 256-byte "
+                                       "aligned, of at least %d bytes" % wsz.value)
+        ws = workspace
+    else:
+        ws = _workspace(dev, wsz.value, (f.data_ptr(), tuple(f.shape), id(table), depthwise))
     dbg_ptr = None
     dbg_t = None
     if debug:
@@ -197,11 +227,16 @@ def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_
         dbg_ptr = C.byref(dbg)
     stream = torch.cuda.current_stream(dev).cuda_stream
     dev_index = dev.index if dev.index is not None else torch.cuda.current_device()
-    ranges = (input_min, input_max, filter_min, filter_max)
-    if not depthwise and all(isinstance(v, torch.Tensor) and v.is_cuda for v in ranges):
+    four = (input_min, input_max, filter_min, filter_max)
+    if ranges is not None and depthwise:
+        raise InvalidArgumentError("device-resident ranges are an option of the dense op")
+    if ranges is not None and (ranges.dtype != torch.float32 or ranges.device != dev or ranges.numel() != 4
+                               or not ranges.is_contiguous()):
+        raise InvalidArgumentError("ranges must be four contiguous fp32 values on the input's device")
+    if not depthwise and (ranges is not None or all(isinstance(v, torch.Tensor) and v.is_cuda for v in four)):
         # the four scalars already live on the GPU (e.g. fresh reductions): hand them over as they are, no
         # device-to-host synchronisation
-        r = torch.stack([v.reshape(()).to(torch.float32) for v in ranges]).contiguous()
+        r = ranges if ranges is not None else torch.stack([v.reshape(()).to(torch.float32) for v in four]).contiguous()
         st = L.axc_conv2d_forward_device_ranges(table.handle, C.byref(d), x.data_ptr(), f.data_ptr(), r.data_ptr(),
                                                 out.data_ptr(), ws.data_ptr(), ws.numel(), dbg_ptr, dev_index,
                                                 C.c_void_p(stream))
@@ -228,7 +263,8 @@ def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_
 
 def approx_conv2d_with_min_max_vars(input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
                                     mul_map_file, padding, explicit_paddings=(), data_format="NHWC",
-                                    dilations=(1, 1, 1, 1), name=None, out=None, debug=False, accumulate="exact"):
+                                    dilations=(1, 1, 1, 1), name=None, out=None, debug=False, accumulate="exact",
+                                    plan="keep", workspace=None, ranges=None):
     """Forward pass of `ApproxConv2DWithMinMaxVars`.
 
     input [N,H,W,C] and filter [KH,KW,C,Cout] are fp32 CUDA tensors; the four min/max values are
@@ -239,9 +275,16 @@ def approx_conv2d_with_min_max_vars(input, filter, input_min, input_max, filter_
 
     accumulate: "exact" (default) dequantises the exact integer sum of the looked-up products; "reference"
     reproduces the reference's fp32 running total added in K order (tf2/src/approx_nn_conv_kernels.cpp:245-246),
-    whose roundings show once a partial sum passes 2^24 - the output then has the reference's bits for every K."""
+    whose roundings show once a partial sum passes 2^24 - the output then has the reference's bits for every K.
+
+    plan: "keep" (default) prepares a lookup plan for the filter in the workspace and reuses it while the filter is
+    unchanged; "none" is for filters that change every call (training).  workspace: a uint8 CUDA tensor of at least
+    `workspace_bytes(...)` bytes that the caller keeps for this layer (default: a cache keyed by the filter's
+    address).  ranges: the four range scalars as one fp32 CUDA tensor {input_min, input_max, filter_min,
+    filter_max} (then the four positional range arguments are ignored and may be None)."""
     return _forward(False, input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
-                    mul_map_file, padding, list(explicit_paddings), data_format, list(dilations), out, debug, accumulate)
+                    mul_map_file, padding, list(explicit_paddings), data_format, list(dilations), out, debug, accumulate,
+                    plan, workspace, ranges)
 
 
 def approx_depthwise_conv2d_with_min_max_vars(input, filter, input_min, input_max, filter_min, filter_max, strides,
@@ -299,6 +342,35 @@ def approx_conv2d(input, filter, strides, padding, explicit_paddings=(), data_fo
     f_min, f_max = torch.aminmax(filter)
     return _forward(False, input, filter, in_min, in_max, f_min, f_max, strides, 8, "", padding, list(explicit_paddings),
                     data_format, list(dilations), out, False)
+
+
+def tensor_range(x, out=None):
+    """{min, max} of a fp32 CUDA tensor as two floats in device memory (one reduction kernel, no host round trip):
+    the wrapper's reduce_min / reduce_max (tf2/python/keras/layers/fake_approx_convolutional.py:233-240)."""
+    if not x.is_cuda or x.dtype != torch.float32:
+        raise InvalidArgumentError("tensor_range expects a fp32 CUDA tensor")
+    x = x.contiguous()
+    if out is None:
+        out = torch.empty(2, dtype=torch.float32, device=x.device)
+    dev_index = x.device.index if x.device.index is not None else torch.cuda.current_device()
+    st = _lib.load().axc_tensor_range(x.data_ptr(), x.numel(), out.data_ptr(), dev_index,
+                                      C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream))
+    raise_for_status(st, "tensor range", _cuda_detail() if st == 100 else "")
+    return out
+
+
+def fake_quant_device_range(x, range2, out=None):
+    """Forward of FakeQuantWithMinMaxVars (8 bits) with the range {min, max} read from device memory."""
+    if not x.is_cuda or x.dtype != torch.float32:
+        raise InvalidArgumentError("fake_quant_device_range expects a fp32 CUDA tensor")
+    x = x.contiguous()
+    if out is None:
+        out = torch.empty_like(x)
+    dev_index = x.device.index if x.device.index is not None else torch.cuda.current_device()
+    st = _lib.load().axc_fake_quant(x.data_ptr(), x.numel(), range2.data_ptr(), out.data_ptr(), dev_index,
+                                    C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream))
+    raise_for_status(st, "fake quant", _cuda_detail() if st == 100 else "")
+    return out
 
 
 def launch_count():
