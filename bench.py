@@ -434,6 +434,17 @@ def run_layer(args):
     mm = (-1.0, 1.0, float(f.min()), float(f.max()))
     fn = ax.approx_depthwise_conv2d_with_min_max_vars if dw else ax.approx_conv2d_with_min_max_vars
     kw = {} if dw else {"accumulate": args.accumulate}
+    if args.via_layer and not dw:
+        # the layer-level caller: per-batch range reductions and fake quantisation on the device, then the op with
+        # device-resident ranges; "train": the weights count as changing every step (no lookup plan is kept)
+        layer = ax.FakeApproxConv2D(c, cout, k, strides=stride, padding="same", use_bias=False, mul_map_file=table).to(dev)
+        with torch.no_grad():
+            layer.kernel.copy_(f)
+        layer.train(args.via_layer == "train")
+
+        def fn(x_, f_, *a, **k_):      # noqa: F811 - same call shape as the op
+            with torch.no_grad():
+                return layer(x_)
     out = None
     for _ in range(args.warmup):
         out = fn(x, f, *mm, [1, stride, stride, 1], 8, table, "SAME", out=out, **kw)
@@ -448,7 +459,8 @@ def run_layer(args):
     oh, ow = -(-h // stride), -(-w // stride)
     macs = n * oh * ow * k * k * c * (1 if dw else cout)
     io = 4 * (x.numel() + out.numel() + f.numel())
-    print(json.dumps({"layer": args.layer, "table": args.table, "accumulate": args.accumulate, "ms": ms, "lut_macs": macs,
+    print(json.dumps({"layer": args.layer, "table": args.table, "accumulate": args.accumulate, "via_layer": args.via_layer,
+                      "ms": ms, "lut_macs": macs,
                       "glut_macs_per_s": macs / ms / 1e6, "lookups_per_clk_per_sm_at_1965MHz": macs / (ms * 1e-3) / (SM_COUNT * 1965e6),
                       "io_gbs": io / ms / 1e6}))
 
@@ -484,6 +496,8 @@ def main():
     ap.add_argument("--per-layer", action="store_true", help="add per-layer times and lookups/clk/SM to the JSON line")
     ap.add_argument("--layer", default=None, help="time one layer instead: N,H,W,C,K,Cout,stride[,dw]")
     ap.add_argument("--table", default="truncated", choices=["truncated", "noisy", "exact"])
+    ap.add_argument("--via-layer", default=None, choices=["eval", "train"],
+                    help="--layer only: time the layer-level caller (range reductions + fake quantisation + op)")
     ap.add_argument("--accumulate", default="exact", choices=["exact", "reference"],
                     help="--layer only: exact integer sum (default) or the reference's fp32 running total in K order")
     args = ap.parse_args()

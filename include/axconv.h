@@ -146,6 +146,33 @@ int axc_conv2d_forward_device_ranges(axc_table *table, const axc_conv_desc *desc
                                      float *output, void *workspace, size_t workspace_bytes,
                                      const axc_debug_out *debug, int device, void *stream);
 
+/* ---- batch sharding over the GPUs of one box (no counterpart in the reference, which drives one GPU) ----------
+ * Every output pixel depends on its own image only, so a batch is cut into contiguous NHWC slabs, one per shard; the
+ * shards share nothing but the table handle (one 128 KiB replica per device) and the four range scalars, and no
+ * collective sits on the compute path.  One shard = the tensors of one slab on one device with a stream and a
+ * workspace of their own (axc_conv2d_workspace_bytes for a desc with n = the shard's images). */
+typedef struct {
+    int32_t device;
+    int32_t n;                 /* images in this slab */
+    const float *input;        /* [n,h,w,c] on `device` */
+    const float *filter;       /* this device's copy of the filter */
+    float *output;             /* [n,oh,ow,cout] on `device` */
+    void *workspace;
+    size_t workspace_bytes;
+    void *stream;              /* cudaStream_t of `device` */
+} axc_shard;
+/* Enqueues axc_conv2d_forward for every shard (desc->n is ignored, the shard's n counts); the launches are
+ * asynchronous, so one host thread keeps all GPUs busy.  Stops at the first shard that fails, stores its index in
+ * *failed_shard (if not NULL; -1 when all were accepted) and returns that shard's status; shards before it are
+ * already in flight and stay valid. */
+int axc_conv2d_forward_sharded(axc_table *table, const axc_conv_desc *desc, const axc_shard *shards, int32_t nshards,
+                               float in_min, float in_max, float f_min, float f_max, int32_t *failed_shard);
+/* Optional gather of the shards' outputs into one contiguous [sum n, oh, ow, cout] tensor `dst` on `dst_device`:
+ * one peer copy per shard, each enqueued on the shard's own stream (so it follows that shard's convolution), slab
+ * order = shard order.  `image_bytes` = bytes of one image's output.  In a one-process-per-GPU deployment the same
+ * step is an NCCL all-gather (the Python package's parallel.gather_outputs). */
+int axc_gather_outputs(const axc_shard *shards, int32_t nshards, size_t image_bytes, void *dst, int32_t dst_device);
+
 /* Depthwise variant (new: the reference rejects grouped shapes,
  * tf2/src/approx_nn_conv_ops.cpp:229-232).  filter [kh,kw,c,mult] in TensorFlow's
  * DepthwiseConv2dNative layout, output channel c*mult + m, same quantiser, table

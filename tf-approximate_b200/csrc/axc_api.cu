@@ -462,6 +462,41 @@ int axc_conv2d_forward_device_ranges(axc_table *table, const axc_conv_desc *desc
                         workspace_bytes, debug, device, stream);
 }
 
+int axc_conv2d_forward_sharded(axc_table *table, const axc_conv_desc *desc, const axc_shard *shards, int32_t nshards,
+                               float in_min, float in_max, float f_min, float f_max, int32_t *failed_shard)
+{
+    if (failed_shard) *failed_shard = -1;
+    if (!table || !desc || !shards || nshards <= 0) return AXC_INVALID_ARGUMENT;
+    for (int32_t i = 0; i < nshards; ++i) {
+        const axc_shard &sh = shards[i];
+        axc_conv_desc d = *desc;
+        d.n = sh.n;
+        const int rc = axc::forward(false, table, &d, sh.input, sh.filter, nullptr, in_min, in_max, f_min, f_max, sh.output,
+                                    sh.workspace, sh.workspace_bytes, nullptr, sh.device, sh.stream);
+        if (rc != AXC_OK) {
+            if (failed_shard) *failed_shard = i;
+            return rc;
+        }
+    }
+    return AXC_OK;
+}
+
+int axc_gather_outputs(const axc_shard *shards, int32_t nshards, size_t image_bytes, void *dst, int32_t dst_device)
+{
+    if (!shards || nshards <= 0 || !dst) return AXC_INVALID_ARGUMENT;
+    unsigned char *p = static_cast<unsigned char *>(dst);
+    for (int32_t i = 0; i < nshards; ++i) {
+        const axc_shard &sh = shards[i];
+        const size_t bytes = size_t(sh.n) * image_bytes;
+        if (bytes > 0) {
+            if (!sh.output) return AXC_INVALID_ARGUMENT;
+            AXC_CUDA(cudaMemcpyPeerAsync(p, dst_device, sh.output, sh.device, bytes, cudaStream_t(sh.stream)));
+        }
+        p += bytes;
+    }
+    return AXC_OK;
+}
+
 int axc_depthwise_conv2d_forward(axc_table *table, const axc_conv_desc *desc, const float *input,
                                  const float *filter, float in_min, float in_max, float f_min, float f_max,
                                  float *output, void *workspace, size_t workspace_bytes,
