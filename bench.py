@@ -199,6 +199,9 @@ def run_gpu(args):
     net, filters, tables, cfg = build_params(args.workload)
     batch = args.batch if args.batch else WORKLOADS[args.workload][1]
     runner = W.GpuRunner(net, tables, filters, dev)
+    if args.unfused:       # shortcut additions and ReLUs as separate element-wise kernels instead of inside the convolutions
+        fused_forward = runner.forward
+        runner.forward = lambda xx: fused_forward(xx, fused=False)
     x_host = torch.from_numpy(W.make_input(batch, net.hw, net.in_channels, 1000 + cfg + rank)).pin_memory()
     x = x_host.to(dev)
 
@@ -496,6 +499,8 @@ def main():
     ap.add_argument("--per-layer", action="store_true", help="add per-layer times and lookups/clk/SM to the JSON line")
     ap.add_argument("--layer", default=None, help="time one layer instead: N,H,W,C,K,Cout,stride[,dw]")
     ap.add_argument("--table", default="truncated", choices=["truncated", "noisy", "exact"])
+    ap.add_argument("--unfused", action="store_true",
+                    help="run shortcut additions and ReLUs as separate element-wise kernels (default: fused into the convolutions)")
     ap.add_argument("--via-layer", default=None, choices=["eval", "train"],
                     help="--layer only: time the layer-level caller (range reductions + fake quantisation + op)")
     ap.add_argument("--accumulate", default="exact", choices=["exact", "reference"],

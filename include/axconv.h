@@ -135,6 +135,28 @@ int axc_conv2d_forward(axc_table *table, const axc_conv_desc *desc,
                        float *output, void *workspace, size_t workspace_bytes,
                        const axc_debug_out *debug, int device, void *stream);
 
+/* What the callers of the op add to its output before anything else reads it: the bias and the activation of the
+ * reference's Keras layer (tf2/python/keras/layers/fake_approx_convolutional.py:245-261) and the shortcut of a
+ * residual block.  Fused into the kernels' dequantisation, so the output is written once:
+ *     y = conv;  if (bias) y += bias[channel];  if (residual) y += residual[same index];  if (relu) y = max(y, 0)
+ * - each addition a separately rounded fp32 operation, i.e. the bits of the same steps done by separate kernels.
+ * bias: [out channels] on the device or NULL; residual: a tensor of the output's shape on the device or NULL. */
+typedef struct {
+    const float *bias;
+    const float *residual;
+    int32_t relu;
+} axc_epilogue;
+/* axc_conv2d_forward (ranges == NULL: the four host scalars count) or axc_conv2d_forward_device_ranges
+ * (ranges != NULL) with a fused epilogue (NULL = none). */
+int axc_conv2d_forward_fused(axc_table *table, const axc_conv_desc *desc, const float *input, const float *filter,
+                             float in_min, float in_max, float f_min, float f_max, const float *ranges,
+                             const axc_epilogue *epilogue, float *output, void *workspace, size_t workspace_bytes,
+                             const axc_debug_out *debug, int device, void *stream);
+int axc_depthwise_conv2d_forward_fused(axc_table *table, const axc_conv_desc *desc, const float *input,
+                                       const float *filter, float in_min, float in_max, float f_min, float f_max,
+                                       const axc_epilogue *epilogue, float *output, void *workspace,
+                                       size_t workspace_bytes, const axc_debug_out *debug, int device, void *stream);
+
 /* Same op with the four range scalars read from DEVICE memory: `ranges` = {input_min, input_max, filter_min,
  * filter_max}, four floats on `device`, typically written by the reductions that precede the op in the
  * reference's Keras wrapper (tf2/python/keras/layers/fake_approx_convolutional.py:233-242).  The quantisation

@@ -115,3 +115,52 @@ def test_config4_batch256_slice_equals_alone(built):
 def test_config5_batch512_slice_equals_alone(built):
     import tf_approximate_b200 as ax
     _slice_equals_alone("mobilenet_stack", 512, ax.noisy_table(3000 + 500), 5, 300, 303)
+
+
+@pytest.mark.parametrize("kind,hw,batch", [("resnet50", 64, 2), ("resnet20", 32, 4), ("mobilenet_stack", 56, 2)])
+def test_fused_epilogue_equals_separate_steps(built, kind, hw, batch):
+    """Shortcut addition and ReLU fused into the convolution kernels' dequantisation give the bits of the same steps
+    done by separate element-wise kernels, through the whole network."""
+    import torch
+    import tf_approximate_b200 as ax
+    from tf_approximate_b200 import workloads as W
+    net = W.Network(kind, hw)
+    filters = W.make_filters(net.convs, 2000 + 100 * 4)
+    dev = torch.device("cuda", 0)
+    runner = W.GpuRunner(net, [ax.noisy_table(3090)], filters, dev)
+    x = torch.from_numpy(W.make_input(batch, net.hw, net.in_channels, 1004)).to(dev)
+    runner.calibrate(x)
+    y_fused = runner.forward(x, fused=True)
+    y_plain = runner.forward(x, fused=False)
+    assert torch.isfinite(y_plain).all() and float(y_plain.abs().max()) > 0
+    assert torch.equal(y_fused, y_plain)
+
+
+def test_op_epilogue_bias_residual_relu(built):
+    """The op-level epilogue on every kernel that has one: scheduled kernel, kernel without a plan, reference-order
+    kernel, expanded-table depthwise kernel, small depthwise kernels."""
+    import torch
+    import tf_approximate_b200 as ax
+    g = torch.Generator(device="cuda").manual_seed(9)
+    t = ax.Table(array=ax.noisy_table(3091))
+    x = torch.rand((2, 40, 40, 48), device="cuda", generator=g) * 2 - 1
+    f = torch.randn((3, 3, 48, 72), device="cuda", generator=g) * 0.1
+    mm = (-1.0, 1.0, float(f.min()), float(f.max()))
+    bias = torch.randn(72, device="cuda", generator=g)
+    res = torch.randn((2, 40, 40, 72), device="cuda", generator=g)
+    for kw in ({}, {"plan": "none"}, {"accumulate": "reference"}):
+        y0 = ax.approx_conv2d_with_min_max_vars(x, f, *mm, [1, 1, 1, 1], 8, t, "SAME", **kw)
+        y1 = ax.approx_conv2d_with_min_max_vars(x, f, *mm, [1, 1, 1, 1], 8, t, "SAME", bias=bias, residual=res, relu=True, **kw)
+        assert torch.equal(y1, torch.relu((y0 + bias) + res)), kw
+        y2 = ax.approx_conv2d_with_min_max_vars(x, f, *mm, [1, 1, 1, 1], 8, t, "SAME", relu=True, **kw)
+        assert torch.equal(y2, torch.relu(y0)), kw
+    for shape, stride in (((2, 40, 40, 48), 1), ((2, 41, 39, 40), 2), ((1, 9, 9, 16), 1)):
+        xd = torch.rand(shape, device="cuda", generator=g) * 2
+        fd = torch.randn((3, 3, shape[3], 1), device="cuda", generator=g) * 0.3
+        mmd = (0.0, 2.0, float(fd.min()), float(fd.max()))
+        y0 = ax.approx_depthwise_conv2d_with_min_max_vars(xd, fd, *mmd, [1, stride, stride, 1], 8, t, "SAME")
+        b = torch.randn(shape[3], device="cuda", generator=g)
+        r = torch.randn(tuple(y0.shape), device="cuda", generator=g)
+        y1 = ax.approx_depthwise_conv2d_with_min_max_vars(xd, fd, *mmd, [1, stride, stride, 1], 8, t, "SAME", bias=b, residual=r,
+                                                          relu=True)
+        assert torch.equal(y1, torch.relu((y0 + b) + r)), shape

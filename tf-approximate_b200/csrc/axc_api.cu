@@ -145,6 +145,7 @@ int resolve_geometry(const axc_conv_desc *d, bool depthwise, Geom *g)
     g->accum = d->accumulate;
     if (d->plan != AXC_PLAN_KEEP && d->plan != AXC_PLAN_NONE) return AXC_INVALID_ARGUMENT;
     g->plan = d->plan;
+    g->ep = Epilogue{nullptr, nullptr, 0};
 
     g->N = d->n; g->H = d->h; g->W = d->w; g->C = d->c;
     g->KH = d->kh; g->KW = d->kw; g->Cout = d->cout;
@@ -288,12 +289,13 @@ int device_info(int device, DeviceInfo *out)
 static int forward(bool depthwise, axc_table *table, const axc_conv_desc *desc, const float *input,
                    const float *filter, const float *ranges_dev, float in_min, float in_max, float f_min, float f_max,
                    float *output, void *workspace, size_t workspace_bytes, const axc_debug_out *dbg,
-                   int device, void *stream)
+                   int device, void *stream, const axc_epilogue *epilogue = nullptr)
 {
     if (!table || !desc) return AXC_INVALID_ARGUMENT;
     Geom g;
     int rc = resolve_geometry(desc, depthwise, &g);
     if (rc) return rc;
+    if (epilogue) g.ep = Epilogue{epilogue->bias, epilogue->residual, epilogue->relu != 0 ? 1 : 0};
     const long long out_c = depthwise ? (long long)g.C * g.Cout : g.Cout;
     if (g.M * out_c == 0) return AXC_OK;  // empty output: nothing to do
     if (!input || !filter || !output) return AXC_INVALID_ARGUMENT;
@@ -451,6 +453,24 @@ int axc_conv2d_forward(axc_table *table, const axc_conv_desc *desc, const float 
 {
     return axc::forward(false, table, desc, input, filter, nullptr, in_min, in_max, f_min, f_max, output, workspace,
                         workspace_bytes, debug, device, stream);
+}
+
+int axc_conv2d_forward_fused(axc_table *table, const axc_conv_desc *desc, const float *input, const float *filter,
+                             float in_min, float in_max, float f_min, float f_max, const float *ranges,
+                             const axc_epilogue *epilogue, float *output, void *workspace, size_t workspace_bytes,
+                             const axc_debug_out *debug, int device, void *stream)
+{
+    return axc::forward(false, table, desc, input, filter, ranges, in_min, in_max, f_min, f_max, output, workspace,
+                        workspace_bytes, debug, device, stream, epilogue);
+}
+
+int axc_depthwise_conv2d_forward_fused(axc_table *table, const axc_conv_desc *desc, const float *input,
+                                       const float *filter, float in_min, float in_max, float f_min, float f_max,
+                                       const axc_epilogue *epilogue, float *output, void *workspace,
+                                       size_t workspace_bytes, const axc_debug_out *debug, int device, void *stream)
+{
+    return axc::forward(true, table, desc, input, filter, nullptr, in_min, in_max, f_min, f_max, output, workspace,
+                        workspace_bytes, debug, device, stream, epilogue);
 }
 
 int axc_conv2d_forward_device_ranges(axc_table *table, const axc_conv_desc *desc, const float *input,

@@ -19,6 +19,8 @@
 #include <cstdio>
 #include <cstdlib>
 
+#include <cmath>
+
 #include "axc_internal.h"
 #include "axc_sched.h"
 
@@ -53,6 +55,8 @@ struct DenseParams {
     const DevQuant *dq;    // quantisation parameters of the call (workspace header)
     int vec_ok;            // C % 4 == 0 and 16-byte aligned input
     const int *gate;       // when set: run only if *gate != 0 (the scheduled kernel handed the call over)
+    const float *bias;     // fused epilogue: per-channel bias or NULL
+    float floor;           // fused epilogue: y = max(y, floor); 0 = ReLU, -inf = none
 };
 
 __device__ __forceinline__ unsigned quantize_u8(float x, float off, float inv)
@@ -467,6 +471,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
         const int j = j0 + wn * 32 + lane;
         if (j < P.Cout) {
             const float t2 = __fmul_rn(Q.m1, __ldg(P.bsum + j));
+            const float bias_j = P.bias ? __ldg(P.bias + j) : 0.0f;
 #pragma unroll
             for (int i = 0; i < kPixPerLane; ++i) {
                 const long long p = m0 + wm * kPixPerLane + i;
@@ -475,12 +480,34 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
                     const float total = REF ? __int_as_float(acc[i]) : float(acc[i]);
                     const float t0 = __fmul_rn(total, Q.s1s2);
                     const float t1 = __fmul_rn(Q.m2, a_sum);
-                    const float o = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), Q.km1m2);
-                    if (P.output) P.output[p * P.Cout + j] = o;
+                    const float y = __fadd_rn(__fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), Q.km1m2), bias_j);
+                    if (P.output) P.output[p * P.Cout + j] = max_keep_nan(y, P.floor);
                     if (P.acc_out) P.acc_out[p * P.Cout + j] = REF ? __float2int_rz(total) : acc[i];
                 }
             }
         }
+    }
+}
+
+// Shortcut of a residual block: out = out + residual, then the ReLU if asked for - one pass over the output instead
+// of the two of separate element-wise kernels.  (Inside the convolution kernels the extra loads would stall the
+// warps that do the lookups: measured, a 1x1 layer with 64 input channels took 5.0 ms instead of 2.75 ms.)
+__global__ void __launch_bounds__(256) add_residual_kernel(float *__restrict__ out, const float *__restrict__ residual, long long count,
+                                                           int relu)
+{
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthreads = (long long)gridDim.x * blockDim.x;
+    const bool vec = ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(residual)) & 15u) == 0;
+    const long long quads = vec ? count / 4 : 0;
+    for (long long q = tid; q < quads; q += nthreads) {
+        float4 a = reinterpret_cast<const float4 *>(out)[q];
+        const float4 b = __ldg(reinterpret_cast<const float4 *>(residual) + q);
+        a.x = __fadd_rn(a.x, b.x); a.y = __fadd_rn(a.y, b.y); a.z = __fadd_rn(a.z, b.z); a.w = __fadd_rn(a.w, b.w);
+        if (relu) { a.x = fmaxf(a.x, 0.f); a.y = fmaxf(a.y, 0.f); a.z = fmaxf(a.z, 0.f); a.w = fmaxf(a.w, 0.f); }
+        reinterpret_cast<float4 *>(out)[q] = a;
+    }
+    for (long long e = quads * 4 + tid; e < count; e += nthreads) {
+        const float y = __fadd_rn(out[e], __ldg(residual + e));
+        out[e] = relu ? fmaxf(y, 0.f) : y;
     }
 }
 
@@ -573,15 +600,25 @@ int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, con
     P.acc_out = dbg ? dbg->acc : nullptr;
     P.status = status;
     P.gate = gate;
+    P.bias = g.ep.bias;
+    P.floor = (g.ep.relu && !g.ep.residual) ? 0.0f : -INFINITY;
     P.N = g.N; P.H = g.H; P.W = g.W; P.C = g.C; P.KH = g.KH; P.KW = g.KW; P.Cout = g.Cout;
     P.sh = g.sh; P.sw = g.sw; P.dh = g.dh; P.dw = g.dw; P.ph = g.ph; P.pw = g.pw; P.OH = g.OH; P.OW = g.OW;
     P.K = g.K; P.M = g.M;
     P.tiles_n = 0; P.tiles_total = 0;
     P.dq = dq;
     P.vec_ok = (g.C % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
-    if (ref_order) return g.Cout <= 32 ? launch_dense_variant<1, true>(P, di, stream) : launch_dense_variant<2, true>(P, di, stream);
-    if (g.Cout <= 32) return launch_dense_variant<1, false>(P, di, stream);
-    return launch_dense_variant<2, false>(P, di, stream);
+    if (ref_order) rc = g.Cout <= 32 ? launch_dense_variant<1, true>(P, di, stream) : launch_dense_variant<2, true>(P, di, stream);
+    else rc = g.Cout <= 32 ? launch_dense_variant<1, false>(P, di, stream) : launch_dense_variant<2, false>(P, di, stream);
+    if (rc == AXC_OK && g.ep.residual && output) {
+        const long long count = g.M * g.Cout;
+        const long long want = (count / 4 + 255) / 256;
+        const unsigned blocks = unsigned(want < (long long)di.sm_count * 8 ? (want > 0 ? want : 1) : (long long)di.sm_count * 8);
+        add_residual_kernel<<<blocks, 256, 0, stream>>>(output, g.ep.residual, count, g.ep.relu);
+        AXC_CUDA(cudaGetLastError());
+        count_launch();
+    }
+    return rc;
 }
 
 }  // namespace axc

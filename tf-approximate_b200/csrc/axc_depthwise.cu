@@ -47,6 +47,7 @@ struct DwParams {
     int bands;             // bands of output rows per image
     int units_per_group;   // N * bands
     int wave, sets;        // CTAs per set (= channel groups served at a time) and sets: grid = wave * sets
+    Epilogue ep;           // fused additions to the output
 };
 
 __device__ __forceinline__ unsigned dw_quantize_u8(float x, float off, float inv)
@@ -106,11 +107,12 @@ __device__ __forceinline__ void dw_fill_table(const uint16_t *lut, int tid, int 
     }
 }
 
-__device__ __forceinline__ float dw_epilogue(int acc, float a_sum, float t2, const DwParams &P)
+__device__ __forceinline__ float dw_epilogue(int acc, float a_sum, float t2, const DwParams &P, int oc, long long idx)
 {
     const float t0 = __fmul_rn(float(acc), P.s1s2);
     const float t1 = __fmul_rn(P.m2, a_sum);
-    return __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), P.km1m2);
+    const float y = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), P.km1m2);
+    return apply_epilogue(y, P.ep, P.ep.bias ? __ldg(P.ep.bias + oc) : 0.0f, idx);
 }
 
 // Any KH x KW, stride and dilation: every tap is fetched for every output.
@@ -156,7 +158,7 @@ __global__ void __launch_bounds__(kDwThreads, 1) depthwise_generic_kernel(const 
                 acc += int(dw_lds_u16(__byte_perm(w, qa, 0x3240)));
             }
             const long long o = (((long long)n * P.OH + oh) * P.OW + ow) * P.OC + oc;
-            P.output[o] = dw_epilogue(acc, a_sum, t2, P);
+            P.output[o] = dw_epilogue(acc, a_sum, t2, P, oc, o);
             if (P.acc_out) P.acc_out[o] = acc;
         }
     }
@@ -303,7 +305,7 @@ __global__ void __launch_bounds__(kDwThreads, 1) depthwise_3x3_kernel(const DwPa
                     } else {
                         a_sum = dw_window<S, 2>(xf, xq, wp, &acc);
                     }
-                    P.output[outoff] = dw_epilogue(acc, a_sum, t2, P);
+                    P.output[outoff] = dw_epilogue(acc, a_sum, t2, P, oc, outoff);
                     if (P.acc_out) P.acc_out[outoff] = acc;
                     outoff += P.OC;
                 }
@@ -479,6 +481,7 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
         const bool oc_ok = oc < P.OC;
         const int cin = oc_ok ? oc / P.mult : 0;
         const float t2 = oc_ok ? __fmul_rn(P.m1, __ldg(P.bsum + oc)) : 0.0f;
+        const float bias_j = (oc_ok && P.ep.bias) ? __ldg(P.ep.bias + oc) : 0.0f;
 
         for (int w = w_begin + warp; w < w_end; w += kTabWarps) {
             const int n = w / P.bands;
@@ -494,6 +497,7 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
             const long long o0 = ((long long)n * P.OH + oy0) * (long long)(P.OW * P.OC) + (oc_ok ? oc : 0);
             const char *out0 = reinterpret_cast<const char *>(P.output + o0);
             const char *acc0 = DBG ? reinterpret_cast<const char *>(P.acc_out + o0) : nullptr;
+            const char *res0 = P.ep.residual ? reinterpret_cast<const char *>(P.ep.residual + o0) : nullptr;
 
             int acc[R][S == 1 ? 3 : 2];
             float xf[IR][3];      // raw taps of the columns in flight: S == 1 ring slot = column % 3; S == 2: 0 / 1 = even
@@ -570,7 +574,11 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
                     }
                     const float t0 = __fmul_rn(float(acc[r][sa]), s1s2);
                     const float t1 = __fmul_rn(m2, a);
-                    const float y = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), km1m2);
+                    float y = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), km1m2);
+                    if (P.ep.bias) y = __fadd_rn(y, bias_j);
+                    if (P.ep.residual && r < rows_here)
+                        y = __fadd_rn(y, __ldg(reinterpret_cast<const float *>(dw_ptr_mad(dw_ptr_mad(res0, unsigned(ox), opix_bytes), unsigned(r), orow_bytes))));
+                    if (P.ep.relu) y = fmaxf(y, 0.0f);
                     // predicated stores (no branch): rows_here is 0 for a lane without a channel
                     asm volatile("{\n\t.reg .pred p;\n\tsetp.gt.s32 p, %2, %3;\n\t@p st.global.f32 [%0], %1;\n\t}"
                                  ::"l"(dw_ptr_mad(outp, unsigned(r), orow_bytes)), "f"(y), "r"(rows_here), "r"(r) : "memory");
@@ -857,6 +865,7 @@ int launch_depthwise(const uint16_t *lut_dev, const Geom &g, const Quant &q, con
     const bool k3 = small && g.KH == 3 && g.KW == 3 && g.dh == 1 && g.dw == 1 && g.sh == g.sw;
     P.filter = filter; P.f_off = q.f_off; P.f_inv = q.f_inv;
     P.bands = 0; P.units_per_group = 0; P.wave = 0; P.sets = 0;
+    P.ep = g.ep;
     // The expanded-table kernel pays about 74 000 lookups per CTA and channel group for its table: worth it from
     // some ten thousand outputs per group on.
     if (k3 && (g.sw == 1 || g.sw == 2) && g.M * 32 >= kTabMinOutputsPerGroup && di.max_smem_optin >= int(kTabSmem) &&

@@ -15,6 +15,31 @@ struct Quant {
     float s1s2, m1, m2, m1m2;
 };
 
+// Optional additions fused into the dequantisation (axc_epilogue of the C ABI).
+struct Epilogue {
+    const float *bias;      // [out channels] or NULL
+    const float *residual;  // output shape or NULL
+    int relu;
+};
+
+// y after the fused epilogue; `idx` = element index of the output, `bias_j` = bias of its channel (0 without one)
+__device__ __forceinline__ float apply_epilogue(float y, const Epilogue &ep, float bias_j, long long idx)
+{
+    if (ep.bias) y = __fadd_rn(y, bias_j);
+    if (ep.residual) y = __fadd_rn(y, __ldg(ep.residual + idx));
+    if (ep.relu) y = fmaxf(y, 0.0f);
+    return y;
+}
+
+// max(y, floor) that keeps a NaN: the fused ReLU is this with floor = 0, no ReLU is floor = -inf - one instruction
+// either way, no branch and no select in the kernels' epilogues.
+__device__ __forceinline__ float max_keep_nan(float y, float floor)
+{
+    float d;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(y), "f"(floor));
+    return d;
+}
+
 // Resolved geometry (TensorFlow window arithmetic applied).
 struct Geom {
     int N, H, W, C;
@@ -26,6 +51,7 @@ struct Geom {
     long long M;       // N*OH*OW
     int accum;         // AXC_ACCUM_*
     int plan;          // AXC_PLAN_*
+    Epilogue ep;       // set by the entry point after resolve_geometry
 };
 
 void var_quant_props(float min_v, float max_v, float *scale, float *inv, float *offset);

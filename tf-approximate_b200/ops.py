@@ -181,7 +181,7 @@ def workspace_bytes(input_shape, filter_shape, strides, padding, dilations=(1, 1
 
 def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
              mul_map_file, padding, explicit_paddings, data_format, dilations, out, debug, accumulate="exact",
-             plan="keep", workspace=None, ranges=None):
+             plan="keep", workspace=None, ranges=None, bias=None, residual=None, relu=False):
     L = _lib.load()
     if not isinstance(input, torch.Tensor) or not isinstance(filter, torch.Tensor):
         raise InvalidArgumentError("input and filter must be torch tensors")
@@ -233,18 +233,32 @@ def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_
     if ranges is not None and (ranges.dtype != torch.float32 or ranges.device != dev or ranges.numel() != 4
                                or not ranges.is_contiguous()):
         raise InvalidArgumentError("ranges must be four contiguous fp32 values on the input's device")
+    # fused additions to the output (bias of the layer, shortcut of a residual block, ReLU)
+    ep_ptr, keep = None, []
+    if bias is not None or residual is not None or relu:
+        for name, t, shape in (("bias", bias, (oshape[3],)), ("residual", residual, oshape)):
+            if t is not None and (t.dtype != torch.float32 or t.device != dev or tuple(t.shape) != shape):
+                raise InvalidArgumentError("%s must be a fp32 tensor of shape %s on the input's device" % (name, shape))
+        keep = [t.contiguous() if t is not None else None for t in (bias, residual)]
+        ep = _lib.Epilogue(keep[0].data_ptr() if keep[0] is not None else None,
+                           keep[1].data_ptr() if keep[1] is not None else None, 1 if relu else 0)
+        ep_ptr = C.byref(ep)
     if not depthwise and (ranges is not None or all(isinstance(v, torch.Tensor) and v.is_cuda for v in four)):
         # the four scalars already live on the GPU (e.g. fresh reductions): hand them over as they are, no
         # device-to-host synchronisation
         r = ranges if ranges is not None else torch.stack([v.reshape(()).to(torch.float32) for v in four]).contiguous()
-        st = L.axc_conv2d_forward_device_ranges(table.handle, C.byref(d), x.data_ptr(), f.data_ptr(), r.data_ptr(),
-                                                out.data_ptr(), ws.data_ptr(), ws.numel(), dbg_ptr, dev_index,
-                                                C.c_void_p(stream))
+        st = L.axc_conv2d_forward_fused(table.handle, C.byref(d), x.data_ptr(), f.data_ptr(), 0.0, 0.0, 0.0, 0.0, r.data_ptr(),
+                                        ep_ptr, out.data_ptr(), ws.data_ptr(), ws.numel(), dbg_ptr, dev_index,
+                                        C.c_void_p(stream))
+    elif depthwise:
+        st = L.axc_depthwise_conv2d_forward_fused(table.handle, C.byref(d), x.data_ptr(), f.data_ptr(), _scalar(input_min),
+                                                  _scalar(input_max), _scalar(filter_min), _scalar(filter_max), ep_ptr,
+                                                  out.data_ptr(), ws.data_ptr(), ws.numel(), dbg_ptr, dev_index,
+                                                  C.c_void_p(stream))
     else:
-        fwd = L.axc_depthwise_conv2d_forward if depthwise else L.axc_conv2d_forward
-        st = fwd(table.handle, C.byref(d), x.data_ptr(), f.data_ptr(), _scalar(input_min), _scalar(input_max),
-                 _scalar(filter_min), _scalar(filter_max), out.data_ptr(), ws.data_ptr(), ws.numel(), dbg_ptr,
-                 dev_index, C.c_void_p(stream))
+        st = L.axc_conv2d_forward_fused(table.handle, C.byref(d), x.data_ptr(), f.data_ptr(), _scalar(input_min),
+                                        _scalar(input_max), _scalar(filter_min), _scalar(filter_max), None, ep_ptr,
+                                        out.data_ptr(), ws.data_ptr(), ws.numel(), dbg_ptr, dev_index, C.c_void_p(stream))
     raise_for_status(st, "ApproxConv2D", _cuda_detail() if st == 100 else "")
     if debug:
         if not depthwise:
@@ -264,7 +278,7 @@ def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_
 def approx_conv2d_with_min_max_vars(input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
                                     mul_map_file, padding, explicit_paddings=(), data_format="NHWC",
                                     dilations=(1, 1, 1, 1), name=None, out=None, debug=False, accumulate="exact",
-                                    plan="keep", workspace=None, ranges=None):
+                                    plan="keep", workspace=None, ranges=None, bias=None, residual=None, relu=False):
     """Forward pass of `ApproxConv2DWithMinMaxVars`.
 
     input [N,H,W,C] and filter [KH,KW,C,Cout] are fp32 CUDA tensors; the four min/max values are
@@ -281,19 +295,23 @@ def approx_conv2d_with_min_max_vars(input, filter, input_min, input_max, filter_
     unchanged; "none" is for filters that change every call (training).  workspace: a uint8 CUDA tensor of at least
     `workspace_bytes(...)` bytes that the caller keeps for this layer (default: a cache keyed by the filter's
     address).  ranges: the four range scalars as one fp32 CUDA tensor {input_min, input_max, filter_min,
-    filter_max} (then the four positional range arguments are ignored and may be None)."""
+    filter_max} (then the four positional range arguments are ignored and may be None).
+
+    bias [Cout], residual (a tensor of the output's shape) and relu are fused into the kernel's dequantisation:
+    y = conv; y += bias; y += residual; y = max(y, 0) - with the bits of the same steps done by separate kernels."""
     return _forward(False, input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
                     mul_map_file, padding, list(explicit_paddings), data_format, list(dilations), out, debug, accumulate,
-                    plan, workspace, ranges)
+                    plan, workspace, ranges, bias, residual, relu)
 
 
 def approx_depthwise_conv2d_with_min_max_vars(input, filter, input_min, input_max, filter_min, filter_max, strides,
                                               num_bits, mul_map_file, padding, explicit_paddings=(),
                                               data_format="NHWC", dilations=(1, 1, 1, 1), name=None, out=None,
-                                              debug=False):
+                                              debug=False, bias=None, residual=None, relu=False):
     """Depthwise variant: filter [KH,KW,C,mult] (DepthwiseConv2dNative layout), output [N,OH,OW,C*mult]."""
     return _forward(True, input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
-                    mul_map_file, padding, list(explicit_paddings), data_format, list(dilations), out, debug)
+                    mul_map_file, padding, list(explicit_paddings), data_format, list(dilations), out, debug,
+                    bias=bias, residual=residual, relu=relu)
 
 
 def ax_conv2d(input, filter, min_input, max_input, min_filter, max_filter, strides, padding, table="",

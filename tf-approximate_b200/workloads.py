@@ -150,33 +150,44 @@ class Network:
     def io_bytes(self, batch):
         return sum(conv_io_bytes(s, h, batch) for s, h in self.convs)
 
-    def forward(self, x, conv, relu, maxpool3s2):
-        """conv(i, x) -> y;  relu(x) -> x;  maxpool3s2(x) -> x (3x3, stride 2, SAME)."""
+    def forward(self, x, conv, relu, maxpool3s2, fused=False):
+        """conv(i, x) -> y;  relu(x) -> x;  maxpool3s2(x) -> x (3x3, stride 2, SAME).
+        fused=True: the backend's conv takes (i, x, relu=bool, residual=tensor or None) and applies the shortcut
+        addition and the ReLU itself (the CUDA op fuses them into its dequantisation); otherwise they are separate
+        steps here.  Both orders of evaluation are the same arithmetic: relu(conv + shortcut)."""
         ix = self.index
+
+        def c(i, x, act=False, res=None):
+            if fused:
+                return conv(i, x, relu=act, residual=res)
+            y = conv(i, x)
+            if res is not None:
+                y = y + res
+            return relu(y) if act else y
+
         if self.kind == "resnet50":
-            x = maxpool3s2(relu(conv(ix["stem"], x)))
+            x = maxpool3s2(c(ix["stem"], x, act=True))
             for stage, b, width, cout, stride, proj in resnet50_blocks():
                 tag = "s%db%d" % (stage + 1, b)
-                y = relu(conv(ix[tag + "_1x1a"], x))
-                y = relu(conv(ix[tag + "_3x3"], y))
-                y = conv(ix[tag + "_1x1b"], y)
-                sc = conv(ix[tag + "_proj"], x) if proj else x
-                x = relu(y + sc)
+                y = c(ix[tag + "_1x1a"], x, act=True)
+                y = c(ix[tag + "_3x3"], y, act=True)
+                sc = c(ix[tag + "_proj"], x) if proj else x
+                x = c(ix[tag + "_1x1b"], y, act=True, res=sc)
             return x
         if self.kind == "resnet20":
-            x = relu(conv(ix["stem"], x))
+            x = c(ix["stem"], x, act=True)
             for stage in range(3):
                 for b in range(3):
                     tag = "s%db%d" % (stage + 1, b)
-                    y = relu(conv(ix[tag + "_a"], x))
-                    y = conv(ix[tag + "_b"], y)
-                    if y.shape != x.shape:  # option-A shortcut: subsample, zero-pad the new channels
-                        xs = x[:, ::2, ::2, :]
-                        x = _pad_channels(xs, y.shape[3])
-                    x = relu(y + x)
+                    y = c(ix[tag + "_a"], x, act=True)
+                    stride = self.convs[ix[tag + "_a"]][0].stride
+                    if stride != 1 or self.convs[ix[tag + "_a"]][0].cin != self.convs[ix[tag + "_a"]][0].cout:
+                        # option-A shortcut: subsample, zero-pad the new channels
+                        x = _pad_channels(x[:, ::stride, ::stride, :], self.convs[ix[tag + "_a"]][0].cout)
+                    x = c(ix[tag + "_b"], y, act=True, res=x)
             return x
         for i in range(len(self.convs)):
-            x = relu(conv(i, x))
+            x = c(i, x, act=True)
         return x
 
 
@@ -235,7 +246,7 @@ class GpuRunner:
         self.calibrating = False
         self.conv_events = None   # when a list: (start, end) CUDA events around every conv call
 
-    def _conv(self, i, x):
+    def _conv(self, i, x, relu=False, residual=None):
         spec, _ = self.net.convs[i]
         if self.calibrating:
             self.in_ranges[i] = (float(x.min()), float(x.max()))
@@ -247,8 +258,10 @@ class GpuRunner:
             e0 = self.torch.cuda.Event(enable_timing=True)
             e1 = self.torch.cuda.Event(enable_timing=True)
             e0.record()
+        if residual is not None and not residual.is_contiguous():
+            residual = residual.contiguous()
         y = fn(x, self.filters[i], lo, hi, self.f_ranges[i][0], self.f_ranges[i][1],
-               [1, spec.stride, spec.stride, 1], 8, table, "SAME")
+               [1, spec.stride, spec.stride, 1], 8, table, "SAME", relu=relu, residual=residual)
         if self.conv_events is not None:
             e1.record()
             self.conv_events.append((i, e0, e1))
@@ -261,8 +274,9 @@ class GpuRunner:
         finally:
             self.calibrating = False
 
-    def forward(self, x):
-        return self.net.forward(x, self._conv, self.torch.relu, torch_maxpool3s2)
+    def forward(self, x, fused=True):
+        """fused: shortcut additions and ReLUs inside the convolution kernels (default) or as separate torch kernels."""
+        return self.net.forward(x, self._conv, self.torch.relu, torch_maxpool3s2, fused=fused)
 
 
 class CpuRunner:
