@@ -281,6 +281,13 @@ const char *axc_status_string(int status);
 int axc_last_cuda_error(void);
 /* Number of kernels this library has launched in the calling process (monotonic). */
 uint64_t axc_launch_count(void);
+/* Debug flavour only (libaxconv_check.so, built with -DAXC_BOUNDS_CHECK): every shared-memory address the kernels
+ * compute and every global index they form is checked before use; a violation is counted and skipped, never a trap.
+ * out4 = {violations since the last call, site number of the first, its offending value: low word, high word};
+ * reading clears the record.  Blocks until the device is idle.  In the normal build: AXC_UNIMPLEMENTED.  No
+ * counterpart in the reference. */
+int axc_debug_bounds_record(int device, uint32_t out4[4]);
+
 /* Measures what one SM sustains in conflict-free 16-bit shared-memory loads - the operation a table MAC of the
  * dense kernels costs (the reference does the same lookup through a texture fetch,
  * tf2/src/cuda/approx_nn_conv_kernels.cu:471-472) - in lookups per clock and SM; 32 by the construction of the

@@ -13,7 +13,7 @@ SYMBOLS = [
     "axc_conv2d_workspace_bytes", "axc_depthwise_conv2d_workspace_bytes", "axc_conv2d_plan_info",
     "axc_conv2d_forward", "axc_conv2d_forward_device_ranges", "axc_depthwise_conv2d_forward",
     "axc_depthwise_conv2d_forward_noalloc", "axc_depthwise_conv2d_status",
-    "axc_quant_props", "axc_status_string", "axc_last_cuda_error", "axc_launch_count", "axc_measure_lookup_peak",
+    "axc_quant_props", "axc_status_string", "axc_last_cuda_error", "axc_launch_count", "axc_measure_lookup_peak", "axc_debug_bounds_record",
     "axc_conv2d_forward_fused", "axc_depthwise_conv2d_forward_fused", "axc_tensor_range", "axc_fake_quant", "axc_conv2d_forward_sharded", "axc_gather_outputs",
     "axc_qconv2d_workspace_bytes", "axc_qconv2d_forward", "axc_quantized_zero_point", "axc_quantized_output_range",
 ]
@@ -45,7 +45,9 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    path = _build.LIB
+    # AXC_LIBRARY_FLAVOUR=check loads the debug flavour with bounds checks (libaxconv_check.so)
+    check = os.environ.get("AXC_LIBRARY_FLAVOUR", "") == "check"
+    path = _build.LIB_CHECK if check else _build.LIB
     if not os.path.exists(path):
         raise RuntimeError("libaxconv.so is not built (%s): run `python -c \"import __graft_entry__ as g; "
                            "g.build()\"` at the repository root; there is no CPU fallback" % path)
@@ -93,6 +95,7 @@ def load():
     L.axc_status_string.restype = C.c_char_p
     L.axc_last_cuda_error.restype = C.c_int
     L.axc_launch_count.restype = C.c_uint64
+    L.axc_debug_bounds_record.argtypes = [C.c_int, C.POINTER(C.c_uint32)]
     L.axc_measure_lookup_peak.argtypes = [C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.POINTER(C.c_double)]
     _lib = L
     return L

@@ -546,6 +546,33 @@ int axc_depthwise_conv2d_status(const axc_conv_desc *desc, const void *workspace
     return axc::depthwise_status(g, workspace, status, device, cudaStream_t(stream));
 }
 
+int axc_debug_bounds_record(int device, uint32_t out4[4])
+{
+    if (!out4) return AXC_INVALID_ARGUMENT;
+#ifndef AXC_BOUNDS_CHECK
+    (void)device;
+    out4[0] = out4[1] = out4[2] = out4[3] = 0;
+    return AXC_UNIMPLEMENTED;
+#else
+    int prev = 0;
+    AXC_CUDA(cudaGetDevice(&prev));
+    if (prev != device) AXC_CUDA(cudaSetDevice(device));
+    cudaError_t e = cudaDeviceSynchronize();
+    unsigned parts[3][4] = {};
+    int rc = e == cudaSuccess ? AXC_OK : axc::cuda_failed(e);
+    if (rc == AXC_OK) rc = axc::bounds_record_sched(parts[0]);
+    if (rc == AXC_OK) rc = axc::bounds_record_conv(parts[1]);
+    if (rc == AXC_OK) rc = axc::bounds_record_depthwise(parts[2]);
+    if (prev != device) cudaSetDevice(prev);
+    out4[0] = out4[1] = out4[2] = out4[3] = 0;
+    for (int t = 0; t < 3; ++t) {
+        if (parts[t][0] != 0 && out4[0] == 0) { out4[1] = parts[t][1]; out4[2] = parts[t][2]; out4[3] = parts[t][3]; }
+        out4[0] += parts[t][0];
+    }
+    return rc;
+#endif
+}
+
 int axc_quant_props(float min_value, float max_value, float out3[3])
 {
     if (!out3) return AXC_INVALID_ARGUMENT;

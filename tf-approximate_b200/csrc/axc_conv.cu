@@ -68,8 +68,10 @@ __device__ __forceinline__ unsigned quantize_u8(float x, float off, float inv)
     return u > 255u ? 255u : u;
 }
 
+// Shared-memory accessors; the debug flavour checks every address first (table lookups: planes and zero word).
 __device__ __forceinline__ unsigned lds_u16(unsigned addr)
 {
+    if (!AXC_SHARED_OK(addr, 2u, kLutBase, kSmemEnd, 201u)) return 0u;
     unsigned v;
     asm("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
@@ -77,6 +79,7 @@ __device__ __forceinline__ unsigned lds_u16(unsigned addr)
 
 __device__ __forceinline__ uint4 lds_v4(unsigned addr)
 {
+    if (!AXC_SHARED_OK(addr, 16u, 0u, kSmemEnd, 202u)) return make_uint4(0, 0, 0, 0);
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
@@ -84,21 +87,25 @@ __device__ __forceinline__ uint4 lds_v4(unsigned addr)
 
 __device__ __forceinline__ void sts_u32(unsigned addr, unsigned v)
 {
+    if (!AXC_SHARED_OK(addr, 4u, 0u, kSmemEnd, 203u)) return;
     asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 
 __device__ __forceinline__ void sts_v4(unsigned addr, uint4 v)
 {
+    if (!AXC_SHARED_OK(addr, 16u, 0u, kSmemEnd, 204u)) return;
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
 __device__ __forceinline__ void sts_f32(unsigned addr, float v)
 {
+    if (!AXC_SHARED_OK(addr, 4u, 0u, kSmemEnd, 205u)) return;
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
 __device__ __forceinline__ float lds_f32(unsigned addr)
 {
+    if (!AXC_SHARED_OK(addr, 4u, 0u, kSmemEnd, 206u)) return 0.0f;
     float v;
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
     return v;
@@ -295,7 +302,8 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
                     for (int s = 0; s < PIX_SLOTS; ++s) {
                         const int iy = piy[s] + dy, ix = pix[s] + dx;
                         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (l0 < P.K && iy >= 0 && iy < P.H && ix >= 0 && ix < P.W)
+                        if (l0 < P.K && iy >= 0 && iy < P.H && ix >= 0 && ix < P.W &&
+                            AXC_GLOBAL_OK(pbase[s] + toff + 3, (long long)P.N * P.H * P.W * P.C, 211u))
                             v = __ldg(reinterpret_cast<const float4 *>(P.input + pbase[s] + toff));
                         a_stage[h * PIX_SLOTS + s] = v;
                     }
@@ -314,7 +322,9 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
                         for (int s = 0; s < PIX_SLOTS; ++s) {
                             const int iy = piy[s] + dy, ix = pix[s] + dx;
                             float v = 0.f;
-                            if (l < P.K && iy >= 0 && iy < P.H && ix >= 0 && ix < P.W) v = __ldg(P.input + pbase[s] + toff);
+                            if (l < P.K && iy >= 0 && iy < P.H && ix >= 0 && ix < P.W &&
+                                AXC_GLOBAL_OK(pbase[s] + toff, (long long)P.N * P.H * P.W * P.C, 212u))
+                                v = __ldg(P.input + pbase[s] + toff);
                             vals[s][e] = v;
                         }
                     }
@@ -475,7 +485,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_kernel(const DenseParams P)
 #pragma unroll
             for (int i = 0; i < kPixPerLane; ++i) {
                 const long long p = m0 + wm * kPixPerLane + i;
-                if (p < P.M) {
+                if (p < P.M && AXC_GLOBAL_OK(p * P.Cout + j, P.M * P.Cout, 213u)) {
                     const float a_sum = lds_f32(sAsum + (wm * kPixPerLane + i) * 4);
                     const float total = REF ? __int_as_float(acc[i]) : float(acc[i]);
                     const float t0 = __fmul_rn(total, Q.s1s2);
@@ -531,6 +541,8 @@ int launch_dense_variant(const DenseParams &P, const DeviceInfo &di, cudaStream_
 
 // 0 = bank-scheduled kernel with the common-K kernel as its device-side fallback (default),
 // 1 = common-K kernel only.  Read once from AXC_DENSE_VARIANT.
+AXC_DEFINE_BOUNDS_READER(bounds_record_conv)
+
 static int dense_variant()
 {
     static int v = -1;

@@ -528,8 +528,11 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
                 }
                 const unsigned a = my_stage0 + unsigned(st) * stage_bytes + lane_off;
 #pragma unroll
-                for (int i = 0; i < IR; ++i)
-                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(xf[i][slot]) : "r"(a + unsigned(i) * 128u));
+                for (int i = 0; i < IR; ++i) {
+                    xf[i][slot] = 0.0f;
+                    if (AXC_SHARED_OK(a + unsigned(i) * 128u, 4u, stages0, bars0, 307u))
+                        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(xf[i][slot]) : "r"(a + unsigned(i) * 128u));
+                }
             };
 
             // raw taps of input column `c` (relative: image column c - pw); zeros outside the image
@@ -580,6 +583,7 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
                         y = __fadd_rn(y, __ldg(reinterpret_cast<const float *>(dw_ptr_mad(dw_ptr_mad(res0, unsigned(ox), opix_bytes), unsigned(r), orow_bytes))));
                     if (P.ep.relu) y = fmaxf(y, 0.0f);
                     // predicated stores (no branch): rows_here is 0 for a lane without a channel
+                    if (AXC_GLOBAL_OK(r < rows_here ? o0 + (long long)r * P.OW * P.OC + (long long)ox * P.OC : 0, (long long)P.N * P.OH * P.OW * P.OC, 313u))
                     asm volatile("{\n\t.reg .pred p;\n\tsetp.gt.s32 p, %2, %3;\n\t@p st.global.f32 [%0], %1;\n\t}"
                                  ::"l"(dw_ptr_mad(outp, unsigned(r), orow_bytes)), "f"(y), "r"(rows_here), "r"(r) : "memory");
                     if (DBG)
@@ -608,16 +612,18 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
 #pragma unroll
                     for (int i = 0; i < IR; ++i) {
                         const unsigned qa = dw_q_u8(xf[i][J], in_off, in_inv);
-                        uint4 t;
-                        asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t.x), "=r"(t.y), "=r"(t.z), "=r"(t.w) : "r"(lane16 + qa * 512u));
+                        uint4 t = make_uint4(0, 0, 0, 0);
+                        if (AXC_SHARED_OK(lane16 + qa * 512u, 16u, tab16, tab16 + kTab16Bytes, 301u))
+                            asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t.x), "=r"(t.y), "=r"(t.z), "=r"(t.w) : "r"(lane16 + qa * 512u));
                         if (i < R) {                                   // ky = 0 -> output row i
                             acc[i][s0] = dw_add_lo(t.x, 0);
                             acc[i][s1] = dw_add_lo(t.z, acc[i][s1]);
                             acc[i][s2] = dw_add_hi(t.x, acc[i][s2]);
                         }
                         if (i >= 1 && i - 1 < R) {                     // ky = 1 -> output row i - 1
-                            unsigned t11;
-                            asm("ld.shared.u32 %0, [%1];" : "=r"(t11) : "r"(lane4 + qa * 128u));
+                            unsigned t11 = 0;
+                            if (AXC_SHARED_OK(lane4 + qa * 128u, 4u, tab4, tab4 + kTab4Bytes, 302u))
+                                asm("ld.shared.u32 %0, [%1];" : "=r"(t11) : "r"(lane4 + qa * 128u));
                             acc[i - 1][s0] = dw_add_lo(t.w, acc[i - 1][s0]);
                             acc[i - 1][s1] += int(t11);
                             acc[i - 1][s2] = dw_add_hi(t.w, acc[i - 1][s2]);
@@ -662,8 +668,9 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
                     for (int i = 0; i < IR; ++i) {
                         const unsigned qa = dw_q_u8(xf[i][J], in_off, in_inv);
                         if ((i & 1) == 0) {
-                            unsigned tx, ty;
-                            asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(tx), "=r"(ty) : "r"(lane16 + qa * 512u));
+                            unsigned tx = 0, ty = 0;
+                            if (AXC_SHARED_OK(lane16 + qa * 512u, 8u, tab16, tab16 + kTab16Bytes, 303u))
+                                asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(tx), "=r"(ty) : "r"(lane16 + qa * 512u));
                             if (i / 2 < R) {
                                 acc[i / 2][J] = dw_add_lo(tx, 0);                                  // t00 starts the sum
                                 acc[i / 2][J ^ 1] = dw_add_hi(tx, acc[i / 2][J ^ 1]);              // t02
@@ -673,8 +680,9 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
                                 acc[i / 2 - 1][J ^ 1] = dw_add_hi(ty, acc[i / 2 - 1][J ^ 1]);      // t22
                             }
                         } else {
-                            unsigned tw;
-                            asm("ld.shared.u32 %0, [%1];" : "=r"(tw) : "r"(lane16 + qa * 512u + 12u));
+                            unsigned tw = 0;
+                            if (AXC_SHARED_OK(lane16 + qa * 512u + 12u, 4u, tab16, tab16 + kTab16Bytes, 304u))
+                                asm("ld.shared.u32 %0, [%1];" : "=r"(tw) : "r"(lane16 + qa * 512u + 12u));
                             acc[i / 2][J] = dw_add_lo(tw, acc[i / 2][J]);                          // t10
                             acc[i / 2][J ^ 1] = dw_add_hi(tw, acc[i / 2][J ^ 1]);                  // t12
                         }
@@ -696,13 +704,15 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
                     for (int i = 0; i < IR; ++i) {
                         const unsigned qa = dw_q_u8(xf[i][2], in_off, in_inv);
                         if ((i & 1) == 0) {
-                            unsigned tz;
-                            asm("ld.shared.u32 %0, [%1];" : "=r"(tz) : "r"(lane16 + qa * 512u + 8u));
+                            unsigned tz = 0;
+                            if (AXC_SHARED_OK(lane16 + qa * 512u + 8u, 4u, tab16, tab16 + kTab16Bytes, 305u))
+                                asm("ld.shared.u32 %0, [%1];" : "=r"(tz) : "r"(lane16 + qa * 512u + 8u));
                             if (i / 2 < R) acc[i / 2][J] = dw_add_lo(tz, acc[i / 2][J]);           // t01
                             if (i >= 2) acc[i / 2 - 1][J] = dw_add_hi(tz, acc[i / 2 - 1][J]);      // t21
                         } else {
-                            unsigned t11;
-                            asm("ld.shared.u32 %0, [%1];" : "=r"(t11) : "r"(lane4 + qa * 128u));
+                            unsigned t11 = 0;
+                            if (AXC_SHARED_OK(lane4 + qa * 128u, 4u, tab4, tab4 + kTab4Bytes, 306u))
+                                asm("ld.shared.u32 %0, [%1];" : "=r"(t11) : "r"(lane4 + qa * 128u));
                             acc[i / 2][J] += int(t11);
                         }
                     }
@@ -906,6 +916,8 @@ int static_scratch_address(int device, void **out)
 }
 
 }  // namespace
+
+AXC_DEFINE_BOUNDS_READER(bounds_record_depthwise)
 
 int depthwise_status(const Geom &g, const void *workspace, int32_t *status, int device, cudaStream_t stream)
 {

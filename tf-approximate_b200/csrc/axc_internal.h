@@ -5,7 +5,69 @@
 
 #include "axconv.h"
 
+// ---- debug flavour with bounds checks (-DAXC_BOUNDS_CHECK, libaxconv_check.so) ---------------------------------
+// Every shared-memory address the kernels compute and every global index they form from the launch parameters is
+// checked before use.  A violation is counted, the first one is recorded (site number and offending value) and the
+// access is skipped (loads give 0): the kernel finishes, nothing traps, and axc_debug_bounds_record() reports.  In the
+// normal build the macros are `true` and cost nothing.
+#ifdef AXC_BOUNDS_CHECK
 namespace axc {
+// one record per translation unit (the library is built without relocatable device code):
+// {violations, site of the first, its value low word, high word}
+static __device__ unsigned g_bounds_record[4];
+__device__ __forceinline__ bool bounds_note(bool ok, unsigned site, unsigned long long value)
+{
+    if (!ok && atomicAdd(&g_bounds_record[0], 1u) == 0u) {
+        g_bounds_record[1] = site;
+        g_bounds_record[2] = unsigned(value);
+        g_bounds_record[3] = unsigned(value >> 32);
+    }
+    return ok;
+}
+// `bytes` (a power of two) at the shared-window address `addr`: inside [lo, hi) and aligned
+__device__ __forceinline__ bool shared_ok(unsigned addr, unsigned bytes, unsigned lo, unsigned hi, unsigned site)
+{
+    unsigned window;
+    asm("mov.u32 %0, %%aggr_smem_size;" : "=r"(window));      // user + reserved shared memory of this CTA
+    hi = hi < window ? hi : window;
+    return bounds_note(addr >= lo && addr + bytes <= hi && (addr & (bytes - 1u)) == 0u, site, addr);
+}
+__device__ __forceinline__ bool global_ok(long long index, long long count, unsigned site)
+{
+    return bounds_note(index >= 0 && index < count, site, (unsigned long long)index);
+}
+}  // namespace axc
+#define AXC_SHARED_OK(addr, bytes, lo, hi, site) (::axc::shared_ok((addr), (bytes), (lo), (hi), (site)))
+#define AXC_GLOBAL_OK(index, count, site) (::axc::global_ok((index), (count), (site)))
+#else
+#define AXC_SHARED_OK(addr, bytes, lo, hi, site) (true)
+#define AXC_GLOBAL_OK(index, count, site) (true)
+#endif
+
+namespace axc {
+
+// Reads and clears this translation unit's bounds record (all zeros in the normal build).  Defined once per .cu file
+// that has checked kernels, under its own name.
+#ifdef AXC_BOUNDS_CHECK
+#define AXC_DEFINE_BOUNDS_READER(name)                                                                   \
+    int name(unsigned out4[4])                                                                           \
+    {                                                                                                    \
+        const unsigned zero[4] = {0, 0, 0, 0};                                                           \
+        AXC_CUDA(cudaMemcpyFromSymbol(out4, g_bounds_record, sizeof(zero)));                             \
+        AXC_CUDA(cudaMemcpyToSymbol(g_bounds_record, zero, sizeof(zero)));                               \
+        return AXC_OK;                                                                                   \
+    }
+#else
+#define AXC_DEFINE_BOUNDS_READER(name)                \
+    int name(unsigned out4[4])                        \
+    {                                                 \
+        out4[0] = out4[1] = out4[2] = out4[3] = 0;    \
+        return AXC_OK;                                \
+    }
+#endif
+int bounds_record_sched(unsigned out4[4]);
+int bounds_record_conv(unsigned out4[4]);
+int bounds_record_depthwise(unsigned out4[4]);
 
 // Quantisation state of one call: what the reference keeps in
 // BaseTableApproxOpType_t::quantProps (tf2/src/approx_ops_types.h:84-96).

@@ -65,32 +65,40 @@ __device__ __forceinline__ unsigned prmt_r(unsigned a, unsigned b, unsigned sel)
     return d;
 }
 
+// Shared-memory accessors.  In the debug flavour each checks its address first (table lookups: the two table planes
+// and the zero words; everything else: the CTA's window) and skips the access on a violation.
 __device__ __forceinline__ unsigned lds16(unsigned addr)
 {
+    if (!AXC_SHARED_OK(addr, 2u, kLutBase, kBuf1Base + 128u, 101u)) return 0u;
     unsigned v;
     asm("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
 __device__ __forceinline__ uint4 lds128(unsigned addr)
 {
+    if (!AXC_SHARED_OK(addr, 16u, 0u, kWindowEnd, 102u)) return make_uint4(0, 0, 0, 0);
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
 __device__ __forceinline__ void sts128(unsigned addr, uint4 v)
 {
+    if (!AXC_SHARED_OK(addr, 16u, 0u, kWindowEnd, 103u)) return;
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 __device__ __forceinline__ void sts8(unsigned addr, unsigned v)
 {
+    if (!AXC_SHARED_OK(addr, 1u, 0u, kWindowEnd, 104u)) return;
     asm volatile("st.shared.u8 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 __device__ __forceinline__ void sts32(unsigned addr, unsigned v)
 {
+    if (!AXC_SHARED_OK(addr, 4u, 0u, kWindowEnd, 105u)) return;
     asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 __device__ __forceinline__ unsigned lds32(unsigned addr)
 {
+    if (!AXC_SHARED_OK(addr, 4u, 0u, kWindowEnd, 106u)) return 0u;
     unsigned v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
@@ -808,6 +816,9 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
     __syncthreads();
 
     const int NCH = P.L.NCH;
+    const long long n_input = (long long)P.N * P.H * P.W * P.C;         // bounds of the debug flavour's checks
+    const long long n_output = (long long)P.N * P.OH * P.OW * P.Cout;
+    (void)n_input; (void)n_output;
     const long long my_groups = P.tiles_total > blockIdx.x ? (P.tiles_total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
     // tile group number tl of this CTA -> first pixel and channel tile
@@ -825,10 +836,11 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
         constexpr int kBatch = 6;                           // gathers in flight per thread
 
         auto tap_value = [&](int l, int iy0, int ix0, long long base) -> float {
-            unsigned off, dd;
-            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(off), "=r"(dd) : "r"(sTap + unsigned(l) * 8u));
+            unsigned off = 0, dd = 0;
+            if (AXC_SHARED_OK(sTap + unsigned(l) * 8u, 8u, 0u, kWindowEnd, 107u))
+                asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(off), "=r"(dd) : "r"(sTap + unsigned(l) * 8u));
             const unsigned iy = unsigned(iy0 + int(dd & 0xFFFFu)), ix = unsigned(ix0 + int(dd >> 16));
-            return (iy < unsigned(P.H) && ix < unsigned(P.W)) ? __ldg(P.input + base + int(off)) : 0.0f;
+            return (iy < unsigned(P.H) && ix < unsigned(P.W) && AXC_GLOBAL_OK(base + int(off), n_input, 110u)) ? __ldg(P.input + base + int(off)) : 0.0f;
         };
 
         // half_sel: -1 all tiles, else only the tiles of that half of the slots; the pixel geometry of a tile group
@@ -851,8 +863,10 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
                         x0 = ow * P.sw - P.pw;
                         b = (((long long)n * P.H + y0) * P.W + x0) * P.C;
                     }
-                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(sGeo + unsigned(x) * 16u), "r"(unsigned(b)), "r"(unsigned(b >> 32)) : "memory");
-                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(sGeo + unsigned(x) * 16u + 8u), "r"(unsigned(y0)), "r"(unsigned(x0)) : "memory");
+                    if (AXC_SHARED_OK(sGeo + unsigned(x) * 16u, 16u, 0u, kWindowEnd, 108u)) {
+                        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(sGeo + unsigned(x) * 16u), "r"(unsigned(b)), "r"(unsigned(b >> 32)) : "memory");
+                        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(sGeo + unsigned(x) * 16u + 8u), "r"(unsigned(y0)), "r"(unsigned(x0)) : "memory");
+                    }
                 }
                 AXC_BAR(kBarLoad, kLoaderThreads);
             }
@@ -888,7 +902,8 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
                         if (lq_first + QS * (s0 + u) < LQ) {
                             if (P.vec_ok) {
                                 const int iy = iy0 + ky * P.dh, ix = ix0 + kx * P.dw;
-                                if (iy >= 0 && iy < P.H && ix >= 0 && ix < P.W)
+                                if (iy >= 0 && iy < P.H && ix >= 0 && ix < P.W &&
+                                    AXC_GLOBAL_OK(base + ((long long)(ky * P.dh) * P.W + kx * P.dw) * P.C + cc + 3, n_input, 111u))
                                     v = __ldg(reinterpret_cast<const float4 *>(
                                         P.input + base + ((long long)(ky * P.dh) * P.W + kx * P.dw) * P.C + cc));
                                 cc += 4 * QS;
@@ -908,7 +923,8 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
                                     for (int e = 0; e < 4; ++e) {
                                         if (l0 + e < P.K) {
                                             const int iy = iy0 + y2 * P.dh, ix = ix0 + x2 * P.dw;
-                                            if (iy >= 0 && iy < P.H && ix >= 0 && ix < P.W)
+                                            if (iy >= 0 && iy < P.H && ix >= 0 && ix < P.W &&
+                                                AXC_GLOBAL_OK(base + ((long long)(y2 * P.dh) * P.W + x2 * P.dw) * P.C + c2, n_input, 112u))
                                                 e4[e] = __ldg(P.input + base + ((long long)(y2 * P.dh) * P.W + x2 * P.dw) * P.C + c2);
                                         }
                                         if (++c2 >= P.C) { c2 = 0; if (++x2 >= P.KW) { x2 = 0; ++y2; } }
@@ -1091,7 +1107,7 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
                 for (int x = 0; x < kTilePix; ++x) {
                     const long long pix = m0 + tile * kTilePix + x;
                     const float a_sum = __uint_as_float(lds32(sAsum + ((unsigned(tl % 3) * unsigned(nt_eff) + unsigned(tile)) * kTilePix + unsigned(x)) * 4u));
-                    if (live && pix < P.M) {
+                    if (live && pix < P.M && AXC_GLOBAL_OK(pix * P.Cout + j, n_output, 113u)) {
                         const float t0 = __fmul_rn(float(acc[i][x]), Q.s1s2);
                         const float t1 = __fmul_rn(Q.m2, a_sum);
                         // y + 0.0f is y (y is never -0.0: its first term is a non-negative product); no branches here
@@ -1337,6 +1353,8 @@ int launch_dense_sched(const Geom &g, const float *input, float *output,
     }
     return AXC_OK;
 }
+
+AXC_DEFINE_BOUNDS_READER(bounds_record_sched)
 
 int plan_info(const void *workspace, int32_t out4[4], cudaStream_t stream)
 {
