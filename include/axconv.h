@@ -135,16 +135,22 @@ int axc_conv2d_forward(axc_table *table, const axc_conv_desc *desc,
                        float *output, void *workspace, size_t workspace_bytes,
                        const axc_debug_out *debug, int device, void *stream);
 
-/* What the callers of the op add to its output before anything else reads it: the bias and the activation of the
- * reference's Keras layer (tf2/python/keras/layers/fake_approx_convolutional.py:245-261) and the shortcut of a
- * residual block.  Fused into the kernels' dequantisation, so the output is written once:
- *     y = conv;  if (bias) y += bias[channel];  if (residual) y += residual[same index];  if (relu) y = max(y, 0)
- * - each addition a separately rounded fp32 operation, i.e. the bits of the same steps done by separate kernels.
+/* Steps of the op's callers that can ride along with the call: the bias and the activation of the reference's
+ * Keras layer (tf2/python/keras/layers/fake_approx_convolutional.py:245-261), the shortcut of a residual block, and
+ * the ReLU of the layer that PRODUCED this call's input.
+ *   output side:  y = conv;  if (bias) y += bias[channel];  if (residual) y += residual[same index];
+ *                 if (relu) y = max(y, 0)   - each a separately rounded fp32 operation, i.e. the bits of the same steps
+ *                 done by separate kernels.  The dense op runs them as one extra pass over the output (inside the lookup
+ *                 kernels even two instructions per output cost more than that pass); the depthwise kernels in place.
+ *   input side:   input_relu != 0: every input element counts as max(x, 0) - applied by the kernels' loaders to the raw
+ *                 value, before quantisation and patch sum, at no cost to the lookups.  A chain conv -> ReLU -> conv
+ *                 can thus leave the ReLU to the second convolution and never write the activated tensor.
  * bias: [out channels] on the device or NULL; residual: a tensor of the output's shape on the device or NULL. */
 typedef struct {
     const float *bias;
     const float *residual;
     int32_t relu;
+    int32_t input_relu;
 } axc_epilogue;
 /* axc_conv2d_forward (ranges == NULL: the four host scalars count) or axc_conv2d_forward_device_ranges
  * (ranges != NULL) with a fused epilogue (NULL = none). */
@@ -156,6 +162,10 @@ int axc_depthwise_conv2d_forward_fused(axc_table *table, const axc_conv_desc *de
                                        const float *filter, float in_min, float in_max, float f_min, float f_max,
                                        const axc_epilogue *epilogue, float *output, void *workspace,
                                        size_t workspace_bytes, const axc_debug_out *debug, int device, void *stream);
+
+/* The shortcut step of a residual block on its own: out[i] = out[i] + residual[i], then max(., 0) if relu - one pass
+ * over `count` floats (the pass axc_conv2d_forward_fused runs after the convolution, without a bias). */
+int axc_add_residual(float *out, const float *residual, size_t count, int relu, int device, void *stream);
 
 /* Same op with the four range scalars read from DEVICE memory: `ranges` = {input_min, input_max, filter_min,
  * filter_max}, four floats on `device`, typically written by the reductions that precede the op in the

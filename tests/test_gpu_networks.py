@@ -154,6 +154,10 @@ def test_op_epilogue_bias_residual_relu(built):
         assert torch.equal(y1, torch.relu((y0 + bias) + res)), kw
         y2 = ax.approx_conv2d_with_min_max_vars(x, f, *mm, [1, 1, 1, 1], 8, t, "SAME", relu=True, **kw)
         assert torch.equal(y2, torch.relu(y0)), kw
+        # the producer's ReLU applied by this call's loaders: the bits of the call on the activated tensor
+        y3 = ax.approx_conv2d_with_min_max_vars(x, f, *mm, [1, 1, 1, 1], 8, t, "SAME", input_relu=True, **kw)
+        y4 = ax.approx_conv2d_with_min_max_vars(torch.relu(x), f, *mm, [1, 1, 1, 1], 8, t, "SAME", **kw)
+        assert torch.equal(y3, y4) and not torch.equal(y3, y0), kw
     for shape, stride in (((2, 40, 40, 48), 1), ((2, 41, 39, 40), 2), ((1, 9, 9, 16), 1)):
         xd = torch.rand(shape, device="cuda", generator=g) * 2
         fd = torch.randn((3, 3, shape[3], 1), device="cuda", generator=g) * 0.3
@@ -164,3 +168,7 @@ def test_op_epilogue_bias_residual_relu(built):
         y1 = ax.approx_depthwise_conv2d_with_min_max_vars(xd, fd, *mmd, [1, stride, stride, 1], 8, t, "SAME", bias=b, residual=r,
                                                           relu=True)
         assert torch.equal(y1, torch.relu((y0 + b) + r)), shape
+        xs = xd - 1.0                                   # negative values as well
+        y3 = ax.approx_depthwise_conv2d_with_min_max_vars(xs, fd, *mmd, [1, stride, stride, 1], 8, t, "SAME", input_relu=True)
+        y4 = ax.approx_depthwise_conv2d_with_min_max_vars(torch.relu(xs), fd, *mmd, [1, stride, stride, 1], 8, t, "SAME")
+        assert torch.equal(y3, y4), shape

@@ -145,7 +145,7 @@ int resolve_geometry(const axc_conv_desc *d, bool depthwise, Geom *g)
     g->accum = d->accumulate;
     if (d->plan != AXC_PLAN_KEEP && d->plan != AXC_PLAN_NONE) return AXC_INVALID_ARGUMENT;
     g->plan = d->plan;
-    g->ep = Epilogue{nullptr, nullptr, 0};
+    g->ep = Epilogue{nullptr, nullptr, 0, 0};
 
     g->N = d->n; g->H = d->h; g->W = d->w; g->C = d->c;
     g->KH = d->kh; g->KW = d->kw; g->Cout = d->cout;
@@ -295,7 +295,7 @@ static int forward(bool depthwise, axc_table *table, const axc_conv_desc *desc, 
     Geom g;
     int rc = resolve_geometry(desc, depthwise, &g);
     if (rc) return rc;
-    if (epilogue) g.ep = Epilogue{epilogue->bias, epilogue->residual, epilogue->relu != 0 ? 1 : 0};
+    if (epilogue) g.ep = Epilogue{epilogue->bias, epilogue->residual, epilogue->relu != 0 ? 1 : 0, epilogue->input_relu != 0 ? 1 : 0};
     const long long out_c = depthwise ? (long long)g.C * g.Cout : g.Cout;
     if (g.M * out_c == 0) return AXC_OK;  // empty output: nothing to do
     if (!input || !filter || !output) return AXC_INVALID_ARGUMENT;

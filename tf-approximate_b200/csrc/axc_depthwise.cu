@@ -12,6 +12,8 @@
 // the dense kernel (plane p at 65536*(1+p), byte a*256 + 2*(b&127)).
 #include <cuda.h>
 
+#include <cmath>
+
 #include <mutex>
 #include <type_traits>
 
@@ -48,6 +50,7 @@ struct DwParams {
     int units_per_group;   // N * bands
     int wave, sets;        // CTAs per set (= channel groups served at a time) and sets: grid = wave * sets
     Epilogue ep;           // fused additions to the output
+    float in_floor;        // every input element is max(x, in_floor) as it is loaded: 0 = the producer's ReLU, -inf = none
 };
 
 __device__ __forceinline__ unsigned dw_quantize_u8(float x, float off, float inv)
@@ -89,11 +92,11 @@ __global__ void dw_filter_prep_kernel(const float *__restrict__ filter, int KHW,
 }
 
 __global__ void dw_quantize_tensor_kernel(const float *__restrict__ x, long long n, float off, float inv,
-                                          uint8_t *__restrict__ q)
+                                          uint8_t *__restrict__ q, float in_floor)
 {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (; i < n; i += stride) q[i] = uint8_t(dw_quantize_u8(x[i], off, inv));
+    for (; i < n; i += stride) q[i] = uint8_t(dw_quantize_u8(max_keep_nan(x[i], in_floor), off, inv));
 }
 
 __device__ __forceinline__ void dw_fill_table(const uint16_t *lut, int tid, int nthreads)
@@ -151,7 +154,7 @@ __global__ void __launch_bounds__(kDwThreads, 1) depthwise_generic_kernel(const 
                 const int iy = oh * P.sh - P.ph + ky * P.dh, ix = ow * P.sw - P.pw + kx * P.dw;
                 float v = 0.0f;
                 if (iy >= 0 && iy < P.H && ix >= 0 && ix < P.W)
-                    v = __ldg(P.input + (((long long)n * P.H + iy) * P.W + ix) * P.C + c);
+                    v = max_keep_nan(__ldg(P.input + (((long long)n * P.H + iy) * P.W + ix) * P.C + c), P.in_floor);
                 a_sum = __fadd_rn(a_sum, v);
                 const unsigned qa = dw_quantize_u8(v, P.in_off, P.in_inv);
                 const unsigned w = __ldg(P.prog + (size_t)tap * P.OC + oc);
@@ -264,7 +267,7 @@ __global__ void __launch_bounds__(kDwThreads, 1) depthwise_3x3_kernel(const DwPa
 #pragma unroll
             for (int kx = 0; kx < 3 - S; ++kx) {
                 const bool ok = rowok[ky] && unsigned(ix_first + kx) < unsigned(P.W);
-                xf[ky][kx] = ok ? __ldg(P.input + (rowoff[ky] + kx * P.C)) : 0.0f;
+                xf[ky][kx] = ok ? max_keep_nan(__ldg(P.input + (rowoff[ky] + kx * P.C)), P.in_floor) : 0.0f;
                 xq[ky] |= dw_quantize_u8(xf[ky][kx], P.in_off, P.in_inv) << (8 * kx);
             }
         int col = 3 - S;                                  // next new column, relative to ix_first
@@ -279,7 +282,7 @@ __global__ void __launch_bounds__(kDwThreads, 1) depthwise_3x3_kernel(const DwPa
                     const int o = rel * P.C;
 #pragma unroll
                     for (int ky = 0; ky < 3; ++ky)
-                        nf[u][k2][ky] = (colok && rowok[ky]) ? __ldg(P.input + (rowoff[ky] + o)) : 0.0f;
+                        nf[u][k2][ky] = (colok && rowok[ky]) ? max_keep_nan(__ldg(P.input + (rowoff[ky] + o)), P.in_floor) : 0.0f;
                 }
             col += 3 * S;
 #pragma unroll
@@ -469,7 +472,7 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
     const unsigned row_bytes = unsigned(P.W) * unsigned(P.C) * 4u;        // the launcher keeps IR rows below 2^32 bytes
     const unsigned orow_bytes = unsigned(P.OW) * unsigned(P.OC) * 4u;
     const unsigned pix_bytes = unsigned(P.C) * 4u, opix_bytes = unsigned(P.OC) * 4u;
-    const float in_off = P.in_off, in_inv = P.in_inv, s1s2 = P.s1s2, m2 = P.m2, km1m2 = P.km1m2;
+    const float in_off = P.in_off, in_inv = P.in_inv, s1s2 = P.s1s2, m2 = P.m2, km1m2 = P.km1m2, in_floor = P.in_floor;
     constexpr int PF = kPlainL2Ahead;
 
     for (int g = slot; g < P.groups; g += wave) {
@@ -532,6 +535,7 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
                     xf[i][slot] = 0.0f;
                     if (AXC_SHARED_OK(a + unsigned(i) * 128u, 4u, stages0, bars0, 307u))
                         asm volatile("ld.shared.f32 %0, [%1];" : "=f"(xf[i][slot]) : "r"(a + unsigned(i) * 128u));
+                    if (P.ep.input_relu) xf[i][slot] = fmaxf(xf[i][slot], 0.0f);     // the producer's ReLU (zeros of the padding stay zeros)
                 }
             };
 
@@ -542,7 +546,7 @@ __device__ __forceinline__ void depthwise_3x3_tab_body(const DwParams &P, const 
 #pragma unroll
                     for (int i = 0; i < IR; ++i) {
                         float x = 0.0f;
-                        if (i >= lo && i < hi) x = __ldg(reinterpret_cast<const float *>(dw_ptr_mad(colp, unsigned(i), row_bytes)));
+                        if (i >= lo && i < hi) x = max_keep_nan(__ldg(reinterpret_cast<const float *>(dw_ptr_mad(colp, unsigned(i), row_bytes))), in_floor);
                         nx[i] = x;
                     }
                     if (PF > 0 && unsigned(c + PF - P.pw) < unsigned(P.W)) {
@@ -849,7 +853,7 @@ int launch_depthwise(const uint16_t *lut_dev, const Geom &g, const Quant &q, con
         const long long n = (long long)g.N * g.H * g.W * g.C;
         if (n > 0) {
             const unsigned blocks = unsigned(n / 256 + 1 < 4096 ? n / 256 + 1 : 4096);
-            dw_quantize_tensor_kernel<<<blocks, 256, 0, stream>>>(input, n, q.in_off, q.in_inv, dbg->qinput);
+            dw_quantize_tensor_kernel<<<blocks, 256, 0, stream>>>(input, n, q.in_off, q.in_inv, dbg->qinput, g.ep.input_relu ? 0.0f : -INFINITY);
             AXC_CUDA(cudaGetLastError());
             count_launch();
         }
@@ -876,6 +880,7 @@ int launch_depthwise(const uint16_t *lut_dev, const Geom &g, const Quant &q, con
     P.filter = filter; P.f_off = q.f_off; P.f_inv = q.f_inv;
     P.bands = 0; P.units_per_group = 0; P.wave = 0; P.sets = 0;
     P.ep = g.ep;
+    P.in_floor = g.ep.input_relu ? 0.0f : -INFINITY;
     // The expanded-table kernel pays about 74 000 lookups per CTA and channel group for its table: worth it from
     // some ten thousand outputs per group on.
     if (k3 && (g.sw == 1 || g.sw == 2) && g.M * 32 >= kTabMinOutputsPerGroup && di.max_smem_optin >= int(kTabSmem) &&

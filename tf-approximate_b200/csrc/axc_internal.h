@@ -82,6 +82,7 @@ struct Epilogue {
     const float *bias;      // [out channels] or NULL
     const float *residual;  // output shape or NULL
     int relu;
+    int input_relu;         // max(x, 0) on every input element as it is loaded (the producer's ReLU, applied here)
 };
 
 // y after the fused epilogue; `idx` = element index of the output, `bias_j` = bias of its channel (0 without one)
@@ -177,6 +178,9 @@ Workspace depthwise_workspace(int KHW, int C, int mult);
 int launch_dense(const uint16_t *lut_dev, unsigned table_uid, const Geom &g, const Quant &q, const float *ranges_dev,
                  const float *input, const float *filter, float *output, void *workspace, const axc_debug_out *dbg,
                  int device, cudaStream_t stream, bool ref_order);
+// out = out (+ bias[channel]) (+ residual), then max(out, 0) if relu, in one pass; bias / residual may be NULL
+int launch_post(float *out, const float *bias, const float *residual, long long count, int channels, int relu,
+                const DeviceInfo &di, cudaStream_t stream);
 int launch_depthwise(const uint16_t *lut_dev, const Geom &g, const Quant &q, const float *input,
                      const float *filter, float *output, void *workspace, const axc_debug_out *dbg,
                      int device, cudaStream_t stream);

@@ -717,8 +717,7 @@ struct SchedParams {
     long long tiles_total;    // pixel tile groups x channel tiles
     int vec_ok;
     unsigned long long magic_c, magic_kw;   // ceil(2^40 / C), ceil(2^40 / KW): n / d == (n * magic) >> 40 for n*d < 2^40
-    const float *bias;        // fused epilogue: per-channel bias or NULL
-    float floor;              // fused epilogue: y = max(y, floor); 0 = ReLU, -inf = none
+    float in_floor;           // every input element is max(x, in_floor) as it is loaded: 0 = the producer's ReLU, -inf = none
 };
 
 __device__ __forceinline__ int fast_div(int n, unsigned long long magic)
@@ -934,6 +933,9 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
                             }
                             l0 += 4 * QS;
                         }
+                        // the producer's ReLU, applied to the raw taps (quantiser and patch sum both see max(x, 0))
+                        v.x = max_keep_nan(v.x, P.in_floor); v.y = max_keep_nan(v.y, P.in_floor);
+                        v.z = max_keep_nan(v.z, P.in_floor); v.w = max_keep_nan(v.w, P.in_floor);
                         st[u] = v;
                     }
                     // quantise -> rows of the activation buffer; lanes = pixels, so the byte stores of a warp fall
@@ -1099,7 +1101,6 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
         {
             const int j = (P.g_base + nt * GW + gl) * 32 + chan_lane;
             const bool live = (nt * GW + gl) < P.g_count && j < P.Cout;
-            const float bias_j = (P.bias && live) ? __ldg(P.bias + j) : 0.0f;      // fused epilogue: bias of this lane's channel
 #pragma unroll
             for (int i = 0; i < NTW; ++i) {
                 const int tile = P.dual ? 2 * (slot * NTW + i) + half : slot * NTW + i;
@@ -1110,9 +1111,8 @@ __global__ void __launch_bounds__((kComputeWarps + LW) * 32, 1) dense_sched_kern
                     if (live && pix < P.M && AXC_GLOBAL_OK(pix * P.Cout + j, n_output, 113u)) {
                         const float t0 = __fmul_rn(float(acc[i][x]), Q.s1s2);
                         const float t1 = __fmul_rn(Q.m2, a_sum);
-                        // y + 0.0f is y (y is never -0.0: its first term is a non-negative product); no branches here
-                        const float y = __fadd_rn(__fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), Q.km1m2), bias_j);
-                        if (P.output) P.output[pix * P.Cout + j] = max_keep_nan(y, P.floor);
+                        P.output[pix * P.Cout + j] = __fsub_rn(__fadd_rn(__fadd_rn(t0, t1), t2), Q.km1m2);
+                        asm volatile("" ::: "memory");      // the tap may be the same memory (integer sums only): keep the order
                         if (P.acc_out) P.acc_out[pix * P.Cout + j] = acc[i][x];
                     }
                     acc[i][x] = 0;
@@ -1270,8 +1270,7 @@ int launch_dense_sched(const Geom &g, const float *input, float *output,
     P.K = g.K; P.M = g.M; P.pix_base = 0; P.tiles_n = 0; P.tiles_total = 0;
     P.vec_ok = (g.C % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
     P.dual = 0;
-    P.bias = g.ep.bias;
-    P.floor = (g.ep.relu && !g.ep.residual) ? 0.0f : -INFINITY;     // with a shortcut the ReLU follows its addition (launch_dense)
+    P.in_floor = g.ep.input_relu ? 0.0f : -INFINITY;
     // n / d == (n * magic) >> 40 holds while n * d < 2^40; launch_dense keeps shapes beyond that on the common-K kernel
     P.magic_c = ((1ull << 40) + unsigned(g.C) - 1) / unsigned(g.C);
     P.magic_kw = ((1ull << 40) + unsigned(g.KW) - 1) / unsigned(g.KW);

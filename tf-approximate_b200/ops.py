@@ -181,7 +181,7 @@ def workspace_bytes(input_shape, filter_shape, strides, padding, dilations=(1, 1
 
 def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
              mul_map_file, padding, explicit_paddings, data_format, dilations, out, debug, accumulate="exact",
-             plan="keep", workspace=None, ranges=None, bias=None, residual=None, relu=False):
+             plan="keep", workspace=None, ranges=None, bias=None, residual=None, relu=False, input_relu=False):
     L = _lib.load()
     if not isinstance(input, torch.Tensor) or not isinstance(filter, torch.Tensor):
         raise InvalidArgumentError("input and filter must be torch tensors")
@@ -235,13 +235,13 @@ def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_
         raise InvalidArgumentError("ranges must be four contiguous fp32 values on the input's device")
     # fused additions to the output (bias of the layer, shortcut of a residual block, ReLU)
     ep_ptr, keep = None, []
-    if bias is not None or residual is not None or relu:
+    if bias is not None or residual is not None or relu or input_relu:
         for name, t, shape in (("bias", bias, (oshape[3],)), ("residual", residual, oshape)):
             if t is not None and (t.dtype != torch.float32 or t.device != dev or tuple(t.shape) != shape):
                 raise InvalidArgumentError("%s must be a fp32 tensor of shape %s on the input's device" % (name, shape))
         keep = [t.contiguous() if t is not None else None for t in (bias, residual)]
         ep = _lib.Epilogue(keep[0].data_ptr() if keep[0] is not None else None,
-                           keep[1].data_ptr() if keep[1] is not None else None, 1 if relu else 0)
+                           keep[1].data_ptr() if keep[1] is not None else None, 1 if relu else 0, 1 if input_relu else 0)
         ep_ptr = C.byref(ep)
     if not depthwise and (ranges is not None or all(isinstance(v, torch.Tensor) and v.is_cuda for v in four)):
         # the four scalars already live on the GPU (e.g. fresh reductions): hand them over as they are, no
@@ -278,7 +278,7 @@ def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_
 def approx_conv2d_with_min_max_vars(input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
                                     mul_map_file, padding, explicit_paddings=(), data_format="NHWC",
                                     dilations=(1, 1, 1, 1), name=None, out=None, debug=False, accumulate="exact",
-                                    plan="keep", workspace=None, ranges=None, bias=None, residual=None, relu=False):
+                                    plan="keep", workspace=None, ranges=None, bias=None, residual=None, relu=False, input_relu=False):
     """Forward pass of `ApproxConv2DWithMinMaxVars`.
 
     input [N,H,W,C] and filter [KH,KW,C,Cout] are fp32 CUDA tensors; the four min/max values are
@@ -298,20 +298,22 @@ def approx_conv2d_with_min_max_vars(input, filter, input_min, input_max, filter_
     filter_max} (then the four positional range arguments are ignored and may be None).
 
     bias [Cout], residual (a tensor of the output's shape) and relu are fused into the kernel's dequantisation:
-    y = conv; y += bias; y += residual; y = max(y, 0) - with the bits of the same steps done by separate kernels."""
+    y = conv; y += bias; y += residual; y = max(y, 0) - with the bits of the same steps done by separate kernels.
+    input_relu: every input element counts as max(x, 0) (the ReLU of the layer that produced the input, applied by
+    this call's loaders for free)."""
     return _forward(False, input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
                     mul_map_file, padding, list(explicit_paddings), data_format, list(dilations), out, debug, accumulate,
-                    plan, workspace, ranges, bias, residual, relu)
+                    plan, workspace, ranges, bias, residual, relu, input_relu)
 
 
 def approx_depthwise_conv2d_with_min_max_vars(input, filter, input_min, input_max, filter_min, filter_max, strides,
                                               num_bits, mul_map_file, padding, explicit_paddings=(),
                                               data_format="NHWC", dilations=(1, 1, 1, 1), name=None, out=None,
-                                              debug=False, bias=None, residual=None, relu=False):
+                                              debug=False, bias=None, residual=None, relu=False, input_relu=False):
     """Depthwise variant: filter [KH,KW,C,mult] (DepthwiseConv2dNative layout), output [N,OH,OW,C*mult]."""
     return _forward(True, input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
                     mul_map_file, padding, list(explicit_paddings), data_format, list(dilations), out, debug,
-                    bias=bias, residual=residual, relu=relu)
+                    bias=bias, residual=residual, relu=relu, input_relu=input_relu)
 
 
 def ax_conv2d(input, filter, min_input, max_input, min_filter, max_filter, strides, padding, table="",
@@ -360,6 +362,19 @@ def approx_conv2d(input, filter, strides, padding, explicit_paddings=(), data_fo
     f_min, f_max = torch.aminmax(filter)
     return _forward(False, input, filter, in_min, in_max, f_min, f_max, strides, 8, "", padding, list(explicit_paddings),
                     data_format, list(dilations), out, False)
+
+
+def add_residual_(out, residual, relu=True):
+    """In place: out = out + residual, then ReLU - the shortcut step of a residual block in one pass."""
+    if (out.dtype != torch.float32 or residual.dtype != torch.float32 or not out.is_cuda or residual.device != out.device
+            or out.shape != residual.shape or not out.is_contiguous()):
+        raise InvalidArgumentError("add_residual_ expects two fp32 CUDA tensors of one shape, the first contiguous")
+    r = residual.contiguous()
+    dev_index = out.device.index if out.device.index is not None else torch.cuda.current_device()
+    st = _lib.load().axc_add_residual(out.data_ptr(), r.data_ptr(), out.numel(), 1 if relu else 0, dev_index,
+                                      C.c_void_p(torch.cuda.current_stream(out.device).cuda_stream))
+    raise_for_status(st, "add residual", _cuda_detail() if st == 100 else "")
+    return out
 
 
 def tensor_range(x, out=None):

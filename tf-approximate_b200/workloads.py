@@ -152,43 +152,55 @@ class Network:
 
     def forward(self, x, conv, relu, maxpool3s2, fused=False):
         """conv(i, x) -> y;  relu(x) -> x;  maxpool3s2(x) -> x (3x3, stride 2, SAME).
-        fused=True: the backend's conv takes (i, x, relu=bool, residual=tensor or None) and applies the shortcut
-        addition and the ReLU itself (the CUDA op fuses them into its dequantisation); otherwise they are separate
-        steps here.  Both orders of evaluation are the same arithmetic: relu(conv + shortcut)."""
+        fused=True: the backend's conv takes (i, x, input_relu=bool, relu=bool, residual=tensor or None).  A ReLU that
+        follows a convolution is then not executed where it stands: the tensor is passed on as "ReLU pending" and the
+        convolution that consumes it applies max(x, 0) while loading (free for the lookup kernels); a shortcut addition
+        with its ReLU is one pass of the backend.  Where a pending tensor is needed as it is (as a shortcut, as the
+        network's output) the ReLU is executed.  Max pooling commutes with the ReLU.  Same arithmetic either way."""
         ix = self.index
 
-        def c(i, x, act=False, res=None):
-            if fused:
-                return conv(i, x, relu=act, residual=res)
-            y = conv(i, x)
-            if res is not None:
-                y = y + res
-            return relu(y) if act else y
+        def mat(xp):
+            t, pending = xp
+            return relu(t) if pending else t
 
+        def c(i, xp, act=False, res=None):
+            t, pending = xp
+            if not fused:
+                y = conv(i, mat(xp))
+                if res is not None:
+                    y = y + mat(res)
+                return (relu(y) if act else y, False)
+            if res is not None:
+                return (conv(i, t, input_relu=pending, relu=act, residual=mat(res)), False)
+            return (conv(i, t, input_relu=pending, relu=False, residual=None), act)
+
+        xp = (x, False)
         if self.kind == "resnet50":
-            x = maxpool3s2(c(ix["stem"], x, act=True))
+            t, pending = c(ix["stem"], xp, act=True)
+            xp = (maxpool3s2(t), pending)
             for stage, b, width, cout, stride, proj in resnet50_blocks():
                 tag = "s%db%d" % (stage + 1, b)
-                y = c(ix[tag + "_1x1a"], x, act=True)
+                y = c(ix[tag + "_1x1a"], xp, act=True)
                 y = c(ix[tag + "_3x3"], y, act=True)
-                sc = c(ix[tag + "_proj"], x) if proj else x
-                x = c(ix[tag + "_1x1b"], y, act=True, res=sc)
-            return x
+                sc = c(ix[tag + "_proj"], xp) if proj else xp
+                xp = c(ix[tag + "_1x1b"], y, act=True, res=sc)
+            return mat(xp)
         if self.kind == "resnet20":
-            x = c(ix["stem"], x, act=True)
+            xp = c(ix["stem"], xp, act=True)
             for stage in range(3):
                 for b in range(3):
                     tag = "s%db%d" % (stage + 1, b)
-                    y = c(ix[tag + "_a"], x, act=True)
-                    stride = self.convs[ix[tag + "_a"]][0].stride
-                    if stride != 1 or self.convs[ix[tag + "_a"]][0].cin != self.convs[ix[tag + "_a"]][0].cout:
-                        # option-A shortcut: subsample, zero-pad the new channels
-                        x = _pad_channels(x[:, ::stride, ::stride, :], self.convs[ix[tag + "_a"]][0].cout)
-                    x = c(ix[tag + "_b"], y, act=True, res=x)
-            return x
+                    first = self.convs[ix[tag + "_a"]][0]
+                    y = c(ix[tag + "_a"], xp, act=True)
+                    sc = xp
+                    if first.stride != 1 or first.cin != first.cout:
+                        # option-A shortcut: subsample, zero-pad the new channels (both commute with a pending ReLU)
+                        sc = (_pad_channels(xp[0][:, ::first.stride, ::first.stride, :], first.cout), xp[1])
+                    xp = c(ix[tag + "_b"], y, act=True, res=sc)
+            return mat(xp)
         for i in range(len(self.convs)):
-            x = c(i, x, act=True)
-        return x
+            xp = c(i, xp, act=True)
+        return mat(xp)
 
 
 def _pad_channels(x, c):
@@ -246,10 +258,11 @@ class GpuRunner:
         self.calibrating = False
         self.conv_events = None   # when a list: (start, end) CUDA events around every conv call
 
-    def _conv(self, i, x, relu=False, residual=None):
+    def _conv(self, i, x, input_relu=False, relu=False, residual=None):
         spec, _ = self.net.convs[i]
         if self.calibrating:
-            self.in_ranges[i] = (float(x.min()), float(x.max()))
+            seen = self.torch.relu(x) if input_relu else x
+            self.in_ranges[i] = (float(seen.min()), float(seen.max()))
         lo, hi = self.in_ranges[i]
         table = self.tables[i if len(self.tables) > 1 else 0]
         fn = (self.ax.approx_depthwise_conv2d_with_min_max_vars if spec.depthwise
@@ -258,13 +271,15 @@ class GpuRunner:
             e0 = self.torch.cuda.Event(enable_timing=True)
             e1 = self.torch.cuda.Event(enable_timing=True)
             e0.record()
-        if residual is not None and not residual.is_contiguous():
-            residual = residual.contiguous()
+        # a shortcut (with its ReLU) is added by the library's one-pass kernel right after the convolution - outside the
+        # convolution's event pair, so that the per-layer times stay those of the table convolution
         y = fn(x, self.filters[i], lo, hi, self.f_ranges[i][0], self.f_ranges[i][1],
-               [1, spec.stride, spec.stride, 1], 8, table, "SAME", relu=relu, residual=residual)
+               [1, spec.stride, spec.stride, 1], 8, table, "SAME", input_relu=input_relu, relu=relu and residual is None)
         if self.conv_events is not None:
             e1.record()
             self.conv_events.append((i, e0, e1))
+        if residual is not None:
+            self.ax.ops.add_residual_(y, residual, relu=relu)
         return y
 
     def calibrate(self, x):
