@@ -1285,8 +1285,8 @@ int launch_dense_sched(const Geom &g, const float *input, float *output,
         P.g_count = count;
         P.dual = (count == 1 && plan_group_dual(g_done, L.G, g.Cout, g.K)) ? 1 : 0;
         // two consumer halves pay off once an iteration is long enough to hide the second barrier (measured:
-        // +1-3 % for K >= 144, -14 % for K = 32)
-        P.split = L.KC >= 128 ? 1 : 0;
+        // +1-4 % for K >= 64, -14 % for K = 32)
+        P.split = L.KC >= 64 ? 1 : 0;
         // pixel tiles per consumer warp: as many as the shared-memory budget allows (two sets of buffers)
         const int slots = (kComputeWarps / gw) * (P.dual ? 2 : 1);   // pixel tiles in flight per unit of NTW
         int ntw = 4;
