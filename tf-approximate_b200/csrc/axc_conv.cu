@@ -568,11 +568,10 @@ AXC_DEFINE_BOUNDS_READER(bounds_record_conv)
 
 static int dense_variant()
 {
-    static int v = -1;
-    if (v < 0) {
+    static const int v = [] {
         const char *e = getenv("AXC_DENSE_VARIANT");
-        v = (e && e[0] == '1') ? 1 : 0;
-    }
+        return (e && e[0] == '1') ? 1 : 0;
+    }();
     return v;
 }
 

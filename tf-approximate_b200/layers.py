@@ -131,7 +131,7 @@ class FakeApproxConv2D(torch.nn.Module):
             return None
         info = (C.c_int32 * 4)()
         dev = self._workspace.device
-        st = _lib.load().axc_conv2d_plan_info(self._workspace.data_ptr(), info, dev.index or 0,
+        st = _lib.load().axc_conv2d_plan_info(self._workspace.data_ptr(), info, ops._device_index(dev),
                                               C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
         ops.raise_for_status(st, "plan info")
         return {"rebuilt": int(info[0]), "fallback": int(info[1]), "status": int(info[2]), "steps_per_mille": int(info[3])}

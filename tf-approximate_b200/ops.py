@@ -179,6 +179,11 @@ def workspace_bytes(input_shape, filter_shape, strides, padding, dilations=(1, 1
     return int(wsz.value)
 
 
+def _device_index(dev):
+    """CUDA ordinal of a torch device; a device without an index means the current one."""
+    return dev.index if dev.index is not None else torch.cuda.current_device()
+
+
 def _forward(depthwise, input, filter, input_min, input_max, filter_min, filter_max, strides, num_bits,
              mul_map_file, padding, explicit_paddings, data_format, dilations, out, debug, accumulate="exact",
              plan="keep", workspace=None, ranges=None, bias=None, residual=None, relu=False, input_relu=False):
@@ -416,7 +421,7 @@ def measure_lookup_peak(device=None):
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     scratch = torch.zeros(8192, dtype=torch.uint8, device=dev)
     out = C.c_double()
-    st = _lib.load().axc_measure_lookup_peak(dev.index or 0, scratch.data_ptr(), scratch.numel(),
+    st = _lib.load().axc_measure_lookup_peak(_device_index(dev), scratch.data_ptr(), scratch.numel(),
                                              C.c_void_p(torch.cuda.current_stream(dev).cuda_stream), C.byref(out))
     raise_for_status(st, "lookup peak", _cuda_detail() if st == 100 else "")
     return float(out.value)

@@ -71,7 +71,7 @@ def forward_sharded(x_slabs, filters, table, ranges, strides, padding, gather_to
         xs, fs = x.contiguous(), f.contiguous()
         keep += [xs, fs, ws]
         outs.append(y)
-        shards[i] = _lib.Shard(dev.index or 0, int(x.shape[0]), xs.data_ptr(), fs.data_ptr(), y.data_ptr(), ws.data_ptr(),
+        shards[i] = _lib.Shard(ops._device_index(dev), int(x.shape[0]), xs.data_ptr(), fs.data_ptr(), y.data_ptr(), ws.data_ptr(),
                                ws.numel(), torch.cuda.current_stream(dev).cuda_stream)
     failed = C.c_int32(-1)
     st = L.axc_conv2d_forward_sharded(tab.handle, C.byref(d), shards, len(x_slabs), *[float(v) for v in ranges], C.byref(failed))
@@ -82,7 +82,7 @@ def forward_sharded(x_slabs, filters, table, ranges, strides, padding, gather_to
     total = sum(int(y.shape[0]) for y in outs)
     dst = torch.empty((total,) + tuple(outs[0].shape[1:]), dtype=torch.float32, device=gdev)
     image_bytes = 4 * int(outs[0][0].numel()) if total else 0
-    raise_for_status(L.axc_gather_outputs(shards, len(x_slabs), image_bytes, dst.data_ptr(), gdev.index or 0), "gather")
+    raise_for_status(L.axc_gather_outputs(shards, len(x_slabs), image_bytes, dst.data_ptr(), ops._device_index(gdev)), "gather")
     for y in outs:      # the copies run on the slabs' streams: make the gathered tensor's device wait for them
         torch.cuda.current_stream(gdev).wait_stream(torch.cuda.current_stream(y.device))
     return dst
