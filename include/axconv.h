@@ -96,6 +96,12 @@ int axc_table_create_from_file(const char *path, int num_bits, axc_table **out);
 int axc_table_create_from_memory(const uint16_t *lut65536, axc_table **out);
 int axc_table_create_exact(axc_table **out);
 void axc_table_destroy(axc_table *table);
+/* Weight tuning of the first-generation op (attribute AxTune of AxConv2D, on by default there;
+ * ApproximateSelector::init, tf1/axqconv/approximate_selector.h:46-78): out[i][w] = in[i][w2(w)], where w2(w) is
+ * the weight column whose entries are closest to the exact products i*w in summed absolute error; among equally
+ * good columns w itself wins, else the lowest index.  Host arithmetic on uint16[65536] arrays (index = a*256 + w);
+ * `in` and `out` may be the same array.  Feed the result to axc_table_create_from_memory. */
+int axc_table_tune_weights(const uint16_t *in65536, uint16_t *out65536);
 /* Host copy of the 65536 entries (owned by the table). */
 int axc_table_host_data(const axc_table *table, const uint16_t **out);
 /* Uploads the 128 KiB replica for `device` if it is not there yet (blocking, once per
@@ -244,8 +250,11 @@ int axc_depthwise_conv2d_forward_noalloc(axc_table *table, const axc_conv_desc *
  * qinput [n,h,w,c] and qfilter [kh,kw,c,cout] are uint8 codes; every product of the integer convolution is
  * LUT[a][b], and the int32 result carries the reference's zero-point corrections
  *     output = sum_l ( LUT[a_l][b_l] - a_l*filter_offset - b_l*input_offset + input_offset*filter_offset ),
- * a tap outside the image counting as a_l = input_offset.  With both offsets 0 the output is the plain table sum.
- * Offsets must lie in 0..255 (axc_quantized_zero_point gives the reference's value for a float range).  As in the
+ * a tap outside the image counting as a_l = input_offset modulo 256 (the functor stores the offset into its uint8
+ * operand type, :203-214; the zero-point terms use the offset as it is).  With both offsets 0 the output is the plain
+ * table sum.  axc_quantized_zero_point gives the reference's offset for a float range; it lies outside 0..255 when
+ * the range does not contain 0.  Offsets so large that K * max(|input_offset|, 255) * max(|filter_offset|, 255)
+ * exceeds int32 return AXC_INVALID_ARGUMENT (the reference's int32 total would overflow).  As in the
  * reference op the strides must be equal and the dilation 1 (AXC_INVALID_ARGUMENT otherwise, :305-326); shapes on
  * which the reference functor would place the window differently from TensorFlow's padding rule (stride larger
  * than the window by two or more, :153-163) return AXC_UNIMPLEMENTED.  The table sums are computed by the kernels

@@ -454,12 +454,13 @@ int axo_conv2d_direct(const axo_conv_desc *d, const uint16_t *lut, const float *
  * First-generation op AxConv2D: quantised uint8 operands in, int32 sums out.
  * Restates ReferenceConvFunctor::operator() of tf1/axqconv/axqconv.cc:132-263
  * loop for loop: window origin from the functor's own offsets (:153-163), a tap
- * outside the image counts as input_offset (:203-214), every product is a table
- * entry (:232) and carries the zero-point terms (:241-246); offset_output = 0,
+ * outside the image counts as input_offset stored into the uint8 operand type,
+ * i.e. modulo 256 (:203-214), every product is a table entry (:232) and carries
+ * the zero-point terms with the unwrapped offsets (:241-246); offset_output = 0,
  * mult_output = 1, shift_output = 0 (:369-371) leave the total as the output.
- * Pin: the functor needs TensorFlow's quantised types to compile, so it is not
- * built here; for the exact-product table the result must equal the integer
- * convolution sum (a - input_offset) * (b - filter_offset), which the tests check.
+ * Pin: the op's own Compute(), compiled from the reference checkout against
+ * stand-in headers (ref_axq_driver.cpp, _ref/libaxq_ref.so), on random shapes,
+ * ranges and multipliers, bit for bit (tests/test_oracle_vs_ref.py).
  */
 int axo_qconv2d(const axo_conv_desc *d, const uint16_t *lut, const uint8_t *qin, const uint8_t *qf, int input_offset,
                 int filter_offset, int32_t *out)
@@ -492,7 +493,7 @@ int axo_qconv2d(const axo_conv_desc *d, const uint16_t *lut, const uint8_t *qin,
                         for (int fx = 0; fx < d->kw; ++fx)
                             for (int ic = 0; ic < C; ++ic) {
                                 const int ix = x0 + fx, iy = y0 + fy;
-                                int32_t a = input_offset;
+                                int32_t a = (uint8_t)input_offset;
                                 if (ix >= 0 && ix < d->w && iy >= 0 && iy < d->h)
                                     a = qin[(((size_t)b * d->h + iy) * d->w + ix) * C + ic];
                                 const int32_t w = qf[(((size_t)fy * d->kw + fx) * C + ic) * F + oc];
@@ -502,6 +503,32 @@ int axo_qconv2d(const axo_conv_desc *d, const uint16_t *lut, const uint8_t *qin,
                     out[(((size_t)b * oh + oy) * ow + ox) * F + oc] = total;
                 }
     return AXO_OK;
+}
+
+/*
+ * Weight tuning of the first-generation op (attribute AxTune, on by default):
+ * ApproximateSelector::init, tf1/axqconv/approximate_selector.h:46-78.  Column w
+ * of the table is replaced by the column w2 whose entries are closest to the exact
+ * products i * w in summed absolute error; among equally good columns w itself
+ * wins, else the lowest index.  in/out: uint16[65536], index = data * 256 + weight.
+ */
+void axo_tune_table(const uint16_t *in, uint16_t *out)
+{
+    for (int w = 0; w < 256; ++w) {
+        int wpos = -1;
+        int werr = 0;
+        for (int w2 = 0; w2 < 256; ++w2) {
+            int sumerr = 0;
+            for (int i = 0; i < 256; ++i)
+                sumerr += abs(i * w - (int)in[i * 256 + w2]);
+            if (sumerr < werr || (werr == sumerr && w2 == w) || wpos < 0) {
+                werr = sumerr;
+                wpos = w2;
+            }
+        }
+        for (int i = 0; i < 256; ++i)
+            out[i * 256 + w] = in[i * 256 + wpos];
+    }
 }
 
 /* FloatToQuantizedUnclamped<quint8>(0.0f, min, max), tf1/axqconv/quantization_utils.h:49-64. */

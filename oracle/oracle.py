@@ -1,7 +1,8 @@
 """TEST INFRASTRUCTURE - ctypes bindings of the checker libraries.
 
 `libaxc_oracle.so` is the C restatement (oracle/axc_oracle.c); `_ref/libaxc_ref.so`
-is the reference's own CPU kernel translation unit built by oracle/Makefile.
+is the reference's own CPU kernel translation unit and `_ref/libaxq_ref.so` its
+first-generation quantised op, both built by oracle/Makefile from the reference checkout.
 Only tests, the smoke check and the CPU-baseline leg of the benchmark may import
 this module; the shipped package never does.
 """
@@ -14,6 +15,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(_HERE, "libaxc_oracle.so")
 REF_SO = os.path.join(_HERE, "_ref", "libaxc_ref.so")
+AXQ_REF_SO = os.path.join(_HERE, "_ref", "libaxq_ref.so")
 
 SAME, VALID = 0, 1
 
@@ -74,6 +76,8 @@ def lib():
                                           [C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_int32), C.c_int]
         L.axo_qconv2d.argtypes = [C.POINTER(ConvDesc), C.POINTER(C.c_uint16), C.POINTER(C.c_uint8), C.POINTER(C.c_uint8),
                                   C.c_int, C.c_int, C.POINTER(C.c_int32)]
+        L.axo_tune_table.argtypes = [C.POINTER(C.c_uint16), C.POINTER(C.c_uint16)]
+        L.axo_tune_table.restype = None
         L.axo_quantized_zero_point.argtypes = [C.c_float, C.c_float]
         L.axo_quantized_zero_point.restype = C.c_int32
         L.axo_quantized_output_range.argtypes = [C.c_float] * 4 + [C.POINTER(C.c_float)] * 2
@@ -177,6 +181,14 @@ def qconv2d(d, lut, qin, qf, input_offset, filter_offset):
     return out
 
 
+def tune_table(lut):
+    """Weight tuning of the first-generation op (tf1/axqconv/approximate_selector.h:46-78)."""
+    lut = np.ascontiguousarray(lut, np.uint16).reshape(65536)
+    out = np.zeros(65536, np.uint16)
+    lib().axo_tune_table(_ptr(lut, C.c_uint16), _ptr(out, C.c_uint16))
+    return out
+
+
 def quantized_zero_point(range_min, range_max):
     return int(lib().axo_quantized_zero_point(range_min, range_max))
 
@@ -225,6 +237,50 @@ def ref_lib():
                                 [C.c_float] * 4 + [C.POINTER(C.c_float)]
         _ref = R
     return _ref
+
+
+_axq = None
+
+
+def axq_ref_available():
+    return os.path.exists(AXQ_REF_SO)
+
+
+def axq_ref_lib():
+    global _axq
+    if _axq is None:
+        R = C.CDLL(AXQ_REF_SO)
+        R.refq_table.argtypes = [C.c_char_p, C.c_int, C.POINTER(C.c_int32)]
+        R.refq_conv2d.argtypes = [C.c_char_p, C.c_int, C.POINTER(C.c_uint8)] + [C.c_int] * 4 + [C.POINTER(C.c_uint8)] + \
+                                 [C.c_int] * 3 + [C.c_float] * 4 + [C.c_int, C.c_int, C.POINTER(C.c_int32),
+                                                                    C.POINTER(C.c_float), C.POINTER(C.c_float)]
+        _axq = R
+    return _axq
+
+
+def axq_ref_table(name, tune):
+    """The table the reference's multiplier selector builds for `name` (e.g. 'mul8u_L40'), int32[65536]."""
+    t = np.zeros(65536, np.int32)
+    if axq_ref_lib().refq_table(name.encode(), 1 if tune else 0, _ptr(t, C.c_int32)):
+        raise ValueError("unknown multiplier " + name)
+    return t
+
+
+def axq_ref_conv2d(name, tune, qin, qf, min_input, max_input, min_filter, max_filter, stride, padding):
+    """One Compute() of the reference's AxConv2D: (int32 output, min_output, max_output)."""
+    qin = np.ascontiguousarray(qin, np.uint8)
+    qf = np.ascontiguousarray(qf, np.uint8)
+    n, h, w, c = qin.shape
+    kh, kw, _, co = qf.shape
+    oh, ow, _, _ = out_dims(desc(n, h, w, c, kh, kw, co, (stride, stride), (1, 1), padding))
+    out = np.zeros((n, oh, ow, co), np.int32)
+    lo, hi = C.c_float(), C.c_float()
+    rc = axq_ref_lib().refq_conv2d(name.encode(), 1 if tune else 0, _ptr(qin, C.c_uint8), n, h, w, c, _ptr(qf, C.c_uint8),
+                                   kh, kw, co, min_input, max_input, min_filter, max_filter, stride,
+                                   1 if padding == "SAME" else 0, _ptr(out, C.c_int32), C.byref(lo), C.byref(hi))
+    if rc:
+        raise ValueError("the reference op reported an error")
+    return out, lo.value, hi.value
 
 
 class RefOp:

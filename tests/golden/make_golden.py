@@ -7,6 +7,10 @@ checkout is mounted: `python tests/golden/make_golden.py [/path/to/tf-approximat
   oracle_aux.npz  integer accumulators / quantised operands of the dense cases and all outputs of the
                   depthwise cases, from the C restatement (the reference keeps no integer outputs and
                   has no depthwise path)
+  ref_axq.npz     outputs of the REFERENCE's first-generation op AxConv2D (oracle/_ref/libaxq_ref.so: the
+                  reference's tf1/axqconv/axqconv.cc compiled where it lies) on the seeded quantised cases, the
+                  plain tables of the multipliers those cases name and their tuned forms, both from the
+                  reference's own multiplier selector
   tables.json     sha256 + 32 sampled entries of each truth-table file shipped by the reference
 """
 import hashlib
@@ -63,6 +67,24 @@ def main(ref_root):
         aux[name + "_acc"] = r["acc"]
         aux[name + "_out_ref"] = r["out_ref"]
         aux[name + "_out_exact"] = r["out_exact"]
+    assert O.axq_ref_available(), "the reference's first-generation op did not build"
+    axq = {}
+    for name in cases.AXQ_MULTIPLIERS:
+        plain, tuned = O.axq_ref_table(name, False), O.axq_ref_table(name, True)
+        assert plain.min() >= 0 and plain.max() <= 65535
+        axq["table_" + name] = plain.astype(np.uint16)
+        # the tuned table is a column selection of the plain one: keep the selection
+        cols = np.array([next(w2 for w2 in ([w] + list(range(256)))
+                              if np.array_equal(tuned.reshape(256, 256)[:, w], plain.reshape(256, 256)[:, w2]))
+                         for w in range(256)], np.uint8)
+        assert np.array_equal(plain.reshape(256, 256)[:, cols].reshape(-1), tuned)
+        axq["tuned_columns_" + name] = cols
+    for name, ishape, fshape3, stride, pad, mult, tune, rin, rf, seed in cases.AXQ_CASES:
+        qin, qf = cases.make_axq_operands(ishape, fshape3, seed)
+        out, lo, hi = O.axq_ref_conv2d(mult, tune, qin, qf, rin[0], rin[1], rf[0], rf[1], stride, pad)
+        axq[name + "_out"] = out
+        axq[name + "_range"] = np.array([lo, hi], np.float32)
+    np.savez_compressed(os.path.join(HERE, "ref_axq.npz"), **axq)
     np.savez_compressed(os.path.join(HERE, "ref_dense.npz"), **ref_out)
     np.savez_compressed(os.path.join(HERE, "oracle_aux.npz"), **aux)
 

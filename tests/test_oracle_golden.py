@@ -166,3 +166,23 @@ def test_table_loader_rejects_short_file(built, tmp_path):
         O.load_table(str(p))
     with pytest.raises(ValueError):
         O.load_table(str(tmp_path / "missing.bin"))
+
+
+def test_quantised_op_golden(built):
+    """The checker's integer functor, weight tuning, zero points and output range against outputs of the
+    reference's own AxConv2D (ref_axq.npz)."""
+    gold = np.load(os.path.join(GDIR, "ref_axq.npz"))
+    for name in cases.AXQ_MULTIPLIERS:
+        plain = gold["table_" + name]
+        tuned = plain.reshape(256, 256)[:, gold["tuned_columns_" + name]].reshape(-1)
+        assert np.array_equal(O.tune_table(plain), tuned), name
+    for name, ishape, fshape3, stride, pad, mult, tune, rin, rf, seed in cases.AXQ_CASES:
+        qin, qf = cases.make_axq_operands(ishape, fshape3, seed)
+        lut = gold["table_" + mult]
+        if tune:
+            lut = O.tune_table(lut)
+        d = O.desc(*ishape, fshape3[0], fshape3[1], fshape3[2], (stride, stride), (1, 1), pad)
+        got = O.qconv2d(d, lut, qin, qf, O.quantized_zero_point(*rin), O.quantized_zero_point(*rf))
+        assert np.array_equal(got, gold[name + "_out"]), name
+        lo, hi = O.quantized_output_range(rin[0], rin[1], rf[0], rf[1])
+        assert np.array_equal(np.array([lo, hi], np.float32).view(np.uint32), gold[name + "_range"].view(np.uint32)), name

@@ -37,6 +37,9 @@ QSHAPES = [
     (2, 8, 8, 64, 1, 1, 96, 1, "VALID", (-2.0, 2.0), (-1.0, 1.0)),
     (1, 14, 14, 8, 5, 5, 33, 1, "VALID", (-1.0, 3.0), (-0.3, 0.1)),
     (1, 21, 19, 3, 7, 7, 64, 2, "SAME", (-1.0, 1.0), (-0.2, 0.2)),
+    # ranges that do not contain 0: zero points outside 0..255; a padded tap then reads offset mod 256
+    (1, 10, 12, 6, 3, 3, 24, 1, "SAME", (0.5, 2.0), (-0.3, 0.1)),
+    (2, 9, 9, 10, 3, 3, 17, 2, "SAME", (-3.0, -1.0), (0.2, 0.9)),
 ]
 
 
@@ -51,6 +54,8 @@ def test_checker_functor_equals_integer_convolution_with_exact_table(built, shap
     n, h, w, c, kh, kw, co, stride, pad, rin, rf = shape
     qin, qf = _operands(shape, 5)
     off_in, off_f = O.quantized_zero_point(*rin), O.quantized_zero_point(*rf)
+    if not 0 <= off_in <= 255:
+        pytest.skip("a padded tap wraps modulo 256 there: not the plain integer convolution")
     got = O.qconv2d(O.desc(n, h, w, c, kh, kw, co, (stride, stride), (1, 1), pad), O.exact_table(), qin, qf, off_in, off_f)
     assert np.array_equal(got.astype(np.int64), _int_conv(qin, qf, off_in, off_f, stride, pad))
 
@@ -80,13 +85,33 @@ def test_ax_conv2d_matches_checker(built, shape):
     n, h, w, c, kh, kw, co, stride, pad, rin, rf = shape
     qin, qf = _operands(shape, 7)
     lut = cases.make_table(("noisy", 61))
-    y, lo, hi = ax.ax_conv2d(torch.from_numpy(qin).cuda(), torch.from_numpy(qf).cuda(), rin[0], rin[1], rf[0], rf[1],
-                             [1, stride, stride, 1], pad, table=ax.Table(array=lut))
-    torch.cuda.synchronize()
     off_in, off_f = O.quantized_zero_point(*rin), O.quantized_zero_point(*rf)
-    want = O.qconv2d(O.desc(n, h, w, c, kh, kw, co, (stride, stride), (1, 1), pad), lut, qin, qf, off_in, off_f)
-    assert np.array_equal(y.cpu().numpy(), want)
-    assert (lo, hi) == O.quantized_output_range(rin[0], rin[1], rf[0], rf[1])
+    d = O.desc(n, h, w, c, kh, kw, co, (stride, stride), (1, 1), pad)
+    for tune in (False, True):
+        y, lo, hi = ax.ax_conv2d(torch.from_numpy(qin).cuda(), torch.from_numpy(qf).cuda(), rin[0], rin[1], rf[0], rf[1],
+                                 [1, stride, stride, 1], pad, table=ax.Table(array=lut), ax_tune=tune)
+        torch.cuda.synchronize()
+        want = O.qconv2d(d, O.tune_table(lut) if tune else lut, qin, qf, off_in, off_f)
+        assert np.array_equal(y.cpu().numpy(), want), tune
+        assert (lo, hi) == O.quantized_output_range(rin[0], rin[1], rf[0], rf[1])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", cases.AXQ_CASES, ids=[c[0] for c in cases.AXQ_CASES])
+def test_ax_conv2d_matches_the_reference_op(built, case):
+    """Against outputs of the reference's own AxConv2D (tests/golden/ref_axq.npz, made by tests/golden/make_golden.py
+    from the op compiled out of the reference checkout), with the reference's multiplier tables."""
+    import os
+    import torch
+    import tf_approximate_b200 as ax
+    gold = np.load(os.path.join(os.path.dirname(os.path.abspath(cases.__file__)), "ref_axq.npz"))
+    name, ishape, fshape3, stride, pad, mult, tune, rin, rf, seed = case
+    qin, qf = cases.make_axq_operands(ishape, fshape3, seed)
+    y, lo, hi = ax.ax_conv2d(torch.from_numpy(qin).cuda(), torch.from_numpy(qf).cuda(), rin[0], rin[1], rf[0], rf[1],
+                             [1, stride, stride, 1], pad, table=ax.Table(array=gold["table_" + mult]), ax_tune=tune)
+    torch.cuda.synchronize()
+    assert np.array_equal(y.cpu().numpy(), gold[name + "_out"])
+    assert np.array_equal(np.array([lo, hi], np.float32).view(np.uint32), gold[name + "_range"].view(np.uint32))
 
 
 @pytest.mark.gpu
@@ -100,6 +125,8 @@ def test_ax_conv2d_refuses_what_the_reference_refuses(built):
     with pytest.raises(ax.InvalidArgumentError):          # dilation (:320-323)
         ax.ax_conv2d(x, f, -1, 1, -1, 1, [1, 1, 1, 1], "SAME", dilations=[1, 2, 2, 1])
     x21 = torch.zeros((1, 21, 21, 4), dtype=torch.uint8, device="cuda")
+    with pytest.raises(ax.InvalidArgumentError):          # a range far from 0: the functor's int32 total would overflow
+        ax.ax_conv2d(x, f, 1000.0, 1000.5, -1, 1, [1, 1, 1, 1], "SAME")
     with pytest.raises(ax.UnimplementedError):            # stride 8 over a 3x3 window on 21 pixels: the functor would start
         ax.ax_conv2d(x21, f, -1, 1, -1, 1, [1, 8, 8, 1], "SAME")   # the window at +1 (:153-163), TensorFlow's padding rule at 0
 

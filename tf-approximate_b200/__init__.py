@@ -11,7 +11,7 @@ the host-side mirror of the reference's Python-visible interface:
 """
 from .errors import InvalidArgumentError, UnimplementedError, InternalError, CudaError  # noqa: F401
 from .tables import (exact_table, truncated_table, noisy_table, write_table, read_table,  # noqa: F401
-                     table_from_function, table_from_c_source, table_report, validate_table_file)
+                     table_from_function, table_from_c_source, table_report, tune_table, validate_table_file)
 from .ops import (approx_conv2d_with_min_max_vars, approx_depthwise_conv2d_with_min_max_vars,  # noqa: F401
                   ax_conv2d, approx_conv2d,
                   conv2d_output_shape, launch_count, measure_lookup_peak, Table)

@@ -8,7 +8,7 @@ from . import _build
 # every symbol include/axconv.h declares
 SYMBOLS = [
     "axc_table_create_from_file", "axc_table_create_from_memory", "axc_table_create_exact",
-    "axc_table_destroy", "axc_table_host_data", "axc_table_ensure_device",
+    "axc_table_destroy", "axc_table_tune_weights", "axc_table_host_data", "axc_table_ensure_device",
     "axc_conv2d_output_dims", "axc_depthwise_conv2d_output_dims",
     "axc_conv2d_workspace_bytes", "axc_depthwise_conv2d_workspace_bytes", "axc_conv2d_plan_info",
     "axc_conv2d_forward", "axc_conv2d_forward_device_ranges", "axc_depthwise_conv2d_forward",
@@ -57,6 +57,7 @@ def load():
     L.axc_table_create_from_file.argtypes = [C.c_char_p, C.c_int, C.POINTER(C.c_void_p)]
     L.axc_table_create_from_memory.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
     L.axc_table_create_exact.argtypes = [C.POINTER(C.c_void_p)]
+    L.axc_table_tune_weights.argtypes = [C.c_void_p, C.c_void_p]
     L.axc_table_destroy.argtypes = [C.c_void_p]
     L.axc_table_destroy.restype = None
     L.axc_table_host_data.argtypes = [C.c_void_p, C.POINTER(C.POINTER(C.c_uint16))]

@@ -389,6 +389,38 @@ void axc_table_destroy(axc_table *t)
     delete t;
 }
 
+// Weight tuning of the first-generation op (tf1/axqconv/approximate_selector.h:46-78): per weight w the column
+// that is closest to the exact products in summed absolute error stands in for column w.
+int axc_table_tune_weights(const uint16_t *in, uint16_t *out)
+{
+    if (!in || !out) return AXC_INVALID_ARGUMENT;
+    // err[w][w2] = sum_i |i*w - in[i][w2]| is needed for all pairs; walk i outermost so that rows stream
+    std::vector<int> err(256 * 256, 0);
+    for (int i = 0; i < 256; ++i) {
+        const uint16_t *row = in + i * 256;
+        for (int w = 0; w < 256; ++w) {
+            const int exact = i * w;
+            int *e = err.data() + w * 256;
+            for (int w2 = 0; w2 < 256; ++w2) {
+                const int d = exact - int(row[w2]);
+                e[w2] += d < 0 ? -d : d;
+            }
+        }
+    }
+    int map[256];
+    for (int w = 0; w < 256; ++w) {
+        const int *e = err.data() + w * 256;
+        int best = 0;
+        for (int w2 = 1; w2 < 256; ++w2)
+            if (e[w2] < e[best]) best = w2;
+        map[w] = e[w] == e[best] ? w : best;      // w itself among the best columns wins, else the lowest index
+    }
+    std::vector<uint16_t> tmp(in, in + 65536);    // `in` and `out` may alias
+    for (int i = 0; i < 256; ++i)
+        for (int w = 0; w < 256; ++w) out[i * 256 + w] = tmp[i * 256 + map[w]];
+    return AXC_OK;
+}
+
 int axc_table_host_data(const axc_table *t, const uint16_t **out)
 {
     if (!t || !out) return AXC_INVALID_ARGUMENT;

@@ -2,12 +2,14 @@
 // `AxConv2D` (tf1/axqconv/axqconv.cc:66-94): every product of the integer convolution is a table lookup and the sum
 // carries the zero-point corrections of the reference functor (tf1/axqconv/axqconv.cc:197-263)
 //     total = sum_l ( LUT[a_l][b_l] - a_l * filter_offset - b_l * input_offset + input_offset * filter_offset ),
-// where a tap outside the image has a_l = input_offset.
+// where a tap outside the image has a_l = input_offset modulo 256: the functor stores the offset into its uint8
+// operand type (:203-214), so an offset outside 0..255 (a range that does not contain 0) wraps there and only there.
 //
-// The table sums come from the same kernels as the fp32 op: the uint8 operands are written out as fp32 values
-// q - offset, and the op is called with the ranges [-offset, 255 - offset], for which its quantiser has scale 1 and
-// zero point `offset`: it maps q - offset back to q exactly, and 0.0 (a padded tap) to `offset`.  The integer sums
-// of the op (its accumulator tap) go straight to the caller's output; a second pass subtracts the zero-point terms.
+// The table sums come from the same kernels as the fp32 op: the uint8 input is written out as fp32 values
+// q - pad, pad = input_offset & 255, and the op is called with the range [-pad, 255 - pad], for which its quantiser
+// has scale 1 and zero point `pad`: it maps q - pad back to q exactly, and 0.0 (a padded tap) to `pad`; the filter
+// goes through as q with the range [0, 255].  The integer sums of the op (its accumulator tap) go straight to the
+// caller's output; a second pass subtracts the zero-point terms.
 #include "axc_internal.h"
 #include "axc_sched.h"
 
@@ -38,10 +40,10 @@ struct CorrParams {
     int32_t *out;
     int N, H, W, C, KH, KW, Cout, sh, sw, dh, dw, ph, pw, OH, OW, K;
     long long M;
-    int in_off, f_off;
+    int in_off, f_off, pad_code;
 };
 
-// One warp per output pixel: A = sum of the patch's quantised taps (input_offset where the tap is outside the image),
+// One warp per output pixel: A = sum of the patch's quantised taps (pad_code where the tap is outside the image),
 // then out[p][j] += K*in_off*f_off - f_off*A - in_off*bsum[j] for all channels.
 __global__ void __launch_bounds__(256) qconv_correct_kernel(const CorrParams P)
 {
@@ -60,7 +62,7 @@ __global__ void __launch_bounds__(256) qconv_correct_kernel(const CorrParams P)
                 const int ix = ow * P.sw - P.pw + kx * P.dw;
                 const bool inside = iy >= 0 && iy < P.H && ix >= 0 && ix < P.W;
                 const uint8_t *src = P.qin + (((long long)n * P.H + (inside ? iy : 0)) * P.W + (inside ? ix : 0)) * P.C;
-                for (int c = lane; c < P.C; c += 32) a += inside ? int(src[c]) : P.in_off;
+                for (int c = lane; c < P.C; c += 32) a += inside ? int(src[c]) : P.pad_code;
             }
         }
 #pragma unroll
@@ -123,11 +125,17 @@ extern "C" int axc_qconv2d_forward(axc_table *table, const axc_conv_desc *desc, 
     if (rc) return rc;
     if (g.M * g.Cout == 0) return AXC_OK;
     if (!qinput || !qfilter || !output) return AXC_INVALID_ARGUMENT;
-    if (input_offset < 0 || input_offset > 255 || filter_offset < 0 || filter_offset > 255) return AXC_INVALID_ARGUMENT;
+    {
+        // the reference's int32 total must not overflow: bound every term of the sum
+        const long long ai = input_offset < 0 ? -(long long)input_offset : input_offset, af = filter_offset < 0 ? -(long long)filter_offset : filter_offset;
+        const long long mi = ai > 255 ? ai : 255, mf = af > 255 ? af : 255;
+        if (mi > 0x7FFFFFFFll / mf || (long long)g.K > 0x7FFFFFFFll / (mi * mf)) return AXC_INVALID_ARGUMENT;
+    }
+    const int pad_code = input_offset & 255;
     // AxQuantizedConv2DOp accepts equal strides and no dilation only (tf1/axqconv/axqconv.cc:305-326)
     if (g.sh != g.sw || g.dh != 1 || g.dw != 1) return AXC_INVALID_ARGUMENT;
     if (!same_window_as_reference(g, desc->padding)) return AXC_UNIMPLEMENTED;
-    if (!table_sum_fits_int32(table, g.K) || (long long)g.K * 255 * 255 > 0x7FFFFFFFll) return AXC_INVALID_ARGUMENT;
+    if (!table_sum_fits_int32(table, g.K)) return AXC_INVALID_ARGUMENT;
     const QLayout L = qconv_layout(g);
     if (!workspace || workspace_bytes < L.total) return AXC_INTERNAL;
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return AXC_INVALID_ARGUMENT;
@@ -145,13 +153,13 @@ extern "C" int axc_qconv2d_forward(axc_table *table, const axc_conv_desc *desc, 
     int *bsum = reinterpret_cast<int *>(ws + L.bsum_off);
     const long long n_in = (long long)g.N * g.H * g.W * g.C, n_f = (long long)g.K * g.Cout;
     auto blocks = [](long long n) { return unsigned(n / 256 + 1 < 8192 ? n / 256 + 1 : 8192); };
-    u8_to_grid_kernel<<<blocks(n_in), 256, 0, s>>>(qinput, n_in, input_offset, xin);
-    u8_to_grid_kernel<<<blocks(n_f), 256, 0, s>>>(qfilter, n_f, filter_offset, xf);
+    u8_to_grid_kernel<<<blocks(n_in), 256, 0, s>>>(qinput, n_in, pad_code, xin);
+    u8_to_grid_kernel<<<blocks(n_f), 256, 0, s>>>(qfilter, n_f, 0, xf);
     cudaError_t e = cudaGetLastError();
     count_launch(2);
     if (e == cudaSuccess) {
-        // scale 1, zero point = offset: the op's quantiser returns the caller's bytes, and `offset` for a padded tap
-        const Quant q = make_quant(float(-input_offset), float(255 - input_offset), float(-filter_offset), float(255 - filter_offset));
+        // scale 1, zero point = pad_code: the op's quantiser returns the caller's bytes, and pad_code for a padded tap
+        const Quant q = make_quant(float(-pad_code), float(255 - pad_code), 0.0f, 255.0f);
         axc_debug_out taps = {nullptr, nullptr, output};
         Geom ge = g;
         ge.accum = AXC_ACCUM_EXACT_I32;
@@ -164,7 +172,7 @@ extern "C" int axc_qconv2d_forward(axc_table *table, const axc_conv_desc *desc, 
         P.qin = qinput; P.bsum = bsum; P.out = output;
         P.N = g.N; P.H = g.H; P.W = g.W; P.C = g.C; P.KH = g.KH; P.KW = g.KW; P.Cout = g.Cout;
         P.sh = g.sh; P.sw = g.sw; P.dh = g.dh; P.dw = g.dw; P.ph = g.ph; P.pw = g.pw; P.OH = g.OH; P.OW = g.OW; P.K = g.K;
-        P.M = g.M; P.in_off = input_offset; P.f_off = filter_offset;
+        P.M = g.M; P.in_off = input_offset; P.f_off = filter_offset; P.pad_code = pad_code;
         const long long warps = g.M;
         qconv_correct_kernel<<<unsigned(warps / 8 + 1 < 4096 ? warps / 8 + 1 : 4096), 256, 0, s>>>(P);
         e = cudaGetLastError();

@@ -50,6 +50,14 @@ class Table:
         raise_for_status(_lib.load().axc_table_host_data(self._h, C.byref(p)), "table data")
         return np.ctypeslib.as_array(p, shape=(65536,)).copy()
 
+    def tuned(self):
+        """The table after the first-generation op's weight tuning (tables.tune_table), made once per table."""
+        t = getattr(self, "_tuned", None)
+        if t is None:
+            from .tables import tune_table
+            t = self._tuned = Table(array=tune_table(self.numpy()))
+        return t
+
     def ensure_device(self, device):
         raise_for_status(_lib.load().axc_table_ensure_device(self._h, int(device)), "table upload", _cuda_detail())
 
@@ -322,16 +330,19 @@ def approx_depthwise_conv2d_with_min_max_vars(input, filter, input_min, input_ma
 
 
 def ax_conv2d(input, filter, min_input, max_input, min_filter, max_filter, strides, padding, table="",
-              dilations=(1, 1, 1, 1), out=None):
+              dilations=(1, 1, 1, 1), out=None, ax_tune=True):
     """Mirror of the reference's first-generation op `AxConv2D` (tf1/axqconv/axqconv.cc:66-94): quantised uint8
     input [N,H,W,C] and filter [KH,KW,C,Cout] with their float ranges in; returns (output int32 [N,OH,OW,Cout],
     min_output, max_output).  `table` stands for the op's AxMult attribute: a `Table` or a table file ('' = exact
-    products).  The offsets are the codes of 0.0 in the two ranges (:365-368); the int32 output is the table sum
-    with the functor's zero-point terms (:241-246)."""
+    products); `ax_tune` for its AxTune attribute (default true, as there): the table's weight columns are re-mapped
+    to the closest ones first (tf1/axqconv/approximate_selector.h:46-78).  The offsets are the codes of 0.0 in the
+    two ranges (:365-368); the int32 output is the table sum with the functor's zero-point terms (:241-246)."""
     L = _lib.load()
     if input.dtype != torch.uint8 or filter.dtype != torch.uint8 or not input.is_cuda or not filter.is_cuda:
         raise InvalidArgumentError("input and filter must be uint8 CUDA tensors")
     tab = _table_for(table, 8)
+    if ax_tune:
+        tab = tab.tuned()
     d = _desc(input.shape, filter.shape, strides, padding, "NHWC", list(dilations), [])
     dims = (C.c_int64 * 4)()
     raise_for_status(L.axc_conv2d_output_dims(C.byref(d), dims), "AxConv2D")

@@ -54,20 +54,43 @@ def table_from_function(fn):
 
 
 def table_from_c_source(c_path, symbol, cc="gcc"):
-    """Compiles a C file that defines `uint16_t symbol(uint8_t a, uint8_t b)` - the form of the EvoApprox
-    multipliers the reference ships (tf1/axqconv/axmult/*.c) - and tabulates it."""
+    """Compiles a C file that defines the multiplier `symbol(a, b)` and tabulates it.  Handles the two forms of
+    the EvoApprox multipliers the reference ships (tf1/axqconv/axmult/*.c): `uint16_t f(uint8_t a, uint8_t b)` and
+    `uint64_t f(const uint64_t B, const uint64_t A)`; the first parameter is the activation either way (the
+    reference calls f(data, weight), tf1/axqconv/approximate_selector.h:38-41)."""
     import ctypes
     import os
+    import re
     import subprocess
     import tempfile
+    with open(c_path) as fh:
+        m = re.search(r"(uint\d+_t)\s+" + re.escape(symbol) + r"\s*\(\s*(?:const\s+)?(uint\d+_t)", fh.read())
+    if m is None:
+        raise ValueError("no function %s with unsigned integer parameters in %s" % (symbol, c_path))
+    ctype = {"uint8_t": ctypes.c_uint8, "uint16_t": ctypes.c_uint16, "uint32_t": ctypes.c_uint32, "uint64_t": ctypes.c_uint64}
     with tempfile.TemporaryDirectory() as tmp:
         so = os.path.join(tmp, "mul.so")
         subprocess.run([cc, "-O2", "-shared", "-fPIC", "-o", so, c_path], check=True, capture_output=True)
         lib = ctypes.CDLL(so)
         f = getattr(lib, symbol)
-        f.restype = ctypes.c_uint16
-        f.argtypes = [ctypes.c_uint8, ctypes.c_uint8]
+        f.restype = ctype[m.group(1)]
+        f.argtypes = [ctype[m.group(2)]] * 2
         return table_from_function(lambda a, b: f(a, b))
+
+
+def tune_table(table):
+    """Weight tuning of the reference's first-generation op (attribute AxTune of AxConv2D, on by default there;
+    tf1/axqconv/approximate_selector.h:46-78): every weight column is replaced by the column that is closest to the
+    exact products."""
+    import ctypes
+    from . import _lib
+    from .errors import raise_for_status
+    t = np.ascontiguousarray(table, dtype=np.uint16).reshape(-1)
+    if t.size != 65536:
+        raise ValueError("a truth table has 65536 entries")
+    out = np.empty(65536, np.uint16)
+    raise_for_status(_lib.load().axc_table_tune_weights(ctypes.c_void_p(t.ctypes.data), ctypes.c_void_p(out.ctypes.data)), "table tuning")
+    return out
 
 
 def table_report(table):
