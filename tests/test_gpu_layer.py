@@ -20,11 +20,11 @@ def test_layer_forward_matches_op_and_float_conv(built):
     xq = ax.fake_quant_with_min_max_vars(x, float(x.min()), float(x.max()))
     wq = ax.fake_quant_with_min_max_vars(layer.kernel.detach(), float(layer.kernel.detach().min()), float(layer.kernel.detach().max()))
     y_op = ax.approx_conv2d_with_min_max_vars(xq, wq, float(x.min()), float(x.max()), float(layer.kernel.detach().min()),
-                                              float(layer.kernel.detach().max()), [1, 1, 1, 1], 8, "", "SAME") + layer.bias
+                                              float(layer.kernel.detach().max()), [1, 1, 1, 1], 8, "", "SAME") + layer.bias.detach()
     assert torch.equal(y.detach(), y_op)
     # exact table + fake-quantised operands = the float convolution of those operands (the reference's own test)
     ref = torch.nn.functional.conv2d(xq.permute(0, 3, 1, 2).double(), wq.permute(3, 2, 0, 1).double(), padding=1)
-    ref = ref.permute(0, 2, 3, 1) + layer.bias.double()
+    ref = ref.permute(0, 2, 3, 1) + layer.bias.detach().double()
     err = float((y.detach().double() - ref).abs().max() / ref.abs().max())
     assert err < 1e-5, err
 
