@@ -448,6 +448,17 @@ def run_layer(args):
         def fn(x_, f_, *a, **k_):      # noqa: F811 - same call shape as the op
             with torch.no_grad():
                 return layer(x_)
+    if args.quantised and not dw:
+        # the first-generation op's contract: uint8 codes in, int32 sums with zero-point terms out (weight tuning is a
+        # transformation of the table, done once, outside the timed calls)
+        xq = torch.randint(0, 256, (n, h, w, c), device=dev, generator=g, dtype=torch.uint8)
+        fq = torch.randint(0, 256, (k, k, c, cout), device=dev, generator=g, dtype=torch.uint8)
+        x, f = xq, fq
+        mm = (-1.0, 1.0, -0.5, 0.5)
+        tuned = table.tuned()
+
+        def fn(x_, f_, a, b, c_, d, strides, bits, tab, pad, out=None, **k_):      # noqa: F811 - same call shape as the op
+            return ax.ax_conv2d(x_, f_, a, b, c_, d, strides, pad, table=tuned, out=out, ax_tune=False)[0]
     out = None
     for _ in range(args.warmup):
         out = fn(x, f, *mm, [1, stride, stride, 1], 8, table, "SAME", out=out, **kw)
@@ -461,8 +472,9 @@ def run_layer(args):
     ms = e0.elapsed_time(e1) / args.steps
     oh, ow = -(-h // stride), -(-w // stride)
     macs = n * oh * ow * k * k * c * (1 if dw else cout)
-    io = 4 * (x.numel() + out.numel() + f.numel())
+    io = x.numel() * x.element_size() + out.numel() * out.element_size() + f.numel() * f.element_size()
     print(json.dumps({"layer": args.layer, "table": args.table, "accumulate": args.accumulate, "via_layer": args.via_layer,
+                      "quantised": bool(args.quantised),
                       "ms": ms, "lut_macs": macs,
                       "glut_macs_per_s": macs / ms / 1e6, "lookups_per_clk_per_sm_at_1965MHz": macs / (ms * 1e-3) / (SM_COUNT * 1965e6),
                       "io_gbs": io / ms / 1e6}))
@@ -503,6 +515,8 @@ def main():
                     help="run shortcut additions and ReLUs as separate element-wise kernels (default: fused into the convolutions)")
     ap.add_argument("--via-layer", default=None, choices=["eval", "train"],
                     help="--layer only: time the layer-level caller (range reductions + fake quantisation + op)")
+    ap.add_argument("--quantised", action="store_true",
+                    help="--layer only: time the uint8-in / int32-out entry point (first-generation op) on random codes")
     ap.add_argument("--accumulate", default="exact", choices=["exact", "reference"],
                     help="--layer only: exact integer sum (default) or the reference's fp32 running total in K order")
     args = ap.parse_args()

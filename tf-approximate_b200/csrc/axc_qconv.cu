@@ -34,8 +34,29 @@ __global__ void qfilter_sum_kernel(const uint8_t *__restrict__ qf, int K, int Co
     bsum[j] = s;
 }
 
+// psum[p] = sum_c qin[p][c] for every input pixel p (the zero-point terms need the sum of a patch's codes: nine of
+// these for a 3x3 window instead of 9*C bytes)
+__global__ void qpixel_sum_kernel(const uint8_t *__restrict__ q, long long pixels, int C, int vec_ok, int *__restrict__ psum)
+{
+    long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; p < pixels; p += stride) {
+        const uint8_t *src = q + p * C;
+        int s = 0;
+        if (vec_ok) {
+            const uint32_t *w = reinterpret_cast<const uint32_t *>(src);
+            unsigned acc = 0;
+            for (int c = 0; c < C / 4; ++c) acc = __dp4a(__ldg(w + c), 0x01010101u, acc);
+            s = int(acc);
+        } else {
+            for (int c = 0; c < C; ++c) s += int(__ldg(src + c));
+        }
+        psum[p] = s;
+    }
+}
+
 struct CorrParams {
-    const uint8_t *qin;
+    const int *psum;
     const int *bsum;
     int32_t *out;
     int N, H, W, C, KH, KW, Cout, sh, sw, dh, dw, ph, pw, OH, OW, K;
@@ -43,27 +64,25 @@ struct CorrParams {
     int in_off, f_off, pad_code;
 };
 
-// One warp per output pixel: A = sum of the patch's quantised taps (pad_code where the tap is outside the image),
-// then out[p][j] += K*in_off*f_off - f_off*A - in_off*bsum[j] for all channels.
+// One warp per output pixel: A = sum of the patch's quantised taps (pad_code where the tap is outside the image), one
+// window position per lane, then out[p][j] += K*in_off*f_off - f_off*A - in_off*bsum[j] for all channels.
 __global__ void __launch_bounds__(256) qconv_correct_kernel(const CorrParams P)
 {
     const int lane = threadIdx.x & 31;
     const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    const int taps = P.KH * P.KW;
     for (long long p = warp0; p < P.M; p += nwarps) {
         const int ow = int(p % P.OW);
         const long long t = p / P.OW;
         const int oh = int(t % P.OH);
         const int n = int(t / P.OH);
         int a = 0;
-        for (int ky = 0; ky < P.KH; ++ky) {
-            const int iy = oh * P.sh - P.ph + ky * P.dh;
-            for (int kx = 0; kx < P.KW; ++kx) {
-                const int ix = ow * P.sw - P.pw + kx * P.dw;
-                const bool inside = iy >= 0 && iy < P.H && ix >= 0 && ix < P.W;
-                const uint8_t *src = P.qin + (((long long)n * P.H + (inside ? iy : 0)) * P.W + (inside ? ix : 0)) * P.C;
-                for (int c = lane; c < P.C; c += 32) a += inside ? int(src[c]) : P.pad_code;
-            }
+        for (int tap = lane; tap < taps; tap += 32) {
+            const int ky = tap / P.KW, kx = tap - ky * P.KW;
+            const int iy = oh * P.sh - P.ph + ky * P.dh, ix = ow * P.sw - P.pw + kx * P.dw;
+            const bool inside = iy >= 0 && iy < P.H && ix >= 0 && ix < P.W;
+            a += inside ? __ldg(P.psum + ((long long)n * P.H + iy) * P.W + ix) : P.C * P.pad_code;
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
@@ -76,7 +95,7 @@ __global__ void __launch_bounds__(256) qconv_correct_kernel(const CorrParams P)
 size_t r256(size_t v) { return (v + 255) & ~size_t(255); }
 
 struct QLayout {
-    size_t dense_bytes, xin_off, xf_off, bsum_off, total;
+    size_t dense_bytes, xin_off, xf_off, bsum_off, psum_off, total;
 };
 
 QLayout qconv_layout(const Geom &g)
@@ -86,7 +105,8 @@ QLayout qconv_layout(const Geom &g)
     L.xin_off = L.dense_bytes;
     L.xf_off = L.xin_off + r256(size_t(g.N) * g.H * g.W * g.C * 4);
     L.bsum_off = L.xf_off + r256(size_t(g.K) * g.Cout * 4);
-    L.total = L.bsum_off + r256(size_t(g.Cout) * 4);
+    L.psum_off = L.bsum_off + r256(size_t(g.Cout) * 4);
+    L.total = L.psum_off + r256(size_t(g.N) * g.H * g.W * 4);
     return L;
 }
 
@@ -168,15 +188,19 @@ extern "C" int axc_qconv2d_forward(axc_table *table, const axc_conv_desc *desc, 
     }
     if (e == cudaSuccess && rc == AXC_OK && (input_offset != 0 || filter_offset != 0)) {
         qfilter_sum_kernel<<<unsigned((g.Cout + 127) / 128), 128, 0, s>>>(qfilter, g.K, g.Cout, bsum);
+        int *psum = reinterpret_cast<int *>(ws + L.psum_off);
+        const long long pixels = (long long)g.N * g.H * g.W;
+        const int vec_ok = (g.C % 4 == 0 && (reinterpret_cast<uintptr_t>(qinput) & 3u) == 0) ? 1 : 0;
+        qpixel_sum_kernel<<<blocks(pixels), 256, 0, s>>>(qinput, pixels, g.C, vec_ok, psum);
         CorrParams P;
-        P.qin = qinput; P.bsum = bsum; P.out = output;
+        P.psum = psum; P.bsum = bsum; P.out = output;
         P.N = g.N; P.H = g.H; P.W = g.W; P.C = g.C; P.KH = g.KH; P.KW = g.KW; P.Cout = g.Cout;
         P.sh = g.sh; P.sw = g.sw; P.dh = g.dh; P.dw = g.dw; P.ph = g.ph; P.pw = g.pw; P.OH = g.OH; P.OW = g.OW; P.K = g.K;
         P.M = g.M; P.in_off = input_offset; P.f_off = filter_offset; P.pad_code = pad_code;
         const long long warps = g.M;
-        qconv_correct_kernel<<<unsigned(warps / 8 + 1 < 4096 ? warps / 8 + 1 : 4096), 256, 0, s>>>(P);
+        qconv_correct_kernel<<<unsigned(warps / 8 + 1 < 16384 ? warps / 8 + 1 : 16384), 256, 0, s>>>(P);
         e = cudaGetLastError();
-        count_launch(2);
+        count_launch(3);
     }
     if (prev != device) cudaSetDevice(prev);
     if (e != cudaSuccess) return cuda_failed(e);
