@@ -146,6 +146,12 @@ SHAPES = [
     (1, 64, 64, 32, 1, 1, 192, (2, 2), (1, 1), "SAME"),   # 6 groups: 4 + 2
     (1, 64, 64, 16, 3, 3, 144, (1, 1), (1, 1), "SAME"),   # 4 + 1 groups, the last with 16 channels on two pixel tiles
     (1, 40, 40, 8, 1, 1, 267, (1, 1), (1, 1), "SAME"),    # 8 + 1 groups, the last with 11 channels
+    # few pixels, many channels: fewer CTA tiles than SMs, or a last round that is mostly empty
+    (2, 7, 7, 512, 3, 3, 512, (1, 1), (1, 1), "SAME"),    # K = 4608 in chunks, 16 groups
+    (32, 7, 7, 512, 1, 1, 512, (1, 1), (1, 1), "SAME"),   # K = 512 in one chunk, several tile groups per CTA
+    (8, 7, 7, 128, 1, 1, 128, (1, 1), (1, 1), "SAME"),    # a run of 4 groups
+    (32, 7, 7, 64, 3, 3, 128, (1, 1), (1, 1), "SAME"),    # a run of 4 groups, several tile groups per CTA
+    (4, 7, 7, 256, 1, 1, 224, (1, 1), (1, 1), "SAME"),    # 7 groups in a run of 8
 ]
 
 
