@@ -111,6 +111,8 @@ private:
 
 namespace errors {
 template <typename... Args> Status InvalidArgument(const char *msg, Args...) { return Status(msg); }
+template <typename... Args> Status Unimplemented(const char *msg, Args...) { return Status(msg); }
+template <typename... Args> Status Internal(const char *msg, Args...) { return Status(msg); }
 }  // namespace errors
 
 // Swallows any Eigen expression the header builds in functions that are never called here.

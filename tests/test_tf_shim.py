@@ -153,3 +153,63 @@ def test_shim_compute_error_paths(harness):
     code, msg, dims, _ = _compute(harness, op, empty, f, (-1.0, 1.0, -1.0, 1.0), (0, 8, 8, 8))
     assert code == 0 and dims == (0, 8, 8, 8)
     harness.shimtest_destroy(op)
+
+
+# ---------------------------------------------------------------------------------------------------
+# The first-generation op's shim (tf-approximate_b200/tf_op/axconv2d_axconv.cc), through the stand-in for the
+# TensorFlow 1.x API that also carries the reference's own op in the checker (oracle/tf1_stub/).
+# ---------------------------------------------------------------------------------------------------
+AXQ_SHIM = os.path.join(ROOT, "tf-approximate_b200", "tf_op", "axconv2d_axconv.cc")
+REF_DIR = os.path.join(ROOT, "oracle", "_ref")
+
+
+def _axq_build(tmp, link):
+    gxx = _toolchain()
+    if not (os.path.exists(os.path.join(REF_DIR, "axmult.h")) and os.path.exists(os.path.join(REF_DIR, "libaxq_ref.so"))):
+        pytest.skip("oracle/_ref not built (no reference checkout): the multiplier sources are the reference's")
+    so = os.path.join(tmp, "libaxqshim.so")
+    cmd = [gxx, "-std=c++14", "-Wall", "-Wextra", "-Werror", "-fPIC"] + (["-shared", "-o", so] if link else ["-c", "-o", os.devnull]) + \
+          ["-I" + os.path.join(ROOT, "tf-approximate_b200", "tf_op"), "-I" + os.path.join(ROOT, "oracle", "tf1_stub"), "-I" + REF_DIR,
+           "-I" + os.path.join(ROOT, "include"), "-I" + CUDA + "/include", os.path.join(ROOT, "tests", "tf_api_stub", "axq_shim_harness.cc")]
+    if link:
+        libdir, cudart = os.path.join(ROOT, "tf-approximate_b200"), os.path.join(CUDA, "lib64")
+        cmd += ["-L" + libdir, "-laxconv", "-L" + REF_DIR, "-laxq_ref", "-L" + cudart, "-lcudart",
+                "-Wl,-rpath," + libdir, "-Wl,-rpath," + REF_DIR, "-Wl,-rpath," + cudart]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    return so
+
+
+def test_first_generation_shim_compiles(built, tmp_path):
+    _axq_build(str(tmp_path), link=False)
+    text = open(AXQ_SHIM).read()
+    for needle in ('Name("AxConv2D")', ".Device(DEVICE_CPU)", '.TypeConstraint<quint8>("Tinput")',
+                   '.TypeConstraint<quint8>("Tfilter")', '.TypeConstraint<qint32>("out_type")'):
+        assert needle in text, needle                      # the reference's registration, tf1/axqconv/axqconv.cc:453-459
+
+
+@pytest.mark.gpu
+def test_first_generation_shim_reproduces_the_reference_op(built, tmp_path):
+    """Same entry point as the one around the reference's own AxConv2D (oracle/ref_axq_driver.cpp), the op replaced by
+    the shim: identical int32 outputs and ranges on the golden cases (tests/golden/ref_axq.npz)."""
+    so = _axq_build(str(tmp_path), link=True)
+    L = C.CDLL(so)
+    L.shimq_conv2d.argtypes = [C.c_char_p, C.c_int, C.c_void_p] + [C.c_int] * 4 + [C.c_void_p] + [C.c_int] * 3 + [C.c_float] * 4 + \
+                              [C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]
+    gold = np.load(os.path.join(os.path.dirname(os.path.abspath(cases.__file__)), "ref_axq.npz"))
+    for name, ishape, fshape3, stride, pad, mult, tune, rin, rf, seed in cases.AXQ_CASES:
+        qin, qf = cases.make_axq_operands(ishape, fshape3, seed)
+        want = gold[name + "_out"]
+        out = np.full(want.shape, -1, np.int32)
+        lo, hi = C.c_float(), C.c_float()
+        rc = L.shimq_conv2d(mult.encode(), int(tune), qin.ctypes.data, *ishape, qf.ctypes.data, *fshape3, rin[0], rin[1], rf[0], rf[1],
+                            stride, 1 if pad == "SAME" else 0, out.ctypes.data, C.byref(lo), C.byref(hi))
+        assert rc == 0, name
+        assert np.array_equal(out, want), name
+        assert np.array_equal(np.array([lo.value, hi.value], np.float32).view(np.uint32), gold[name + "_range"].view(np.uint32)), name
+    # an unknown multiplier is the constructor's InvalidArgument (tf1/axqconv/approximate_selector.h:33-37)
+    qin, qf = cases.make_axq_operands((1, 4, 4, 2), (1, 1, 3), 1)
+    out = np.zeros((1, 4, 4, 3), np.int32)
+    lo, hi = C.c_float(), C.c_float()
+    assert L.shimq_conv2d(b"mul8u_none", 0, qin.ctypes.data, 1, 4, 4, 2, qf.ctypes.data, 1, 1, 3, -1.0, 1.0, -1.0, 1.0, 1, 1,
+                          out.ctypes.data, C.byref(lo), C.byref(hi)) == 1
