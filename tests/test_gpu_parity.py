@@ -320,6 +320,27 @@ def test_two_streams_two_layers(ax):
         assert torch.equal(oa, ya) and torch.equal(ob, yb)
 
 
+def test_first_use_of_a_table_on_a_non_blocking_stream(ax):
+    """A table's 128 KiB replica is uploaded at its first use.  The upload must be complete before the call's kernels
+    read it, also when the caller's stream is a non-blocking one, which does not wait for the legacy stream that a
+    copy from pageable host memory is ordered on.  Fresh table handles, first use on a side stream, many times."""
+    import torch
+    rng = np.random.Generator(np.random.PCG64(43))
+    x = torch.from_numpy(rng.uniform(-1, 1, (1, 6, 6, 8)).astype(np.float32)).cuda()
+    f = torch.from_numpy(rng.normal(0, 0.1, (1, 1, 8, 32)).astype(np.float32)).cuda()
+    side = torch.cuda.Stream()
+    for i in range(40):
+        lut = cases.make_table(("noisy", 500 + i))
+        t_first = ax.Table(array=lut)
+        torch.cuda.synchronize()
+        with torch.cuda.stream(side):
+            y = ax.approx_conv2d_with_min_max_vars(x, f, -1.0, 1.0, -0.4, 0.4, [1, 1, 1, 1], 8, t_first, "SAME")
+        side.synchronize()
+        want = ax.approx_conv2d_with_min_max_vars(x, f, -1.0, 1.0, -0.4, 0.4, [1, 1, 1, 1], 8, ax.Table(array=lut), "SAME")
+        torch.cuda.synchronize()
+        assert torch.equal(y, want), i
+
+
 def test_empty_batch(ax):
     import torch
     y = ax.approx_conv2d_with_min_max_vars(torch.zeros(0, 8, 8, 4).cuda(), torch.zeros(3, 3, 4, 8).cuda(),

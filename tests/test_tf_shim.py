@@ -19,6 +19,8 @@ import cases
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SHIM = os.path.join(ROOT, "tf-approximate_b200", "tf_op", "approx_conv2d_axconv.cc")
+DW_SHIM = os.path.join(ROOT, "tf-approximate_b200", "tf_op", "approx_depthwise_conv2d_axconv.cc")
+DW_OP = b"ApproxDepthwiseConv2DWithMinMaxVars"
 CUDA = "/usr/local/cuda"
 OP = b"ApproxConv2DWithMinMaxVars"
 
@@ -30,10 +32,11 @@ def _toolchain():
     return gxx
 
 
-def test_shim_compiles_against_the_header():
+@pytest.mark.parametrize("src", [SHIM, DW_SHIM], ids=["dense", "depthwise"])
+def test_shim_compiles_against_the_header(src):
     gxx = _toolchain()
     cmd = [gxx, "-std=c++14", "-Wall", "-Wextra", "-Werror", "-c", "-o", os.devnull,
-           "-I" + os.path.join(ROOT, "tests", "tf_api_stub"), "-I" + os.path.join(ROOT, "include"), "-I" + CUDA + "/include", SHIM]
+           "-I" + os.path.join(ROOT, "tests", "tf_api_stub"), "-I" + os.path.join(ROOT, "include"), "-I" + CUDA + "/include", src]
     r = subprocess.run(cmd, capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
 
@@ -49,7 +52,7 @@ def harness(built, tmp_path_factory):
     so = str(tmp_path_factory.mktemp("shim") / "libshimtest.so")
     cmd = [gxx, "-std=c++14", "-Wall", "-Wextra", "-Werror", "-fPIC", "-shared", "-o", so,
            "-I" + os.path.join(ROOT, "tests", "tf_api_stub"), "-I" + os.path.join(ROOT, "include"), "-I" + CUDA + "/include",
-           SHIM, os.path.join(ROOT, "tests", "tf_api_stub", "shim_harness.cc"),
+           SHIM, DW_SHIM, os.path.join(ROOT, "tests", "tf_api_stub", "shim_harness.cc"),
            "-L" + libdir, "-laxconv", "-L" + cudart, "-lcudart", "-Wl,-rpath," + libdir, "-Wl,-rpath," + cudart]
     r = subprocess.run(cmd, capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
@@ -63,9 +66,10 @@ def harness(built, tmp_path_factory):
     return L
 
 
-def _create(L, table_file, strides=(1, 1, 1, 1), dilations=(1, 1, 1, 1), padding=b"SAME", data_format=b"NHWC", num_bits=8):
+def _create(L, table_file, strides=(1, 1, 1, 1), dilations=(1, 1, 1, 1), padding=b"SAME", data_format=b"NHWC", num_bits=8,
+            op_name=OP):
     code, msg = C.c_int(-1), C.create_string_buffer(256)
-    op = L.shimtest_create(OP, table_file, num_bits, (C.c_int * 4)(*strides), (C.c_int * 4)(*dilations), padding,
+    op = L.shimtest_create(op_name, table_file, num_bits, (C.c_int * 4)(*strides), (C.c_int * 4)(*dilations), padding,
                            data_format, C.byref(code), msg, 256)
     return op, code.value, msg.value.decode()
 
@@ -78,6 +82,9 @@ def test_shim_keeps_the_reference_registration(harness):
     assert dev.value == b"GPU"
     assert hm.value == b"input_min,input_max,filter_min,filter_max"
     assert '.TypeConstraint<float>("T")' in open(SHIM).read()
+    # the depthwise op (no counterpart in the reference) is registered the same way under its own name
+    assert harness.shimtest_registration(DW_OP, dev, 32, hm, 256) == 1
+    assert dev.value == b"GPU" and hm.value == b"input_min,input_max,filter_min,filter_max"
 
 
 def test_shim_constructor_reports_the_reference_errors(harness, tmp_path):
@@ -131,6 +138,30 @@ def test_shim_compute_reproduces_the_reference(harness, tmp_path, case):
             assert torch.equal(out.view(torch.int32), want.view(torch.int32))
             err = float(np.abs(out.cpu().numpy() - gold).max() / np.abs(gold).max())
             assert err < 1e-5, err                          # the reference's own metric (test_table_approx_conv_2d.py:62)
+    finally:
+        harness.shimtest_destroy(op)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", cases.DEPTHWISE_CASES, ids=[c[0] for c in cases.DEPTHWISE_CASES])
+def test_depthwise_shim_compute_matches_the_checker(harness, tmp_path, case):
+    import torch
+    import tf_approximate_b200 as ax
+    name, ishape, (kh, kw, mult), stride, dil, pad, tspec, in_range, seed = case
+    gold = np.load(os.path.join(os.path.dirname(os.path.abspath(cases.__file__)), "oracle_aux.npz"))[name + "_out_exact"]
+    path = str(tmp_path / "table.bin")
+    ax.write_table(path, cases.make_table(tspec))
+    x, f = cases.make_inputs(ishape, (kh, kw, ishape[3], mult), in_range, seed)
+    mm = (in_range[0], in_range[1], float(f.min()), float(f.max()))
+    xd, fd = torch.from_numpy(x).cuda(), torch.from_numpy(f).cuda()
+    op, code, msg = _create(harness, path.encode(), strides=(1, stride[0], stride[1], 1), dilations=(1, dil[0], dil[1], 1),
+                            padding=pad.encode(), op_name=DW_OP)
+    assert op is not None, (code, msg)
+    try:
+        code, msg, dims, out = _compute(harness, op, xd, fd, mm, gold.shape)
+        assert code == 0, msg
+        assert dims == gold.shape
+        assert np.array_equal(out.cpu().numpy().view(np.uint32), gold.view(np.uint32))
     finally:
         harness.shimtest_destroy(op)
 

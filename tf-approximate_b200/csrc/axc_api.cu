@@ -219,6 +219,10 @@ const uint16_t *table_device_ptr(axc_table *t, int device, int *status)
     e = cudaSetDevice(device);
     if (e == cudaSuccess) e = cudaMalloc(&p, 65536 * sizeof(uint16_t));
     if (e == cudaSuccess) e = cudaMemcpy(p, t->host.data(), 65536 * sizeof(uint16_t), cudaMemcpyHostToDevice);
+    // A copy from pageable host memory returns once the data is staged; the transfer itself is ordered on the legacy
+    // stream only.  The caller's stream may be a non-blocking one, which does not wait for the legacy stream: wait
+    // here until the replica is complete (once per table and device).
+    if (e == cudaSuccess) e = cudaStreamSynchronize(cudaStreamLegacy);
     cudaSetDevice(prev);
     if (e != cudaSuccess) {
         if (p) cudaFree(p);
