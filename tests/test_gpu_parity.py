@@ -341,6 +341,43 @@ def test_first_use_of_a_table_on_a_non_blocking_stream(ax):
         assert torch.equal(y, want), i
 
 
+def test_host_threads_call_concurrently(ax):
+    """Four host threads, each with its own table handle, stream and workspace, call the op at the same time (ctypes
+    releases the interpreter lock during a call): every result equals the one computed alone."""
+    import threading
+    import torch
+    rng = np.random.Generator(np.random.PCG64(44))
+    jobs = []
+    for i in range(4):
+        x = torch.from_numpy(rng.uniform(-1, 1, (2, 14 + i, 14, 16)).astype(np.float32)).cuda()
+        f = torch.from_numpy(rng.normal(0, 0.1, (3, 3, 16, 32 * (i + 1))).astype(np.float32)).cuda()
+        lut = cases.make_table(("noisy", 600 + i))
+        want = ax.approx_conv2d_with_min_max_vars(x, f, -1.0, 1.0, -0.4, 0.4, [1, 1, 1, 1], 8, ax.Table(array=lut), "SAME")
+        jobs.append((x, f, lut, want))
+    torch.cuda.synchronize()
+    errors = []
+
+    def work(x, f, lut, want):
+        try:
+            stream = torch.cuda.Stream()
+            table = ax.Table(array=lut)                    # first use of this handle happens inside the thread
+            with torch.cuda.stream(stream):
+                for _ in range(10):
+                    y = ax.approx_conv2d_with_min_max_vars(x, f, -1.0, 1.0, -0.4, 0.4, [1, 1, 1, 1], 8, table, "SAME")
+                    stream.synchronize()
+                    if not torch.equal(y, want):
+                        errors.append("mismatch")
+        except Exception as e:                             # noqa: BLE001 - reported by the assertion below
+            errors.append(repr(e))
+
+    threads = [threading.Thread(target=work, args=j) for j in jobs]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+
+
 def test_empty_batch(ax):
     import torch
     y = ax.approx_conv2d_with_min_max_vars(torch.zeros(0, 8, 8, 4).cuda(), torch.zeros(3, 3, 4, 8).cuda(),
