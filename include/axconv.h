@@ -134,7 +134,11 @@ int axc_conv2d_plan_info(const void *workspace, int32_t out4[4], int device, voi
  *      (tf2/src/approx_nn_conv_ops.cpp:420-460, 510-664) with the quantisation state of
  *      Update() (tf2/src/approx_ops_types.h:158-197) passed by value --------------------
  * in_min/in_max/f_min/f_max are the op's host-memory scalar inputs 2..5.
- * An output with zero elements returns AXC_OK without launching anything (:449-450). */
+ * An output with zero elements returns AXC_OK without launching anything (:449-450).
+ * Once the table replica is on the device (axc_table_ensure_device, or an earlier call) the workspace-taking forward
+ * calls of this header (axc_conv2d_forward*, axc_depthwise_conv2d_forward, axc_depthwise_conv2d_forward_fused,
+ * axc_qconv2d_forward) only enqueue kernels and memsets on `stream`: they may be captured into a CUDA graph and
+ * replayed with the same buffers (tests/test_gpu_networks.py::test_forward_as_cuda_graph). */
 int axc_conv2d_forward(axc_table *table, const axc_conv_desc *desc,
                        const float *input, const float *filter,
                        float in_min, float in_max, float f_min, float f_max,

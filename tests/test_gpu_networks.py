@@ -172,3 +172,28 @@ def test_op_epilogue_bias_residual_relu(built):
         y3 = ax.approx_depthwise_conv2d_with_min_max_vars(xs, fd, *mmd, [1, stride, stride, 1], 8, t, "SAME", input_relu=True)
         y4 = ax.approx_depthwise_conv2d_with_min_max_vars(torch.relu(xs), fd, *mmd, [1, stride, stride, 1], 8, t, "SAME")
         assert torch.equal(y3, y4), shape
+
+
+def test_forward_as_cuda_graph(built):
+    """After a warm-up the calls only enqueue kernels on the caller's stream, so a whole forward pass (dense layers with
+    ReLUs and shortcuts riding along, depthwise layers fed by TMA) can be captured once and replayed on new inputs:
+    same bits as the calls made one by one."""
+    import torch
+    import tf_approximate_b200 as ax
+    from tf_approximate_b200 import workloads as W
+    dev = torch.device("cuda", 0)
+    for kind, hw, batch in (("resnet50", 64, 2), ("mobilenet_stack", 56, 4)):
+        net = W.Network(kind, hw=hw)
+        filters = W.make_filters(net.convs, 2600)
+        runner = W.GpuRunner(net, [ax.noisy_table(3095)], filters, dev)
+        x = torch.from_numpy(W.make_input(batch, net.hw, net.in_channels, 1006)).to(dev)
+        x2 = torch.from_numpy(W.make_input(batch, net.hw, net.in_channels, 1007)).to(dev)
+        runner.calibrate(torch.cat([x, x2]))
+        want, want2 = runner.forward(x), runner.forward(x2)
+        torch.cuda.synchronize()
+        replay, static_x, static_y = runner.capture(x)
+        for src, ref in ((x2, want2), (x, want), (x2, want2)):
+            static_x.copy_(src)
+            replay()
+            torch.cuda.synchronize()
+            assert torch.equal(static_y.view(torch.int32), ref.view(torch.int32)), kind

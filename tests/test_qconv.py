@@ -146,3 +146,35 @@ def test_table_less_op_is_the_exact_product_table_with_data_ranges(built):
     ref = torch.nn.functional.conv2d(x.permute(0, 3, 1, 2).double(), f.permute(3, 2, 0, 1).double(), padding=1).permute(0, 2, 3, 1)
     err = float((y.double() - ref).abs().max() / ref.abs().max())
     assert 0 < err < 0.05
+
+
+@pytest.mark.gpu
+def test_ax_conv2d_as_cuda_graph(built):
+    """After a first call the quantised entry point only enqueues work on the caller's stream: captured once, replayed
+    on new codes, same integers."""
+    import torch
+    import tf_approximate_b200 as ax
+    shape = QSHAPES[0]
+    n, h, w, c, kh, kw, co, stride, pad, rin, rf = shape
+    qin, qf = _operands(shape, 8)
+    qin2, _ = _operands(shape, 9)
+    table = ax.Table(array=cases.make_table(("noisy", 62)))
+    xd, xd2, fd = torch.from_numpy(qin).cuda(), torch.from_numpy(qin2).cuda(), torch.from_numpy(qf).cuda()
+
+    def call(x, out=None):
+        return ax.ax_conv2d(x, fd, rin[0], rin[1], rf[0], rf[1], [1, stride, stride, 1], pad, table=table, out=out)[0]
+    want, want2 = call(xd), call(xd2)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    static_x = xd.clone()
+    with torch.cuda.stream(side):
+        static_y = call(static_x)
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        call(static_x, out=static_y)
+    for src, ref in ((xd2, want2), (xd, want)):
+        static_x.copy_(src)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(static_y, ref)

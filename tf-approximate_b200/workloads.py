@@ -293,6 +293,24 @@ class GpuRunner:
         """fused: shortcut additions and ReLUs inside the convolution kernels (default) or as separate torch kernels."""
         return self.net.forward(x, self._conv, self.torch.relu, torch_maxpool3s2, fused=fused)
 
+    def capture(self, x, stream=None, warmup=2):
+        """The forward pass of a batch shaped like `x` as a CUDA graph: returns (replay, static_input, static_output).
+        Copy a batch into `static_input`, call `replay()`, read `static_output`.  The ranges must be calibrated.  The
+        warm-up calls leave everything a call needs outside the stream in place (table replicas, lookup plans in the
+        cached workspaces), so that the captured calls only enqueue kernels."""
+        torch = self.torch
+        stream = stream or torch.cuda.Stream(device=self.device)
+        static_x = x.clone()
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):
+            for _ in range(warmup):
+                self.forward(static_x)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            static_y = self.forward(static_x)
+        return graph.replay, static_x, static_y
+
 
 class CpuRunner:
     """Runs a Network on numpy arrays with a caller-supplied convolution
