@@ -59,7 +59,7 @@ def test_sharded_forward_and_gather_equal_single_gpu(built, tmp_path, batch):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
-    out = tmp_path / "verdict.txt"
+    out = tmp_path / "result.txt"
     mp.spawn(_worker, args=(2, _free_port(), "resnet20", 32, batch, str(out)), nprocs=2, join=True)
     assert out.read_text() == "same"
 
