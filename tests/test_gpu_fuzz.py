@@ -107,3 +107,47 @@ def test_depthwise_random_cases(built):
         assert dbg["status"] == 0, what
         assert np.array_equal(dbg["acc"].cpu().numpy(), ref["acc"]), what
         assert np.array_equal(y.cpu().numpy().view(np.uint32), ref["out_exact"].view(np.uint32)), what
+
+
+def test_quantised_random_cases(built):
+    """The uint8-in / int32-out entry point: random shapes, ranges with zero points inside and outside 0..255, weight
+    tuning on and off."""
+    import torch
+    import tf_approximate_b200 as ax
+    rng = np.random.Generator(np.random.PCG64(7003 + SEED))
+    lut = cases.make_table(("noisy", 73))
+    tuned = O.tune_table(lut)
+    table = ax.Table(array=lut)
+    done = 0
+    for it in range(40 * SCALE):
+        n, h, w = int(rng.integers(1, 3)), int(rng.integers(3, 20)), int(rng.integers(3, 20))
+        c = int(rng.choice([1, 3, 4, 8, 16, 32, 64]))
+        co = int(rng.choice([1, 5, 16, 32, 40, 96, 130]))
+        k = int(rng.integers(1, 5))
+        stride = int(rng.integers(1, 3))
+        pad = "SAME" if rng.integers(0, 2) else "VALID"
+        if pad == "VALID" and (h < k or w < k):
+            continue
+        if it % 2:
+            a = np.sort(rng.normal(0, 2, 2)).astype(np.float32)
+            b = np.sort(rng.normal(0, 0.5, 2)).astype(np.float32)
+            rin, rf = (float(a[0]), float(a[1])), (float(b[0]), float(b[1]))
+        else:
+            rin, rf = (-float(np.float32(rng.uniform(0.1, 3))), float(np.float32(rng.uniform(0.1, 3)))), (-0.5, 0.25)
+        zi, zf = O.quantized_zero_point(*rin), O.quantized_zero_point(*rf)
+        if max(abs(zi), abs(zf), 255) ** 2 * k * k * c > 2 ** 31 - 1:
+            continue                        # the functor's int32 total could overflow: refused by the library
+        tune = bool(rng.integers(0, 2))
+        qin = rng.integers(0, 256, (n, h, w, c), dtype=np.uint8)
+        qf = rng.integers(0, 256, (k, k, c, co), dtype=np.uint8)
+        d = O.desc(n, h, w, c, k, k, co, (stride, stride), (1, 1), pad)
+        want = O.qconv2d(d, tuned if tune else lut, qin, qf, zi, zf)
+        try:
+            y, lo, hi = ax.ax_conv2d(torch.from_numpy(qin).cuda(), torch.from_numpy(qf).cuda(), rin[0], rin[1], rf[0], rf[1],
+                                     [1, stride, stride, 1], pad, table=table, ax_tune=tune)
+        except ax.UnimplementedError:
+            continue                        # window placement differs from the functor's (stride much larger than the window)
+        assert np.array_equal(y.cpu().numpy(), want), (it, n, h, w, c, k, co, stride, pad, rin, rf, zi, zf, tune)
+        assert (lo, hi) == O.quantized_output_range(rin[0], rin[1], rf[0], rf[1])
+        done += 1
+    assert done >= 25 * SCALE
