@@ -177,6 +177,13 @@ int axc_depthwise_conv2d_forward_fused(axc_table *table, const axc_conv_desc *de
  * over `count` floats (the pass axc_conv2d_forward_fused runs after the convolution, without a bias). */
 int axc_add_residual(float *out, const float *residual, size_t count, int relu, int device, void *stream);
 
+/* Max pooling of an NHWC fp32 tensor with a k x k window, stride `stride` and TensorFlow's SAME padding (taps outside
+ * the image do not take part): out[n, oh, ow, c], oh = ceil(h / stride).  Not part of the op; the pooling step between
+ * the stem and the first residual block of the ResNet workloads, kept in NHWC so that no layout copy is needed.
+ * Max pooling commutes with ReLU, so a pending ReLU of the producing layer may be applied by the consumer as usual. */
+int axc_max_pool_same(const float *input, float *output, int n, int h, int w, int c, int k, int stride, int device,
+                      void *stream);
+
 /* Same op with the four range scalars read from DEVICE memory: `ranges` = {input_min, input_max, filter_min,
  * filter_max}, four floats on `device`, typically written by the reductions that precede the op in the
  * reference's Keras wrapper (tf2/python/keras/layers/fake_approx_convolutional.py:233-242).  The quantisation

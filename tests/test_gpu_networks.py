@@ -197,3 +197,23 @@ def test_forward_as_cuda_graph(built):
             replay()
             torch.cuda.synchronize()
             assert torch.equal(static_y.view(torch.int32), ref.view(torch.int32)), kind
+
+
+def test_max_pool_same_matches_torch(built):
+    """The NHWC pooling kernel against torch's max_pool2d with -inf padding placed as TensorFlow's SAME rule does."""
+    import torch
+    import tf_approximate_b200 as ax
+    g = torch.Generator(device="cuda").manual_seed(9)
+    for n, h, w, c, k, s in [(2, 112, 112, 64, 3, 2), (1, 7, 9, 5, 3, 2), (3, 8, 8, 16, 2, 2), (1, 13, 11, 12, 3, 1), (2, 1, 1, 4, 3, 2),
+                             (1, 6, 5, 3, 5, 3)]:
+        x = torch.randn((n, h, w, c), device="cuda", generator=g)
+        oh, ow = -(-h // s), -(-w // s)
+        ph, pw = max((oh - 1) * s + k - h, 0), max((ow - 1) * s + k - w, 0)
+        xc = torch.nn.functional.pad(x.permute(0, 3, 1, 2), (pw // 2, pw - pw // 2, ph // 2, ph - ph // 2), value=float("-inf"))
+        want = torch.nn.functional.max_pool2d(xc, k, s).permute(0, 2, 3, 1).contiguous()
+        got = ax.ops.max_pool_same(x, k, s)
+        assert got.shape == want.shape and torch.equal(got, want), (n, h, w, c, k, s)
+        sliced = x[:, :, :, : max(c - 1, 1)]                       # a non-contiguous view, odd channel count
+        got2 = ax.ops.max_pool_same(sliced, k, s)
+        assert torch.equal(got2, want[..., : max(c - 1, 1)])
+    assert ax.ops.max_pool_same(torch.zeros((0, 8, 8, 4), device="cuda")).shape == (0, 4, 4, 4)

@@ -14,7 +14,7 @@ SYMBOLS = [
     "axc_conv2d_forward", "axc_conv2d_forward_device_ranges", "axc_depthwise_conv2d_forward",
     "axc_depthwise_conv2d_forward_noalloc", "axc_depthwise_conv2d_status",
     "axc_quant_props", "axc_status_string", "axc_last_cuda_error", "axc_launch_count", "axc_measure_lookup_peak", "axc_debug_bounds_record",
-    "axc_add_residual", "axc_conv2d_forward_fused", "axc_depthwise_conv2d_forward_fused", "axc_tensor_range", "axc_fake_quant", "axc_conv2d_forward_sharded", "axc_gather_outputs",
+    "axc_add_residual", "axc_max_pool_same", "axc_conv2d_forward_fused", "axc_depthwise_conv2d_forward_fused", "axc_tensor_range", "axc_fake_quant", "axc_conv2d_forward_sharded", "axc_gather_outputs",
     "axc_qconv2d_workspace_bytes", "axc_qconv2d_forward", "axc_quantized_zero_point", "axc_quantized_output_range",
 ]
 
@@ -87,6 +87,7 @@ def load():
                                                      C.c_float, C.c_float, C.POINTER(Epilogue), C.c_void_p, C.c_void_p, C.c_size_t,
                                                      C.POINTER(DebugOut), C.c_int, C.c_void_p]
     L.axc_add_residual.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_void_p]
+    L.axc_max_pool_same.argtypes = [C.c_void_p, C.c_void_p] + [C.c_int] * 6 + [C.c_int, C.c_void_p]
     L.axc_conv2d_forward_sharded.argtypes = [C.c_void_p, C.POINTER(ConvDesc), C.POINTER(Shard), C.c_int32, C.c_float, C.c_float,
                                              C.c_float, C.c_float, C.POINTER(C.c_int32)]
     L.axc_gather_outputs.argtypes = [C.POINTER(Shard), C.c_int32, C.c_size_t, C.c_void_p, C.c_int32]

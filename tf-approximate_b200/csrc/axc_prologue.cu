@@ -154,3 +154,80 @@ extern "C" int axc_fake_quant(const float *x, size_t count, const float *range2,
     if (prev != device) cudaSetDevice(prev);
     return e == cudaSuccess ? AXC_OK : cuda_failed(e);
 }
+
+// ------------------------------------------------------------------------------------------------
+// Max pooling, NHWC, SAME padding: one thread per output pixel and group of four channels (or one channel when the
+// channel count or the pointers do not allow 16-byte accesses).
+// ------------------------------------------------------------------------------------------------
+namespace axc {
+namespace {
+
+template <int V>
+__global__ void __launch_bounds__(256) max_pool_kernel(const float *__restrict__ in, float *__restrict__ out, int N, int H, int W,
+                                                       int C, int OH, int OW, int k, int stride, int ph, int pw)
+{
+    const int cv = C / V;
+    const long long total = (long long)N * OH * OW * cv;
+    const long long step = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+        const int c = int(i % cv) * V;
+        long long t = i / cv;
+        const int ow = int(t % OW);
+        t /= OW;
+        const int oh = int(t % OH);
+        const int n = int(t / OH);
+        float m[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) m[e] = -INFINITY;
+        for (int ky = 0; ky < k; ++ky) {
+            const int iy = oh * stride - ph + ky;
+            if (iy < 0 || iy >= H) continue;
+            for (int kx = 0; kx < k; ++kx) {
+                const int ix = ow * stride - pw + kx;
+                if (ix < 0 || ix >= W) continue;
+                const float *src = in + (((long long)n * H + iy) * W + ix) * C + c;
+                if (V == 4) {
+                    const float4 v = __ldg(reinterpret_cast<const float4 *>(src));
+                    m[0] = fmaxf(m[0], v.x); m[1 % V] = fmaxf(m[1 % V], v.y); m[2 % V] = fmaxf(m[2 % V], v.z); m[3 % V] = fmaxf(m[3 % V], v.w);
+                } else {
+                    m[0] = fmaxf(m[0], __ldg(src));
+                }
+            }
+        }
+        float *dst = out + (((long long)n * OH + oh) * OW + ow) * C + c;
+        if (V == 4) *reinterpret_cast<float4 *>(dst) = make_float4(m[0], m[1 % V], m[2 % V], m[3 % V]);
+        else dst[0] = m[0];
+    }
+}
+
+}  // namespace
+}  // namespace axc
+
+extern "C" int axc_max_pool_same(const float *input, float *output, int n, int h, int w, int c, int k, int stride, int device,
+                                 void *stream)
+{
+    using namespace axc;
+    if (n < 0 || h <= 0 || w <= 0 || c <= 0 || k <= 0 || stride <= 0) return AXC_INVALID_ARGUMENT;
+    const int oh = (h + stride - 1) / stride, ow = (w + stride - 1) / stride;
+    if ((long long)n * oh * ow * c == 0) return AXC_OK;
+    if (!input || !output) return AXC_INVALID_ARGUMENT;
+    const int need_h = (oh - 1) * stride + k - h, need_w = (ow - 1) * stride + k - w;
+    const int ph = (need_h > 0 ? need_h : 0) / 2, pw = (need_w > 0 ? need_w : 0) / 2;
+    DeviceInfo di;
+    int rc = device_info(device, &di);
+    if (rc) return rc;
+    int prev = 0;
+    AXC_CUDA(cudaGetDevice(&prev));
+    if (prev != device) AXC_CUDA(cudaSetDevice(device));
+    const bool vec = c % 4 == 0 && ((reinterpret_cast<uintptr_t>(input) | reinterpret_cast<uintptr_t>(output)) & 15u) == 0;
+    const long long total = (long long)n * oh * ow * (vec ? c / 4 : c);
+    const long long want = (total + 255) / 256;
+    const unsigned blocks = unsigned(want < (long long)di.sm_count * 16 ? want : (long long)di.sm_count * 16);
+    if (vec) max_pool_kernel<4><<<blocks, 256, 0, cudaStream_t(stream)>>>(input, output, n, h, w, c, oh, ow, k, stride, ph, pw);
+    else max_pool_kernel<1><<<blocks, 256, 0, cudaStream_t(stream)>>>(input, output, n, h, w, c, oh, ow, k, stride, ph, pw);
+    const cudaError_t e = cudaGetLastError();
+    count_launch();
+    if (prev != device) cudaSetDevice(prev);
+    return e == cudaSuccess ? AXC_OK : cuda_failed(e);
+}
+

@@ -393,6 +393,24 @@ def add_residual_(out, residual, relu=True):
     return out
 
 
+def max_pool_same(x, k=3, stride=2, out=None):
+    """Max pooling of an NHWC fp32 CUDA tensor, k x k window, TensorFlow's SAME padding - the pooling step of the
+    ResNet workloads without a layout copy."""
+    if not x.is_cuda or x.dtype != torch.float32 or x.dim() != 4:
+        raise InvalidArgumentError("max_pool_same expects a 4-D fp32 CUDA tensor (NHWC)")
+    x = x.contiguous()
+    n, h, w, c = (int(v) for v in x.shape)
+    oshape = (n, -(-h // stride), -(-w // stride), c)
+    if out is None:
+        out = torch.empty(oshape, dtype=torch.float32, device=x.device)
+    elif tuple(out.shape) != oshape or out.dtype != torch.float32 or out.device != x.device or not out.is_contiguous():
+        raise InvalidArgumentError("out must be a contiguous fp32 tensor of shape %s on the input's device" % (oshape,))
+    st = _lib.load().axc_max_pool_same(x.data_ptr(), out.data_ptr(), n, h, w, c, int(k), int(stride), _device_index(x.device),
+                                       C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream))
+    raise_for_status(st, "max pool", _cuda_detail() if st == 100 else "")
+    return out
+
+
 def tensor_range(x, out=None):
     """{min, max} of a fp32 CUDA tensor as two floats in device memory (one reduction kernel, no host round trip):
     the wrapper's reduce_min / reduce_max (tf2/python/keras/layers/fake_approx_convolutional.py:233-240)."""

@@ -230,6 +230,12 @@ def np_maxpool3s2(x):
     return out
 
 
+def gpu_maxpool3s2(x):
+    """3x3, stride 2, SAME on an NHWC CUDA tensor: the library's pooling kernel (no layout copy)."""
+    from . import ops
+    return ops.max_pool_same(x, 3, 2)
+
+
 def torch_maxpool3s2(x):
     import torch
     n, h, w, c = x.shape
@@ -291,7 +297,7 @@ class GpuRunner:
 
     def forward(self, x, fused=True):
         """fused: shortcut additions and ReLUs inside the convolution kernels (default) or as separate torch kernels."""
-        return self.net.forward(x, self._conv, self.torch.relu, torch_maxpool3s2, fused=fused)
+        return self.net.forward(x, self._conv, self.torch.relu, gpu_maxpool3s2 if fused else torch_maxpool3s2, fused=fused)
 
     def capture(self, x, stream=None, warmup=2):
         """The forward pass of a batch shaped like `x` as a CUDA graph: returns (replay, static_input, static_output).
